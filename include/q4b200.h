@@ -1,0 +1,204 @@
+/*
+ * q4b200 - C ABI of the B200 (sm_100a) decode path for AWQ W4 g128 Llama-2 models in the
+ * llama_cu_awq packed file format.
+ *
+ * Every entry point replaces one host wrapper of the reference program (cited per function as
+ * file:line within the llama_cu_awq project). Conventions:
+ *   - plain pointers and sizes only; `stream` is a cudaStream_t passed as void*;
+ *   - fp16 data is passed as uint16_t* (IEEE binary16 bits);
+ *   - all data pointers are device pointers of the current device unless a comment says
+ *     "pinned host"; the caller owns every buffer;
+ *   - calls are asynchronous on `stream`; nothing is allocated by the per-token entry points;
+ *   - the return value is a status code (Q4_OK = 0). The reference prints a message and calls
+ *     exit() where these functions return Q4_ERR_UNSUPPORTED_SIZE / Q4_ERR_CUDA;
+ *   - the token position is never passed by value on the per-token path: kernels read it from
+ *     device memory (`pPos`), as the reference's kernels do, so that a captured CUDA graph
+ *     can be replayed for every token.
+ * There is no CPU fallback: without a CUDA device every compute entry point returns Q4_ERR_CUDA.
+ */
+#ifndef Q4B200_H
+#define Q4B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define Q4_OK 0
+#define Q4_ERR_UNSUPPORTED_SIZE 1 /* reference: "Unsupported matmul size. Exiting" (llama2_q4.cu:358,368,379,394) */
+#define Q4_ERR_CUDA 2             /* reference: CUDA_CHECK -> exit (llama2_q4.cu:35-43) */
+#define Q4_ERR_IO 3               /* reference: "Couldn't open file" / "error reading weights" -> exit (llama2_q4.cu:203-208,629-631) */
+#define Q4_ERR_BAD_MODEL 4        /* header or file length inconsistent */
+#define Q4_ERR_INVALID 5          /* bad argument */
+#define Q4_ERR_TIMEOUT 6          /* a bounded device-side wait (peer flag) ran out */
+#define Q4_ERR_LIMIT 7            /* request exceeds a fixed capacity of the entry point */
+
+#define Q4_GROUP_SIZE 128 /* llama2_q4.cu:31, weight_packer.cpp:7 */
+#define Q4_MAX_GPUS 8     /* cuda_comm.h:16 */
+#define Q4_MAX_SEQ_LEN (128 * 1024) /* common.h:13 */
+
+/* Model-config header: the first 32 bytes of the packed file. common.h:15-24, weight_packer.cpp:9-18. */
+typedef struct {
+    int32_t dim, hidden_dim, n_layers, n_heads, n_kv_heads, vocab_size, seq_len;
+    float rope_theta;
+} q4_config;
+
+/* One quantized matrix, K inputs x N outputs, K-contiguous per output. common.h:26-30.
+ *   weight u32[N][4*ceil(K/32)]  nibble i of word j holds q(n, 8j+i)
+ *   zeros  u32[N][ceil(ceil(K/128)/8)]
+ *   scales f16[N][ceil(K/128)] */
+typedef struct {
+    const uint32_t* weight;
+    const uint32_t* zeros;
+    const uint16_t* scales;
+} q4_qweight;
+
+/* CPU<->GPU mailbox in pinned host memory. common.h:57-60. */
+typedef struct {
+    volatile int32_t pos;
+    int32_t tokens[Q4_MAX_SEQ_LEN];
+} q4_shared_data;
+
+const char* q4_status_string(int status);
+/* Library/ABI version and the SM architecture the kernels were built for ("sm_100a"). */
+int q4_abi_version(void);
+const char* q4_build_arch(void);
+
+/* ---------------------------------------------------------------------------------------------
+ * Per-op entry points: the op-wrapper boundary of llama2_q4.cu:347-427 and sampler.h:77-84.
+ * ------------------------------------------------------------------------------------------- */
+
+/* rmsnorm(): llama2_q4.cu:347-350, kernel gpu_kernels.h:72-105. o = x * rsqrt(mean(x^2) + 1e-5) * weight. */
+int q4_rmsnorm(void* stream, uint16_t* o, const uint16_t* x, const uint16_t* weight, int size);
+
+/* matmul(QWeight): llama2_q4.cu:367-376, kernels gpu_kernels.h:179-248.
+ * xout[n] = sum_k (q(n,k) - z(n,k/128)) * s(n,k/128) * x[k]; when accum != 0 the old xout[n] / gpu_count
+ * is added first (fused residual); when loff != -1 the result is written at xout + loff + (*pPos) * opSize
+ * (KV-cache row). inpSize and opSize must be multiples of 8. */
+int q4_matmul_q4(void* stream, uint16_t* xout, const uint16_t* x, const q4_qweight* w, int inpSize, int opSize,
+                 int accum, int gpu_count, int loff, const int* pPos);
+
+/* qkv_matvec(): llama2_q4.cu:378-391, kernel gpu_kernels.h:250-262. Three projections of the same x in one
+ * launch; K and V land in cache row *pPos at offset loff. Unlike the reference, kvSize may differ from opSize
+ * (grouped-query models; the reference issues three matmul() calls there, llama2_q4.cu:457-459). */
+int q4_qkv_matvec(void* stream, uint16_t* q, uint16_t* key_cache, uint16_t* value_cache, const uint16_t* x,
+                  const q4_qweight* qw, const q4_qweight* kw, const q4_qweight* vw, int inpSize, int opSize,
+                  int kvSize, int loff, const int* pPos);
+
+/* ffn_matvec_silu(): llama2_q4.cu:393-404, kernel gpu_kernels.h:264-283. xout = silu(gate·x) * (up·x). */
+int q4_ffn_matvec_silu(void* stream, uint16_t* xout, const uint16_t* x, const q4_qweight* gate_w,
+                       const q4_qweight* up_w, int inpSize, int opSize);
+
+/* RoPERotation(): llama2_q4.cu:406-408, kernel gpu_kernels.h:340-363. Rotates q (num_heads heads) and the K row
+ * just written at k + loff + (*pPos) * num_kv_heads * head_size (first num_kv_heads heads), in place. */
+int q4_rope(void* stream, uint16_t* q, uint16_t* k, int num_heads, int num_kv_heads, int head_size, const int* pPos,
+            int loff, float rope_theta);
+
+/* MultiHeadAttention(): llama2_q4.cu:410-427, kernels gpu_kernels.h:150-176,365-454,287-337.
+ * One query per head over cache rows 0..*pPos; key_cache/value_cache already point at the layer; the row
+ * stride is num_heads*head_size/kv_mul halfs. `scratch` replaces the reference's `att` buffer and must hold
+ * q4_attention_scratch_bytes(num_heads, head_size) bytes; it carries the per-split partial results. */
+size_t q4_attention_scratch_bytes(int num_heads, int head_size);
+int q4_attention(void* stream, uint16_t* output, const uint16_t* q, const uint16_t* key_cache,
+                 const uint16_t* value_cache, void* scratch, int num_heads, int head_size, int kv_mul, int max_seq_len,
+                 const int* pPos);
+
+/* matmul(half*): llama2_q4.cu:357-365, kernel gpu_kernels.h:117-147. fp16 GEMV used for the classifier:
+ * xout[d] = alpha * sum_n w[d][n] * x[n]. n and d must be multiples of 8. */
+int q4_matmul_f16(void* stream, uint16_t* xout, const uint16_t* x, const uint16_t* w, int n, int d, float alpha);
+
+/* Embedding row gather: copy_embedding_kernel launch at llama2_q4.cu:441 (gpu_kernels.h:61-69).
+ * `tokens` is the pinned-host token array; the row of tokens[*pPos] is copied to x. */
+int q4_embed(void* stream, uint16_t* x, const uint16_t* table, int dim, const int* tokens, const int* pPos);
+
+/* Greedy branch of sample(): sampler.h:77-84, kernel gpu_kernels.h:456-501. Writes argmax(logits) to
+ * tokens_pinned[*pos_pinned + 1] when write_token != 0 and increments both position counters. Among equal
+ * maxima the lowest index wins (the reference leaves that case to a race). */
+int q4_argmax(void* stream, const uint16_t* logits, int size, int* tokens_pinned, volatile int* pos_pinned,
+              int* pos_dev, int write_token);
+
+/* Test hook without a twin in the reference: dequantised weights w(n,k) as fp32 [N][K]
+ * (the values gpu_kernels.h:204-205 computes on the fly), and raw nibbles as bytes. */
+int q4_dequant(void* stream, float* out, const q4_qweight* w, int K, int N);
+int q4_unpack_nibbles(void* stream, uint8_t* q_out, uint8_t* z_out, const q4_qweight* w, int K, int N);
+
+/* ---------------------------------------------------------------------------------------------
+ * Collectives: cuda_comm.h:80-300 (NCCL-shaped, as in the reference). One communicator per GPU.
+ * Ranks may be threads of one process (the reference's model: peer pointers are exchanged through the
+ * shared q4_comm_id) or separate processes (handles exchanged by the caller, q4_comm_export/_import).
+ * ------------------------------------------------------------------------------------------- */
+typedef struct q4_comm q4_comm;
+typedef struct q4_comm_id q4_comm_id;
+
+/* cudaCommGetUniqueId / cudaCommIdDestroy: cuda_comm.h:80-89,288-300. In-process rendezvous object. */
+int q4_comm_id_create(q4_comm_id** id, int gpu_count);
+int q4_comm_id_destroy(q4_comm_id* id);
+/* cudaCommInitRank: cuda_comm.h:91-141. Thread-per-GPU flavour; call with device `rank`'s context current. */
+int q4_comm_init_rank(q4_comm** comm, int gpu_count, q4_comm_id* id, int rank);
+/* Process-per-GPU flavour: create the local inbox, export its 64-byte IPC handle, import every peer's. */
+int q4_comm_create_local(q4_comm** comm, int gpu_count, int rank);
+int q4_comm_export(q4_comm* comm, uint8_t handle[64]);
+int q4_comm_import(q4_comm* comm, int peer, const uint8_t handle[64]);
+/* cudaAllReduce (fp16 sum, in place): cuda_comm.h:160-224; call sites llama2_q4.cu:474-476,505-507.
+ * One-shot push over NVLink: every rank stores its vector into every peer's inbox and sums the gpu_count
+ * inbox slots in rank order in fp32, so all ranks obtain identical bits. count <= Q4_COMM_MAX_HALFS. */
+#define Q4_COMM_MAX_HALFS 32768
+int q4_all_reduce(q4_comm* comm, void* stream, uint16_t* buf, int count);
+/* cudaAllGather (fp16): cuda_comm.h:227-275; call site llama2_q4.cu:534-536. recv holds gpu_count*sendcount. */
+int q4_all_gather(q4_comm* comm, void* stream, const uint16_t* send, uint16_t* recv, int sendcount);
+/* Device-side wait status: 0, or Q4_ERR_TIMEOUT after a peer flag did not arrive within the bound. */
+int q4_comm_status(q4_comm* comm);
+/* cudaCommDestroy: cuda_comm.h:278-286. */
+int q4_comm_destroy(q4_comm* comm);
+
+/* ---------------------------------------------------------------------------------------------
+ * Model level: build_transformer (llama2_q4.cu:625-659), run_transformer (:541-601),
+ * generate_thread (:683-757).
+ * ------------------------------------------------------------------------------------------- */
+typedef struct q4_model q4_model;
+
+#define Q4_TP_NONE 0   /* llama2_q4.cu:45-50 */
+#define Q4_TP_COLUMN 1
+#define Q4_TP_HYBRID 2
+
+/* Reads the packed file (header + tensors in the order of weight_packer.cpp:256-291), keeps this rank's shard
+ * on the current device (Megatron split of llama2_q4.cu:299-332, with row splits moved to 128-input group
+ * boundaries) and allocates the run state (llama2_q4.cu:62-91). comm may be NULL when gpu_count == 1. */
+int q4_model_load(q4_model** model, const char* path, int rank, int gpu_count, int tp_mode, q4_comm* comm);
+int q4_model_free(q4_model* model);
+int q4_model_config(const q4_model* model, q4_config* out);
+/* Pinned mailbox of this rank (tokens[], pos) and device buffers, for tests and for the host loop. */
+q4_shared_data* q4_model_shared(q4_model* model);
+const uint16_t* q4_model_logits(const q4_model* model); /* device, vocab_size halfs */
+const uint16_t* q4_model_x(const q4_model* model);      /* device, dim halfs */
+/* Resets position counters (device and pinned) to `pos` and copies `n` prompt ids into the mailbox. */
+int q4_model_reset(q4_model* model, const int* prompt_tokens, int n, int pos);
+/* run_transformer(): one token at the current position on `stream`: embedding .. logits, then the greedy
+ * hand-off (gen_token != 0 writes the sampled id to tokens[pos+1]); asynchronous. `path`: 0 = per-op kernels
+ * launched one by one, 1 = the same launches replayed from a captured CUDA graph, 2 = fused schedule. */
+int q4_model_forward(q4_model* model, void* stream, int gen_token, int path);
+/* generate_thread(): the token loop with the reference's timing window (llama2_q4.cu:708-745). Runs `steps`
+ * positions starting from the n_prompt given ids, stops at EOS (id 2). out_tokens receives tokens[0..steps];
+ * *timed_tokens = pos-1 and *seconds is the wall time of the loop. */
+int q4_generate(q4_model* model, const int* prompt_tokens, int n_prompt, int steps, int path, int* out_tokens,
+                int* timed_tokens, double* seconds);
+/* Algorithmic bytes one token at position `pos` reads and writes on this rank (weights, metadata,
+ * classifier, norms, embedding row, KV rows). */
+double q4_model_token_bytes(const q4_model* model, int pos);
+
+/* Host-side shard helpers (no GPU needed): copy rank `rank`'s shard of a quantized matrix held in host
+ * memory. Column split = contiguous slice of outputs (llama2_q4.cu:254-263). Row split = slice of inputs on
+ * 128-input group boundaries with zero nibbles re-packed (replaces llama2_q4.cu:264-285, which misplaces
+ * zeros and scales when groups-per-rank is odd or fractional). q4_row_split_range gives the input range. */
+void q4_row_split_range(int K, int gpu_count, int rank, int* k_begin, int* k_count);
+int q4_shard_columns_host(const q4_qweight* src, int K, int N, int gpu_count, int rank, uint32_t* w_out,
+                          uint32_t* z_out, uint16_t* s_out);
+int q4_shard_rows_host(const q4_qweight* src, int K, int N, int gpu_count, int rank, uint32_t* w_out, uint32_t* z_out,
+                       uint16_t* s_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* Q4B200_H */

@@ -1,0 +1,256 @@
+// Tensor-parallel collectives for 8-16 KB fp16 vectors: one-shot push over NVLink / NVSwitch peer memory.
+// Replaces cudaAllReduce / cudaAllGather / reduce_sum_half_kernel of the reference (cuda_comm.h:144-275),
+// which stage through a 128 MB buffer, two host barriers and one kernel per peer for every call.
+//
+// Every rank owns an inbox in its own memory: slots[2][g][Q4_COMM_MAX_HALFS] halfs and flags[2][g] words,
+// double buffered by the parity of a call counter (epoch). A call is one kernel:
+//   1. store this rank's vector into slot [parity][rank] of EVERY rank's inbox (plain 128-bit peer stores),
+//   2. fence, then release-store the epoch into flag [parity][rank] of every inbox,
+//   3. acquire-spin (bounded) on the g local flags,
+//   4. add the g local slots in rank order in fp32 (all ranks see the same order -> identical bits; the
+//      reference adds in a rank-dependent order in fp16, cuda_comm.h:193-219) and write fp16.
+// Parity p is reused at epoch e+2; a rank can only reach e+2 after every peer published e+1, which a peer does
+// only after it finished reading its epoch-e slots, so no slot is overwritten while it is still being read.
+// No host synchronisation is involved, so the call can be captured in a CUDA graph.
+// Waits are bounded: after kWaitLimitNs the kernel records Q4_ERR_TIMEOUT in the status word and returns.
+#include <mutex>
+#include <string.h>
+
+#include "q4_common.cuh"
+
+namespace {
+constexpr unsigned long long kWaitLimitNs = 2000ULL * 1000 * 1000;  // 2 s on the device's global timer
+constexpr int kCommThreads = 1024;
+
+struct Inbox {
+    uint32_t flags[2][Q4_MAX_GPUS];
+    uint32_t epoch;    // local call counter
+    uint32_t status;   // 0 or Q4_ERR_TIMEOUT
+    uint32_t pad[14];
+    __half slots[2][Q4_MAX_GPUS][Q4_COMM_MAX_HALFS];
+};
+
+struct PeerPtrs { Inbox* p[Q4_MAX_GPUS]; };
+}  // namespace
+
+struct q4_comm_id {
+    int gpu_count;
+    std::mutex mu;
+    Inbox* inbox[Q4_MAX_GPUS];
+    int registered;
+};
+
+struct q4_comm {
+    int rank, gpu_count;
+    Inbox* local;
+    PeerPtrs peers;
+    bool imported[Q4_MAX_GPUS];  // opened through IPC (must be closed)
+    q4_comm_id* id;
+};
+
+namespace {
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) { asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// mode 0: all-reduce (sum) of buf[count] in place. mode 1: all-gather, send[count] -> recv[g*count].
+__global__ void __launch_bounds__(kCommThreads) comm_kernel(PeerPtrs peers, Inbox* local, int rank, int g, __half* buf, const __half* send,
+                                                            int count, int mode) {
+    __shared__ uint32_t s_epoch;
+    griddep_wait();
+    griddep_launch_dependents();
+    if (threadIdx.x == 0) s_epoch = ++local->epoch;
+    __syncthreads();
+    const uint32_t epoch = s_epoch;
+    const int par = epoch & 1;
+    const __half* src = mode == 0 ? buf : send;
+    const int nvec = count >> 3;  // count is a multiple of 8
+    for (int p = 0; p < g; p++) {
+        uint4* dst = reinterpret_cast<uint4*>(peers.p[p]->slots[par][rank]);
+        for (int i = threadIdx.x; i < nvec; i += blockDim.x) dst[i] = reinterpret_cast<const uint4*>(src)[i];
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < g) {
+        st_release_sys(&peers.p[threadIdx.x]->flags[par][rank], epoch);
+        unsigned long long t_start = 0;
+        unsigned spins = 0;
+        while (ld_acquire_sys(&local->flags[par][threadIdx.x]) != epoch) {
+            if ((++spins & 255u) == 0) {
+                const unsigned long long now = global_timer_ns();
+                if (t_start == 0) t_start = now;
+                else if (now - t_start > kWaitLimitNs) { local->status = Q4_ERR_TIMEOUT; break; }
+            }
+        }
+    }
+    __syncthreads();
+    if (mode == 0) {
+        for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+            float acc[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) acc[j] = 0.f;
+            for (int r = 0; r < g; r++) {
+                const uint4 v = reinterpret_cast<const uint4*>(local->slots[par][r])[i];
+                const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+                for (int j = 0; j < 4; j++) { const float2 f = __half22float2(h[j]); acc[2 * j] += f.x; acc[2 * j + 1] += f.y; }
+            }
+            uint4 o;
+            __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+            for (int j = 0; j < 4; j++) oh[j] = __floats2half2_rn(acc[2 * j], acc[2 * j + 1]);
+            reinterpret_cast<uint4*>(buf)[i] = o;
+        }
+    } else {
+        for (int r = 0; r < g; r++)
+            for (int i = threadIdx.x; i < nvec; i += blockDim.x)
+                reinterpret_cast<uint4*>(buf + (size_t)r * count)[i] = reinterpret_cast<const uint4*>(local->slots[par][r])[i];
+    }
+}
+
+int alloc_inbox(Inbox** out) {
+    Q4_CUDA_TRY(cudaMalloc((void**)out, sizeof(Inbox)));
+    Q4_CUDA_TRY(cudaMemset(*out, 0, sizeof(Inbox)));
+    Q4_CUDA_TRY(cudaDeviceSynchronize());
+    return Q4_OK;
+}
+
+}  // namespace
+
+extern "C" int q4_comm_id_create(q4_comm_id** id, int gpu_count) {
+    if (!id || gpu_count < 1 || gpu_count > Q4_MAX_GPUS) return Q4_ERR_INVALID;
+    q4_comm_id* p = new q4_comm_id();
+    p->gpu_count = gpu_count;
+    p->registered = 0;
+    for (int i = 0; i < Q4_MAX_GPUS; i++) p->inbox[i] = nullptr;
+    *id = p;
+    return Q4_OK;
+}
+
+extern "C" int q4_comm_id_destroy(q4_comm_id* id) {
+    delete id;
+    return Q4_OK;
+}
+
+// Thread-per-GPU flavour. Every rank allocates its inbox, publishes the pointer in the shared id and waits
+// (bounded) until all gpu_count ranks have done so; all ranks must therefore call this concurrently.
+extern "C" int q4_comm_init_rank(q4_comm** comm, int gpu_count, q4_comm_id* id, int rank) {
+    if (!comm || !id || rank < 0 || rank >= gpu_count || gpu_count != id->gpu_count) return Q4_ERR_INVALID;
+    q4_comm* c = new q4_comm();
+    c->rank = rank;
+    c->gpu_count = gpu_count;
+    c->id = id;
+    for (int i = 0; i < Q4_MAX_GPUS; i++) { c->peers.p[i] = nullptr; c->imported[i] = false; }
+    int dev = 0;
+    Q4_CUDA_TRY(cudaGetDevice(&dev));
+    for (int i = 0; i < gpu_count; i++) {
+        if (i == dev) continue;
+        int can = 0;
+        Q4_CUDA_TRY(cudaDeviceCanAccessPeer(&can, dev, i));
+        if (!can) { delete c; return Q4_ERR_CUDA; }
+        cudaError_t e = cudaDeviceEnablePeerAccess(i, 0);
+        if (e == cudaErrorPeerAccessAlreadyEnabled) cudaGetLastError();
+        else if (e != cudaSuccess) { q4_note_cuda_error(e, __FILE__, __LINE__); delete c; return Q4_ERR_CUDA; }
+    }
+    if (int e = alloc_inbox(&c->local)) { delete c; return e; }
+    {
+        std::lock_guard<std::mutex> lk(id->mu);
+        id->inbox[rank] = c->local;
+        id->registered++;
+    }
+    // bounded rendezvous: wait until every rank has published its inbox
+    for (long long spins = 0;; spins++) {
+        {
+            std::lock_guard<std::mutex> lk(id->mu);
+            if (id->registered >= gpu_count) break;
+        }
+        if (spins > 2000000000LL) { return Q4_ERR_TIMEOUT; }
+    }
+    for (int i = 0; i < gpu_count; i++) c->peers.p[i] = id->inbox[i];
+    *comm = c;
+    return Q4_OK;
+}
+
+extern "C" int q4_comm_create_local(q4_comm** comm, int gpu_count, int rank) {
+    if (!comm || gpu_count < 1 || gpu_count > Q4_MAX_GPUS || rank < 0 || rank >= gpu_count) return Q4_ERR_INVALID;
+    q4_comm* c = new q4_comm();
+    c->rank = rank;
+    c->gpu_count = gpu_count;
+    c->id = nullptr;
+    for (int i = 0; i < Q4_MAX_GPUS; i++) { c->peers.p[i] = nullptr; c->imported[i] = false; }
+    if (int e = alloc_inbox(&c->local)) { delete c; return e; }
+    c->peers.p[rank] = c->local;
+    *comm = c;
+    return Q4_OK;
+}
+
+extern "C" int q4_comm_export(q4_comm* comm, uint8_t handle[64]) {
+    if (!comm || !handle) return Q4_ERR_INVALID;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    cudaIpcMemHandle_t h;
+    Q4_CUDA_TRY(cudaIpcGetMemHandle(&h, comm->local));
+    memcpy(handle, &h, 64);
+    return Q4_OK;
+}
+
+extern "C" int q4_comm_import(q4_comm* comm, int peer, const uint8_t handle[64]) {
+    if (!comm || !handle || peer < 0 || peer >= comm->gpu_count) return Q4_ERR_INVALID;
+    if (peer == comm->rank) return Q4_OK;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, 64);
+    void* p = nullptr;
+    Q4_CUDA_TRY(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    comm->peers.p[peer] = (Inbox*)p;
+    comm->imported[peer] = true;
+    return Q4_OK;
+}
+
+static int comm_launch(q4_comm* c, cudaStream_t s, __half* buf, const __half* send, int count, int mode) {
+    if (!c || !buf || count <= 0 || (count & 7)) return Q4_ERR_INVALID;
+    if (count > Q4_COMM_MAX_HALFS) return Q4_ERR_LIMIT;
+    for (int i = 0; i < c->gpu_count; i++)
+        if (!c->peers.p[i]) return Q4_ERR_INVALID;
+    Q4Launch L(dim3(1), dim3(kCommThreads), 0, s);
+    Q4_CUDA_TRY(cudaLaunchKernelEx(&L.cfg, comm_kernel, c->peers, c->local, c->rank, c->gpu_count, buf, send, count, mode));
+    return Q4_OK;
+}
+
+extern "C" int q4_all_reduce(q4_comm* comm, void* stream, uint16_t* buf, int count) {
+    if (comm && comm->gpu_count == 1) return Q4_OK;  // cuda_comm.h:163-171: in place, nothing to do
+    return comm_launch(comm, (cudaStream_t)stream, (__half*)buf, nullptr, count, 0);
+}
+
+extern "C" int q4_all_gather(q4_comm* comm, void* stream, const uint16_t* send, uint16_t* recv, int sendcount) {
+    if (!send) return Q4_ERR_INVALID;
+    if (comm && comm->gpu_count == 1) {
+        if (send != recv) Q4_CUDA_TRY(cudaMemcpyAsync(recv, send, (size_t)sendcount * 2, cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+        return Q4_OK;
+    }
+    return comm_launch(comm, (cudaStream_t)stream, (__half*)recv, (const __half*)send, sendcount, 1);
+}
+
+extern "C" int q4_comm_status(q4_comm* comm) {
+    if (!comm) return Q4_ERR_INVALID;
+    uint32_t st = 0;
+    Q4_CUDA_TRY(cudaMemcpy(&st, &comm->local->status, 4, cudaMemcpyDeviceToHost));
+    return (int)st;
+}
+
+extern "C" int q4_comm_destroy(q4_comm* comm) {
+    if (!comm) return Q4_OK;
+    for (int i = 0; i < comm->gpu_count; i++)
+        if (comm->imported[i]) cudaIpcCloseMemHandle(comm->peers.p[i]);
+    cudaFree(comm->local);
+    delete comm;
+    return Q4_OK;
+}
