@@ -173,6 +173,8 @@ int q4_model_config(const q4_model* model, q4_config* out);
 q4_shared_data* q4_model_shared(q4_model* model);
 const uint16_t* q4_model_logits(const q4_model* model); /* device, vocab_size halfs */
 const uint16_t* q4_model_x(const q4_model* model);      /* device, dim halfs */
+/* Synchronous device-to-host copy of a run-state vector: what = 0 logits (vocab_size halfs), 1 x (dim halfs). */
+int q4_model_read(const q4_model* model, int what, uint16_t* host_out);
 /* Resets position counters (device and pinned) to `pos` and copies `n` prompt ids into the mailbox. */
 int q4_model_reset(q4_model* model, const int* prompt_tokens, int n, int pos);
 /* run_transformer(): one token at the current position on `stream`: embedding .. logits, then the greedy
@@ -187,6 +189,11 @@ int q4_generate(q4_model* model, const int* prompt_tokens, int n_prompt, int ste
 /* Algorithmic bytes one token at position `pos` reads and writes on this rank (weights, metadata,
  * classifier, norms, embedding row, KV rows). */
 double q4_model_token_bytes(const q4_model* model, int pos);
+
+/* Measurement hook: launches the fused gate/up GEMV of every layer back to back `reps` times on `stream`
+ * (each layer's own weights, so the working set is far larger than L2) between two CUDA events on that stream.
+ * Returns the total milliseconds and the algorithmic bytes one launch moves. */
+int q4_model_time_ffn(q4_model* model, void* stream, int reps, double* total_ms, double* bytes_per_launch);
 
 /* Host-side shard helpers (no GPU needed): copy rank `rank`'s shard of a quantized matrix held in host
  * memory. Column split = contiguous slice of outputs (llama2_q4.cu:254-263). Row split = slice of inputs on

@@ -1,0 +1,325 @@
+// llama2_q4: command-line front end with the reference program's flags and output lines
+// (llama2_q4.cu:800-936 main/error_usage/get_and_print_gpu_info, :759-786 generate), driving the library
+// through its C ABI only. One host thread per GPU, as in the reference (llama2_q4.cu:776-779).
+//
+// Extra flags (not in the reference): -k <file> reads whitespace-separated prompt token ids instead of text,
+// -g <0|1> picks the forward path (per-op launches / CUDA-graph replay).
+#include <cuda_runtime_api.h>
+
+#include <algorithm>
+#include <chrono>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <ctime>
+#include <string>
+#include <thread>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/q4b200.h"
+
+namespace {
+
+constexpr int kBos = 1, kEos = 2;  // tokenizer.h:8-9
+
+// llama2.c-format vocabulary file (tokenizer.bin): uint32 max_token_length, then per token
+// float32 score, int32 length, bytes. Encoding is greedy best-score pair merging over UTF-8 pieces with byte
+// fallback (+3 offset), decoding strips the leading space after BOS and maps <0xXX> pieces to raw bytes
+// (behaviour of tokenizer.h:36-223).
+class Vocab {
+public:
+    bool load(const char* path, int vocab_size) {
+        FILE* f = fopen(path, "rb");
+        if (!f) return false;
+        uint32_t max_len = 0;
+        if (fread(&max_len, 4, 1, f) != 1) { fclose(f); return false; }
+        pieces_.resize(vocab_size);
+        scores_.resize(vocab_size);
+        for (int i = 0; i < vocab_size; i++) {
+            int len = 0;
+            if (fread(&scores_[i], 4, 1, f) != 1 || fread(&len, 4, 1, f) != 1 || len < 0) { fclose(f); return false; }
+            pieces_[i].resize(len);
+            if (len && fread(&pieces_[i][0], len, 1, f) != 1) { fclose(f); return false; }
+            index_.emplace(pieces_[i], i);
+        }
+        fclose(f);
+        return true;
+    }
+    bool loaded() const { return !pieces_.empty(); }
+
+    std::vector<int> encode(const std::string& text, bool bos) const {
+        std::vector<int> out;
+        if (bos) out.push_back(kBos);
+        if (text.empty()) return out;
+        auto sp = index_.find(" ");
+        if (sp != index_.end()) out.push_back(sp->second);  // dummy prefix
+        for (size_t i = 0; i < text.size();) {
+            size_t n = 1;
+            while (i + n < text.size() && (static_cast<unsigned char>(text[i + n]) & 0xC0) == 0x80 && n < 4) n++;
+            auto it = index_.find(text.substr(i, n));
+            if (it != index_.end()) out.push_back(it->second);
+            else
+                for (size_t b = 0; b < n; b++) out.push_back(static_cast<unsigned char>(text[i + b]) + 3);
+            i += n;
+        }
+        for (;;) {
+            float best = -1e10f;
+            int best_id = -1;
+            size_t best_at = 0;
+            for (size_t i = 0; i + 1 < out.size(); i++) {
+                auto it = index_.find(pieces_[out[i]] + pieces_[out[i + 1]]);
+                if (it != index_.end() && scores_[it->second] > best) { best = scores_[it->second]; best_id = it->second; best_at = i; }
+            }
+            if (best_id < 0) break;
+            out[best_at] = best_id;
+            out.erase(out.begin() + best_at + 1);
+        }
+        return out;
+    }
+
+    // Printable text of `token` following `prev`; empty for unprintable single bytes.
+    std::string decode(int prev, int token) const {
+        if (token < 0 || token >= (int)pieces_.size()) return "";
+        std::string p = pieces_[token];
+        if (prev == kBos && !p.empty() && p[0] == ' ') p.erase(0, 1);
+        unsigned byte = 0;
+        if (p.size() == 6 && sscanf(p.c_str(), "<0x%02X>", &byte) == 1) p = std::string(1, (char)byte);
+        if (p.size() == 1) {
+            unsigned char c = (unsigned char)p[0];
+            if (!(isprint(c) || isspace(c))) return "";
+        }
+        return p;
+    }
+
+private:
+    std::vector<std::string> pieces_;
+    std::vector<float> scores_;
+    std::unordered_map<std::string, int> index_;
+};
+
+[[noreturn]] void error_usage(const char* argv0) {
+    fprintf(stderr, "Usage:   %s <checkpoint> [options]\n", argv0);
+    fprintf(stderr, "Example: %s model.bin -n 256 -i \"Write a poem on GPUs\"\n", argv0);
+    fprintf(stderr, "Options:\n");
+    fprintf(stderr, "  -n <int>    max number of steps to run for, default = max_seq_len\n");
+    fprintf(stderr, "  -i <string> input prompt\n");
+    fprintf(stderr, "  -f <string> path to file containing input prompt. Can be used with for multi-line prompts.\n");
+    fprintf(stderr, "  -t <float>  temperature in [0,inf], default 0.5 (this build decodes greedily: only 0 is honoured)\n");
+    fprintf(stderr, "  -p <float>  p value in top-p (nucleus) sampling in [0,1] default 0.9\n");
+    fprintf(stderr, "  -s <int>    random seed, default time(NULL)\n");
+    fprintf(stderr, "  -z <string> optional path to custom tokenizer\n");
+    fprintf(stderr, "  -y <string> (optional) system prompt in chat mode\n");
+    fprintf(stderr, "  -q <string> dataset file for computing perplexity\n");
+    fprintf(stderr, "  -x <string> tensor parallel mode: none|column|hybrid, default none\n");
+    fprintf(stderr, "  -k <string> path to a file of prompt token ids (replaces -i/-f)\n");
+    fprintf(stderr, "  -g <int>    forward path: 0 per-op launches, 1 CUDA graph (default)\n");
+    exit(EXIT_FAILURE);
+}
+
+int get_and_print_gpu_info() {
+    int device_count = 0;
+    cudaGetDeviceCount(&device_count);
+    if (device_count == 0) {
+        printf("No CUDA devices found!\n");
+        exit(EXIT_FAILURE);
+    }
+    printf("Found %d CUDA devices\n", device_count);
+    for (int dev = 0; dev < device_count; dev++) {
+        cudaDeviceProp prop;
+        cudaGetDeviceProperties(&prop, dev);
+        printf("Device %d: %s\n", dev, prop.name);
+        printf("  Compute capability: %d.%d\n", prop.major, prop.minor);
+        printf("  Total global memory: %.2f GB\n", (float)prop.totalGlobalMem / (1024.0f * 1024.0f * 1024.0f));
+        printf("  Multiprocessors: %d\n", prop.multiProcessorCount);
+        printf("\n");
+    }
+    return device_count;
+}
+
+void die(int status, const char* what) {
+    if (status == Q4_ERR_UNSUPPORTED_SIZE) printf("\nUnsupported matmul size. Exiting\n");
+    else fprintf(stderr, "%s: %s\n", what, q4_status_string(status));
+    exit(EXIT_FAILURE);
+}
+
+struct Shared {
+    q4_comm_id* id = nullptr;
+    std::vector<q4_model*> models;
+    std::vector<q4_comm*> comms;
+};
+
+void load_thread(Shared* sh, const char* path, int rank, int gpu_count, int tp_mode) {
+    cudaSetDevice(rank);
+    q4_comm* comm = nullptr;
+    if (gpu_count > 1) {
+        int e = q4_comm_init_rank(&comm, gpu_count, sh->id, rank);
+        if (e) die(e, "communicator");
+    }
+    sh->comms[rank] = comm;
+    int e = q4_model_load(&sh->models[rank], path, rank, gpu_count, tp_mode, comm);
+    if (e) die(e, "build_transformer");
+}
+
+// The token loop of generate_thread (llama2_q4.cu:683-757) with rank 0 streaming the text.
+void generate_thread(Shared* sh, const Vocab* vocab, const std::vector<int>* prompt, int steps, int rank, int fwd_path) {
+    cudaSetDevice(rank);
+    q4_model* m = sh->models[rank];
+    q4_config cfg;
+    q4_model_config(m, &cfg);
+    cudaStream_t stream;
+    cudaStreamCreate(&stream);
+    q4_shared_data* mb = q4_model_shared(m);
+    int e = q4_model_reset(m, prompt->data(), (int)prompt->size(), 0);
+    if (e) die(e, "reset");
+    int token = (*prompt)[0], next = 0, pos = 0;
+    const auto start = std::chrono::steady_clock::now();
+    while (pos < steps) {
+        cudaStreamSynchronize(stream);
+        e = q4_model_forward(m, stream, pos >= (int)prompt->size() - 1, fwd_path);
+        if (e) die(e, "run_transformer");
+        if (pos > 0) {
+            next = mb->tokens[pos];
+            if (next >= cfg.vocab_size || next < 0) next = 0;
+            if (rank == 0 && vocab->loaded()) {
+                fputs(vocab->decode(token, next).c_str(), stdout);
+                fflush(stdout);
+            }
+            if (next == kEos) break;
+            token = next;
+        }
+        pos++;
+    }
+    cudaStreamSynchronize(stream);
+    const double secs = std::chrono::duration<double>(std::chrono::steady_clock::now() - start).count();
+    const int timed_tokens = pos - 1;
+    printf("\n");
+    printf("\n[GPU: %d] achieved tok/s: %f. Tokens: %d, seconds: %g\n", rank, timed_tokens / secs, timed_tokens, secs);
+    cudaStreamDestroy(stream);
+}
+
+}  // namespace
+
+int main(int argc, char* argv[]) {
+    int gpu_count = get_and_print_gpu_info();
+
+    const char* checkpoint_path = nullptr;
+    const char* tokenizer_path = "tokenizer.bin";
+    const char* dataset_path = nullptr;
+    const char* token_file = nullptr;
+    int steps = 0, fwd_path = 1;
+    std::string prompt;
+    bool have_prompt = false;
+    float temperature = 0.5f, topp = 0.6f;  // the reference's defaults in code (llama2_q4.cu:852-853)
+    unsigned long long rng_seed = 0;
+    int tp_mode = Q4_TP_NONE;
+
+    if (argc >= 2) checkpoint_path = argv[1];
+    else error_usage(argv[0]);
+    for (int i = 2; i < argc; i += 2) {
+        if (i + 1 >= argc || argv[i][0] != '-' || strlen(argv[i]) != 2) error_usage(argv[0]);
+        const char* v = argv[i + 1];
+        switch (argv[i][1]) {
+            case 'n': steps = atoi(v); break;
+            case 'i': prompt = v; have_prompt = true; break;
+            case 'z': tokenizer_path = v; break;
+            case 't': temperature = (float)atof(v); break;
+            case 'p': topp = (float)atof(v); break;
+            case 's': rng_seed = (unsigned long long)atoi(v); break;
+            case 'y': break;  // system prompt: parsed and unused, as in the reference
+            case 'q': dataset_path = v; break;
+            case 'k': token_file = v; break;
+            case 'g': fwd_path = atoi(v); break;
+            case 'x':
+                if (!strcmp(v, "none")) tp_mode = Q4_TP_NONE;
+                else if (!strcmp(v, "column")) tp_mode = Q4_TP_COLUMN;
+                else if (!strcmp(v, "hybrid")) tp_mode = Q4_TP_HYBRID;
+                else { printf("Unknown tp_mode: %s\n", v); exit(1); }
+                break;
+            case 'f': {
+                FILE* file = fopen(v, "r");
+                if (!file) { printf("Couldn't open file %s\n", v); exit(1); }
+                if (have_prompt) printf("Warning: -f overrides -i\n");
+                prompt.clear();
+                char buf[4096];
+                size_t n;
+                while ((n = fread(buf, 1, sizeof(buf), file)) > 0) prompt.append(buf, n);
+                fclose(file);
+                have_prompt = true;
+                break;
+            }
+            default: error_usage(argv[0]);
+        }
+    }
+    if (tp_mode == Q4_TP_NONE) gpu_count = 1;
+    if (gpu_count > Q4_MAX_GPUS) gpu_count = Q4_MAX_GPUS;
+    if (rng_seed == 0) rng_seed = (unsigned int)time(nullptr);
+    if (temperature < 0.0f) temperature = 0.0f;
+    if (topp < 0.0f || 1.0f < topp) topp = 0.9f;
+    if (dataset_path) printf("Warning: dataset path is ignored in non-perplexity mode\n");
+    if (temperature != 0.0f) printf("Note: temperature / top-p sampling is not part of this build; decoding greedily (-t 0)\n");
+    if (tp_mode == Q4_TP_COLUMN && gpu_count > 1) {
+        printf("Note: -x column (4 all-gathers per layer) is not part of this build; using -x hybrid\n");
+        tp_mode = Q4_TP_HYBRID;
+    }
+
+    // header first, for the model summary the reference prints (llama2_q4.cu:633-634)
+    q4_config cfg;
+    {
+        FILE* f = fopen(checkpoint_path, "rb");
+        if (!f) { printf("Couldn't open file %s\n", checkpoint_path); exit(1); }
+        if (fread(&cfg, sizeof(cfg), 1, f) != 1) { printf("Invalid header size\n"); exit(1); }
+        fclose(f);
+    }
+    printf("\nModel params:- \ndim: %d \nhidden_dim: %d\nn_heads: %d\nn_kv_heads: %d\nn_layers: %d\nseq_len: %d\nvocab_size: %d\nrope_theta: %g\n",
+           cfg.dim, cfg.hidden_dim, cfg.n_heads, cfg.n_kv_heads, cfg.n_layers, cfg.seq_len, cfg.vocab_size, cfg.rope_theta);
+
+    Shared sh;
+    sh.models.assign(gpu_count, nullptr);
+    sh.comms.assign(gpu_count, nullptr);
+    if (gpu_count > 1) {
+        int e = q4_comm_id_create(&sh.id, gpu_count);
+        if (e) die(e, "communicator id");
+    }
+    {
+        std::vector<std::thread> th;
+        for (int r = 0; r < gpu_count; r++) th.emplace_back(load_thread, &sh, checkpoint_path, r, gpu_count, tp_mode);
+        for (auto& t : th) t.join();
+    }
+    if (steps <= 0 || steps > cfg.seq_len) steps = cfg.seq_len;
+
+    Vocab vocab;
+    std::vector<int> prompt_tokens;
+    if (token_file) {
+        FILE* f = fopen(token_file, "r");
+        if (!f) { printf("Couldn't open file %s\n", token_file); exit(1); }
+        int id;
+        while (fscanf(f, "%d", &id) == 1) prompt_tokens.push_back(id);
+        fclose(f);
+        vocab.load(tokenizer_path, cfg.vocab_size);  // optional: ids are printed only when a vocabulary is there
+    } else {
+        if (!vocab.load(tokenizer_path, cfg.vocab_size)) { fprintf(stderr, "couldn't load %s\n", tokenizer_path); exit(EXIT_FAILURE); }
+        printf("\nEncoding Prompt... ");
+        prompt_tokens = vocab.encode(prompt, true);
+        printf("Done!\n");
+    }
+    if (prompt_tokens.empty()) {
+        fprintf(stderr, "something is wrong, expected at least 1 prompt token\n");
+        exit(EXIT_FAILURE);
+    }
+    for (int id : prompt_tokens)
+        if (id < 0 || id >= cfg.vocab_size) { fprintf(stderr, "prompt token id %d outside the vocabulary\n", id); exit(EXIT_FAILURE); }
+
+    {
+        std::vector<std::thread> th;
+        for (int r = 0; r < gpu_count; r++) th.emplace_back(generate_thread, &sh, &vocab, &prompt_tokens, steps, r, fwd_path);
+        for (auto& t : th) t.join();
+    }
+    for (int r = 0; r < gpu_count; r++) {
+        cudaSetDevice(r);
+        q4_model_free(sh.models[r]);
+        if (sh.comms[r]) q4_comm_destroy(sh.comms[r]);
+    }
+    if (sh.id) q4_comm_id_destroy(sh.id);
+    return 0;
+}

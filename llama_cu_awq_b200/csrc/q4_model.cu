@@ -359,6 +359,14 @@ extern "C" q4_shared_data* q4_model_shared(q4_model* m) { return m ? m->shared :
 extern "C" const uint16_t* q4_model_logits(const q4_model* m) { return m ? m->logits : nullptr; }
 extern "C" const uint16_t* q4_model_x(const q4_model* m) { return m ? m->x : nullptr; }
 
+extern "C" int q4_model_read(const q4_model* m, int what, uint16_t* host_out) {
+    if (!m || !host_out || what < 0 || what > 1) return Q4_ERR_INVALID;
+    Q4_CUDA_TRY(cudaDeviceSynchronize());
+    if (what == 0) Q4_CUDA_TRY(cudaMemcpy(host_out, m->logits, 2 * (size_t)m->cfg.vocab_size, cudaMemcpyDeviceToHost));
+    else Q4_CUDA_TRY(cudaMemcpy(host_out, m->x, 2 * (size_t)m->cfg.dim, cudaMemcpyDeviceToHost));
+    return Q4_OK;
+}
+
 extern "C" int q4_model_reset(q4_model* m, const int* prompt_tokens, int n, int pos) {
     if (!m || n < 0 || n > Q4_MAX_SEQ_LEN || pos < 0 || pos >= m->cfg.seq_len) return Q4_ERR_INVALID;
     Q4_CUDA_TRY(cudaDeviceSynchronize());
@@ -469,4 +477,29 @@ extern "C" double q4_model_token_bytes(const q4_model* m, int pos) {
     b += 2.0 * c.n_layers * m->kv_n * 2 * (pos + 1);  // K and V rows read
     b += 2.0 * c.n_layers * m->kv_n * 2;            // K and V row written
     return b;
+}
+
+extern "C" int q4_model_time_ffn(q4_model* m, void* stream, int reps, double* total_ms, double* bytes_per_launch) {
+    if (!m || reps < 1 || !total_ms || !bytes_per_launch) return Q4_ERR_INVALID;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int dim = m->cfg.dim;
+    cudaEvent_t e0, e1;
+    Q4_CUDA_TRY(cudaEventCreate(&e0));
+    Q4_CUDA_TRY(cudaEventCreate(&e1));
+    int e = Q4_OK;
+    for (int l = 0; l < m->cfg.n_layers && e == Q4_OK; l++)  // warm-up pass
+        e = q4_ffn_matvec_silu(s, m->hb + m->h_kb, m->xb, &m->layers[l].gate.w, &m->layers[l].up.w, dim, m->h_kc);
+    Q4_CUDA_TRY(cudaEventRecord(e0, s));
+    for (int r = 0; r < reps && e == Q4_OK; r++)
+        for (int l = 0; l < m->cfg.n_layers && e == Q4_OK; l++)
+            e = q4_ffn_matvec_silu(s, m->hb + m->h_kb, m->xb, &m->layers[l].gate.w, &m->layers[l].up.w, dim, m->h_kc);
+    Q4_CUDA_TRY(cudaEventRecord(e1, s));
+    Q4_CUDA_TRY(cudaEventSynchronize(e1));
+    float ms = 0.f;
+    Q4_CUDA_TRY(cudaEventElapsedTime(&ms, e0, e1));
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    *total_ms = ms;
+    *bytes_per_launch = 2.0 * (double)qw_bytes(dim, m->h_kc) + 2.0 * dim + 2.0 * m->h_kc;
+    return e;
 }

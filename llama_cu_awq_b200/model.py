@@ -1,0 +1,71 @@
+"""Model-level host mirror: build_transformer / run_transformer / generate_thread of the reference
+(llama2_q4.cu:625-659, 541-601, 683-757) over the C ABI."""
+import ctypes as C
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import check
+
+
+class Transformer:
+    def __init__(self, checkpoint_path, rank=0, gpu_count=1, tp_mode=_lib.Q4_TP_NONE, comm=None):
+        self._L = _lib.lib()
+        self.h = C.c_void_p()
+        check(self._L.q4_model_load(C.byref(self.h), checkpoint_path.encode(), rank, gpu_count, tp_mode, comm), "build_transformer")
+        self.config = _lib.q4_config()
+        check(self._L.q4_model_config(self.h, C.byref(self.config)), "config")
+        self.stream = torch.cuda.Stream()
+
+    def reset(self, prompt_tokens, pos=0):
+        arr = np.ascontiguousarray(prompt_tokens, dtype=np.int32)
+        check(self._L.q4_model_reset(self.h, arr.ctypes.data_as(C.POINTER(C.c_int)), arr.size, pos), "reset")
+
+    def forward(self, gen_token=True, path=1):
+        check(self._L.q4_model_forward(self.h, C.c_void_p(self.stream.cuda_stream), int(bool(gen_token)), path), "run_transformer")
+
+    def best_path(self):
+        """The fastest forward path this build offers (1 = CUDA-graph replay of the per-op kernels)."""
+        return 1
+
+    def synchronize(self):
+        self.stream.synchronize()
+
+    def _read(self, what, n):
+        out = np.empty(n, np.float16)
+        check(self._L.q4_model_read(self.h, what, out.ctypes.data_as(C.c_void_p)), "read")
+        return out
+
+    def logits(self):
+        return self._read(0, self.config.vocab_size)
+
+    def x(self):
+        return self._read(1, self.config.dim)
+
+    def shared(self):
+        return self._L.q4_model_shared(self.h).contents
+
+    def generate(self, prompt_tokens, steps, path=1):
+        arr = np.ascontiguousarray(prompt_tokens, dtype=np.int32)
+        if steps <= 0 or steps > self.config.seq_len:
+            steps = self.config.seq_len
+        out = np.zeros(steps + 1, np.int32)
+        timed, secs = C.c_int(), C.c_double()
+        check(self._L.q4_generate(self.h, arr.ctypes.data_as(C.POINTER(C.c_int)), arr.size, steps, path,
+                                  out.ctypes.data_as(C.POINTER(C.c_int)), C.byref(timed), C.byref(secs)), "generate")
+        return out, timed.value, secs.value
+
+    def token_bytes(self, pos):
+        return self._L.q4_model_token_bytes(self.h, pos)
+
+    def close(self):
+        if self.h:
+            self._L.q4_model_free(self.h)
+            self.h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
