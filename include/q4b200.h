@@ -179,8 +179,17 @@ int q4_model_read(const q4_model* model, int what, uint16_t* host_out);
 int q4_model_reset(q4_model* model, const int* prompt_tokens, int n, int pos);
 /* run_transformer(): one token at the current position on `stream`: embedding .. logits, then the greedy
  * hand-off (gen_token != 0 writes the sampled id to tokens[pos+1]); asynchronous. `path`: 0 = per-op kernels
- * launched one by one, 1 = the same launches replayed from a captured CUDA graph, 2 = fused schedule. */
+ * launched one by one, 1 = the same launches replayed from a captured CUDA graph, 2 = one persistent
+ * cooperative kernel per token that streams re-tiled weights through a shared-memory ring (head size 128,
+ * one GPU; returns Q4_ERR_UNSUPPORTED_SIZE otherwise). */
 int q4_model_forward(q4_model* model, void* stream, int gen_token, int path);
+/* Builds whatever `path` needs ahead of the first token (path 2: re-tiled weight copy and phase table; needs
+ * as much extra device memory as the quantized weights). Q4_ERR_UNSUPPORTED_SIZE when the path cannot serve
+ * this model; q4_model_forward calls it on demand. */
+int q4_model_prepare(q4_model* model, int path);
+/* Synchronises the device and returns Q4_OK, or the error a bounded device-side wait recorded
+ * (Q4_ERR_TIMEOUT) in the fused path or the communicator. */
+int q4_model_status(q4_model* model);
 /* generate_thread(): the token loop with the reference's timing window (llama2_q4.cu:708-745). Runs `steps`
  * positions starting from the n_prompt given ids, stops at EOS (id 2). out_tokens receives tokens[0..steps];
  * *timed_tokens = pos-1 and *seconds is the wall time of the loop. */
@@ -194,6 +203,12 @@ double q4_model_token_bytes(const q4_model* model, int pos);
  * (each layer's own weights, so the working set is far larger than L2) between two CUDA events on that stream.
  * Returns the total milliseconds and the algorithmic bytes one launch moves. */
 int q4_model_time_ffn(q4_model* model, void* stream, int reps, double* total_ms, double* bytes_per_launch);
+
+/* Profiling hook of the fused path: the first call arms per-phase device timestamps (globaltimer, ns) for the
+ * following launches; later calls copy the last launch's stamps to `out` ([2 CTAs][nphases][4]: phase start,
+ * inputs staged, weights consumed, grid barrier passed) and a type code per phase. Returns the phase count
+ * (>= 0) or a negative... status codes are positive, so: return value > 16 is a phase count. */
+int q4_model_trace(q4_model* model, unsigned long long* out, int* phase_types, int max_phases);
 
 /* Host-side shard helpers (no GPU needed): copy rank `rank`'s shard of a quantized matrix held in host
  * memory. Column split = contiguous slice of outputs (llama2_q4.cu:254-263). Row split = slice of inputs on

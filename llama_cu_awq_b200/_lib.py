@@ -81,9 +81,12 @@ SIGNATURES = {
     "q4_model_read": (_I, [_P, _I, _P]),
     "q4_model_reset": (_I, [_P, C.POINTER(C.c_int), _I, _I]),
     "q4_model_forward": (_I, [_P, _P, _I, _I]),
+    "q4_model_prepare": (_I, [_P, _I]),
+    "q4_model_status": (_I, [_P]),
     "q4_generate": (_I, [_P, C.POINTER(C.c_int), _I, _I, _I, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_double)]),
     "q4_model_token_bytes": (C.c_double, [_P, _I]),
     "q4_model_time_ffn": (_I, [_P, _P, _I, C.POINTER(C.c_double), C.POINTER(C.c_double)]),
+    "q4_model_trace": (_I, [_P, _P, _P, _I]),
     "q4_row_split_range": (None, [_I, _I, _I, C.POINTER(_I), C.POINTER(_I)]),
     "q4_shard_columns_host": (_I, [_QW, _I, _I, _I, _I, _P, _P, _P]),
     "q4_shard_rows_host": (_I, [_QW, _I, _I, _I, _I, _P, _P, _P]),

@@ -1,0 +1,1108 @@
+// Fused decode path: ONE persistent cooperative kernel per token (one CTA per SM) instead of ~9 launches per layer.
+// Replaces the launch sequence of run_llama_network (llama2_q4.cu:430-538) for a single GPU.
+//
+// Why: a 7B layer is 105 MB of weights = 16 us of HBM time; nine kernel boundaries per layer cost as much as the
+// streaming itself. Weight addresses never depend on activations, so each CTA has a PRODUCER warp that walks the
+// whole token's weight list and keeps a 16-slot shared-memory ring full with cp.async.bulk (TMA, 1-D, no
+// multicast), running ahead across op boundaries and grid barriers, while 8 CONSUMER warps do the math and wait at
+// the (bounded) grid barriers between dependent ops. HBM therefore stays busy through the barriers.
+//
+// Stream layout (built once per matrix on the device from the file layout, bytes per weight unchanged):
+//   unit  = 8 output columns x 1 group of 128 inputs = 512 B of nibbles + 32 B metadata (8 fp16 scales, 8 u8 zeros)
+//   block = (8-column tile rt, k-tile kt of <= 16 groups): [2 chunk pairs][8 rows][lane] uint4, then [group] metadata,
+//           so that one bulk copy fills a slot and every LDS.128 is conflict free (lane l = 2*group + half).
+//   blocks are stored [rt][kt]; a block is ng*544 bytes, ng = min(16, G - 16*kt).
+//
+// Arithmetic of the W4 dot product (consumer): activations are re-expressed per group of 128 as 15-bit block
+// fixed point X = rint(x / sx), sx = max|x| / 16256, split into two int8 digits (X = 128*xh + xl). Nibbles are
+// extracted four at a time with one AND (even nibbles) / one AND (odd nibbles, kept as 16*q) and multiplied with
+// DP4A into int32 accumulators: exact integer arithmetic, 6 instructions per 8 weights (the half2 FMA pipe of
+// this GPU issues at half rate, which made the half2 formulation pipe-bound at ~50 % of HBM bandwidth). Per
+// (column, group): y += scale * sx * (128*Sh + Sl - zero * sum(X)). The quantisation step of x is max|x|/32512 per
+// element, below fp16's own rounding of the largest elements; nibbles, zero points and scales are used exactly.
+//
+// Every wait is bounded (mbarrier polls and barrier spins count iterations); on expiry the kernel records
+// Q4_ERR_TIMEOUT in a status word, all later waits fall through, and the kernel returns.
+#include <cooperative_groups.h>
+#include <math_constants.h>
+#include <stdio.h>
+#include <stdlib.h>
+
+#include "q4_model.h"
+
+namespace {
+
+constexpr int kSlotGroups = 16;
+constexpr int kUnitBytes = 544;
+constexpr int kSlotBytes = kSlotGroups * kUnitBytes;  // 8704
+constexpr int kSlots = 16;
+constexpr int kCW = 8;                 // consumer warps
+constexpr int kCT = kCW * 32;          // consumer threads
+constexpr int kThreads = 32 + kCT;     // + producer warp
+constexpr int kClsChunk = 4096;        // halfs of one classifier row per slot (8192 B)
+constexpr unsigned kPollLimit = 1u << 26;                        // polls, and
+constexpr unsigned long long kWaitLimitNs = 2000ULL * 1000 * 1000;  // two seconds on the global timer, whichever comes first
+constexpr unsigned kSpinLimit = 1u << 23;
+
+enum PhaseType { PH_EMBED = 0, PH_GEMV = 1, PH_ATTN = 2, PH_CLS = 3, PH_ARGMAX = 4 };
+enum EpiKind { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SILU = 2 };
+
+struct FMat {
+    const uint8_t* blocks;  // stream layout
+    __half* out;
+    int n;                  // outputs of this matrix
+    int tile0;              // first tile of this matrix in the phase's tile space
+    int kv;                 // 1: out += loff + pos * n
+};
+
+struct FPhase {
+    int type;
+    int K, G, nkt;          // GEMV: inputs, groups, k-tiles; CLS: K = dim, nkt = chunks per row
+    const __half* xin;      // activations (global fp16)
+    const __half* norm_w;   // RMSNorm weight applied while staging x, or null
+    int nmat;
+    FMat m[3];
+    int nunits, tpu;        // work units of the phase and tiles per unit (2 for gate/up pairs)
+    int epi;
+    long long loff;         // KV cache layer offset (halfs)
+    // attention
+    int layer;
+};
+
+struct FParams {
+    const FPhase* phases;
+    int nphases;
+    q4_config cfg;
+    int head_size, kv_n, kv_mul, n_heads, nsplit;
+    float gpu_count;
+    // state
+    __half *x, *xb, *hb, *q, *knew, *logits, *kc, *vc;
+    const __half *emb, *wcls;
+    const float* rope;       // [seq_len][head_size/2] (cos, sin)
+    float* attn_part;        // [heads*nsplit][head_size + 2]
+    unsigned* attn_cnt;      // [heads]
+    float* cand_val;         // [grid]
+    int* cand_idx;           // [grid]
+    int* pos_dev;
+    int* tokens_pinned;
+    volatile int* pos_pinned;
+    unsigned long long* bar_counter;
+    unsigned long long bar_base;  // barriers completed by earlier launches
+    int* status;
+    int write_token;
+    int debug;                   // measurement only: bit 0 = consumers skip the GEMV math (pure streaming)
+    unsigned long long* trace;   // optional: [2 CTAs][nphases][4] device timestamps (ns), or null
+    // shared memory carve-up (bytes)
+    int xq_bytes, meta_off, part_off, part_floats;
+};
+
+// ------------------------------------------------------------------------------------------------------------
+// device helpers
+// ------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* b, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(b)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* b, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(b)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* b) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(b)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t* b, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0,1,0,p; }"
+                 : "=r"(ok) : "r"(smem_u32(b)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait. Returns false (and records the error) when the limit is hit or an error is already recorded.
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, int* status) {
+    unsigned long long t0 = 0;
+    for (unsigned i = 0; i < kPollLimit; i++) {
+        if (mbar_try(b, parity)) return true;
+        if ((i & 63u) == 63u) {
+            if (*(volatile int*)status != 0) return false;
+            const unsigned long long now = global_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitLimitNs) break;
+        }
+    }
+    atomicExch(status, Q4_ERR_TIMEOUT);
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kCT) : "memory"); }
+__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+__device__ __forceinline__ float fma_mixed(__half a, __half b, float c) {
+    float d;
+    asm("fma.rn.f32.f16 %0, %1, %2, %3;" : "=f"(d) : "h"(__half_as_ushort(a)), "h"(__half_as_ushort(b)), "f"(c));
+    return d;
+}
+
+// Grid-wide barrier among the consumer threads of all CTAs (the producer warps never wait here).
+__device__ __forceinline__ void grid_barrier(const FParams& p, unsigned& nbar, int ctid) {
+    consumer_sync();  // orders every consumer thread's stores before thread 0's release below (cumulativity)
+    if (ctid == 0) {
+        nbar++;
+        const unsigned long long target = (p.bar_base + nbar) * (unsigned long long)gridDim.x;
+        unsigned long long v;
+        asm volatile("atom.add.release.gpu.global.u64 %0, [%1], 1;" : "=l"(v) : "l"(p.bar_counter) : "memory");
+        unsigned spins = 0;
+        for (;;) {
+            asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p.bar_counter) : "memory");
+            if (v >= target) break;
+            if ((++spins & 255u) == 0) {
+                if (*(volatile int*)p.status != 0) break;
+                if (spins > kSpinLimit) { atomicExch(p.status, Q4_ERR_TIMEOUT); break; }
+            }
+        }
+    }
+    consumer_sync();
+}
+
+// Timestamps of CTA 0 and of the last CTA: [which][phase][0 start, 1 inputs staged, 2 slots done, 3 after the barrier]
+#define TRACE(k)                                                                                             \
+    do {                                                                                                     \
+        if (p.trace && ctid == 0 && (cta == 0 || cta == grid - 1))                                           \
+            p.trace[((size_t)(cta == 0 ? 0 : 1) * p.nphases + pi) * 4 + (k)] = global_ns();                  \
+    } while (0)
+
+__device__ __forceinline__ float silu_mul(float g, float u) {
+    float val = g;
+    val *= 1.0f / (1.0f + expf(-val));
+    val *= u;
+    return val;
+}
+
+__device__ __forceinline__ float transpose_reduce8(const float acc[8], int lane) {
+    float a4[4], a2[2], a1;
+    const bool up16 = lane & 16, up8 = lane & 8, up4 = lane & 4;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        float keep = up16 ? acc[i + 4] : acc[i];
+        float send = up16 ? acc[i] : acc[i + 4];
+        a4[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+        float keep = up8 ? a4[i + 2] : a4[i];
+        float send = up8 ? a4[i] : a4[i + 2];
+        a2[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+    }
+    {
+        float keep = up4 ? a2[1] : a2[0];
+        float send = up4 ? a2[0] : a2[1];
+        a1 = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+    }
+    a1 += __shfl_xor_sync(0xffffffffu, a1, 2);
+    a1 += __shfl_xor_sync(0xffffffffu, a1, 1);
+    return a1;
+}
+
+// Sum over the consumer threads; every consumer thread gets the total. red: 8 floats of shared memory.
+__device__ __forceinline__ float consumer_sum(float v, float* red, int ctid) {
+    v = warp_sum(v);
+    if ((ctid & 31) == 0) red[ctid >> 5] = v;
+    consumer_sync();
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < kCW; i++) t += red[i];
+    consumer_sync();
+    return t;
+}
+
+// Tile t of a GEMV phase -> (matrix, 8-column tile inside the matrix).
+__device__ __forceinline__ void tile_info(const FPhase& ph, int t, int& mi, int& rt) {
+    if (ph.epi == EPI_SILU) { mi = t & 1; rt = t >> 1; return; }
+    mi = 0;
+    if (ph.nmat > 1 && t >= ph.m[1].tile0) mi = 1;
+    if (ph.nmat > 2 && t >= ph.m[2].tile0) mi = 2;
+    rt = t - ph.m[mi].tile0;
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// Staging of the activation vector into shared memory (all consumer threads).
+// GEMV: optional RMSNorm (same arithmetic as gpu_kernels.h:72-105, result rounded to fp16), then block fixed point.
+// xq uint4 index = ((kt*2 + j2)*4 + wi)*32 + lane, lane = 2*(group%16) + half; .x/.y = high digit for even/odd
+// nibbles, .z/.w = low digit. xs_scale[kt*32 + lane] = sx of the group, xs_sum[kt*32 + lane] = sum X over the
+// lane's 64 inputs.
+// ------------------------------------------------------------------------------------------------------------
+__device__ void stage_x_quant(const FPhase& ph, uint4* xq, float* xs_scale, int* xs_sum, float* red, int ctid) {
+    constexpr int kBatch = 8;  // words per thread whose loads are in flight together (one L2 round trip per batch)
+    const int K = ph.K, nwords = ph.G * 16;
+    const int iters = (nwords + kCT - 1) / kCT;
+    float inv_rms = 1.f;
+    for (int it0 = 0; it0 < iters; it0 += kBatch) {
+        uint4 xv[kBatch], wv[kBatch];
+#pragma unroll
+        for (int b = 0; b < kBatch; b++) {
+            const int wd = ctid + (it0 + b) * kCT;
+            xv[b] = make_uint4(0, 0, 0, 0);
+            wv[b] = make_uint4(0, 0, 0, 0);
+            if (it0 + b < iters && wd < nwords && wd * 8 < K) {
+                xv[b] = __ldcg(reinterpret_cast<const uint4*>(ph.xin + wd * 8));
+                if (ph.norm_w) wv[b] = *reinterpret_cast<const uint4*>(ph.norm_w + wd * 8);
+            }
+        }
+        if (ph.norm_w && it0 == 0) {
+            // RMSNorm inputs have K = dim <= kBatch * kCT * 8, so the whole vector is in registers now (host-checked)
+            float ss = 0.f;
+#pragma unroll
+            for (int b = 0; b < kBatch; b++) {
+                const __half2* h = reinterpret_cast<const __half2*>(&xv[b]);
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const float2 f = __half22float2(h[j]);
+                    ss = fmaf(f.x, f.x, ss);
+                    ss = fmaf(f.y, f.y, ss);
+                }
+            }
+            ss = consumer_sum(ss, red, ctid);
+            ss /= K;
+            ss += 1e-5f;
+            inv_rms = 1.0f / sqrtf(ss);
+        }
+#pragma unroll
+        for (int b = 0; b < kBatch; b++) {
+            if (it0 + b < iters) {  // uniform over the block: the shuffles below see all lanes
+                const int wd = ctid + (it0 + b) * kCT;
+                float v[8];
+                const __half* xh = reinterpret_cast<const __half*>(&xv[b]);
+                if (ph.norm_w) {
+                    const __half* wh = reinterpret_cast<const __half*>(&wv[b]);
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        float val = __half2float(xh[j]);
+                        val *= inv_rms * __half2float(wh[j]);
+                        v[j] = __half2float(__float2half(val));
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; j++) v[j] = __half2float(xh[j]);
+                }
+                float amax = 0.f;
+#pragma unroll
+                for (int j = 0; j < 8; j++) amax = fmaxf(amax, fabsf(v[j]));
+#pragma unroll
+                for (int o = 1; o < 16; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));  // 16 words = 1 group
+                const float sx = amax * (1.0f / 16256.0f);
+                const float inv = amax > 0.f ? 16256.0f / amax : 0.f;
+                uint32_t he = 0, ho = 0, le = 0, lo = 0;
+                int sum = 0;
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const int X = __float2int_rn(v[j] * inv);
+                    sum += X;
+                    const int hi = (X + 64) >> 7;
+                    const int low = X - (hi << 7);
+                    const uint32_t hb = (uint32_t)hi & 0xFFu, lb = (uint32_t)low & 0xFFu;
+                    if (j & 1) { ho |= hb << (8 * (j >> 1)); lo |= lb << (8 * (j >> 1)); }
+                    else       { he |= hb << (8 * (j >> 1)); le |= lb << (8 * (j >> 1)); }
+                }
+                sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 4);  // 8 words = the 64 inputs of one (group, half)
+                if (wd < nwords) {
+                    const int g = wd >> 4, c = (wd >> 2) & 3, wi = wd & 3;
+                    const int kt = g >> 4, lane = 2 * (g & 15) + (c >> 1), j2 = c & 1;
+                    xq[((kt * 2 + j2) * 4 + wi) * 32 + lane] = make_uint4(he, ho, le, lo);
+                    if ((wd & 7) == 0) { xs_scale[kt * 32 + lane] = sx; xs_sum[kt * 32 + lane] = sum; }
+                }
+            }
+        }
+    }
+    consumer_sync();
+}
+
+// Classifier input: final RMSNorm, fp16, plain layout.
+__device__ void stage_x_f16(const FPhase& ph, __half* xf, float* red, int ctid) {
+    const int K = ph.K;
+    float ss = 0.f;
+    for (int i = ctid; i < K; i += kCT) { const float f = __half2float(__ldcg(ph.xin + i)); ss = fmaf(f, f, ss); }
+    ss = consumer_sum(ss, red, ctid);
+    ss /= K;
+    ss += 1e-5f;
+    const float inv_rms = 1.0f / sqrtf(ss);
+    for (int i = ctid; i < K; i += kCT) {
+        float val = __half2float(__ldcg(ph.xin + i));
+        val *= inv_rms * __half2float(ph.norm_w[i]);
+        xf[i] = __float2half(val);
+    }
+    consumer_sync();
+}
+
+// One slot of a GEMV phase: 8 columns x ng groups. Returns via `part` (8 floats per slot in shared memory).
+__device__ __forceinline__ void gemv_slot(const uint8_t* slot, int ng, int kt, const uint4* xq, const float* xs_scale, const int* xs_sum,
+                                          float* part, int lane) {
+    const int nl = 2 * ng;
+    const bool active = lane < nl;
+    float facc[8];
+#pragma unroll
+    for (int r = 0; r < 8; r++) facc[r] = 0.f;
+    if (active) {
+        int ah[8], ah16[8], al[8], al16[8];
+#pragma unroll
+        for (int r = 0; r < 8; r++) { ah[r] = 0; ah16[r] = 0; al[r] = 0; al16[r] = 0; }
+        const uint4* wb = reinterpret_cast<const uint4*>(slot) + lane;
+        const uint4* xb = xq + (kt * 2) * 4 * 32 + lane;
+#pragma unroll
+        for (int j2 = 0; j2 < 2; j2++) {
+            uint4 xv[4];
+#pragma unroll
+            for (int wi = 0; wi < 4; wi++) xv[wi] = xb[(j2 * 4 + wi) * 32];
+#pragma unroll
+            for (int r = 0; r < 8; r++) {
+                const uint4 w = wb[(j2 * 8 + r) * nl];
+                const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                for (int wi = 0; wi < 4; wi++) {
+                    const uint32_t e = ww[wi] & 0x0F0F0F0Fu, o = ww[wi] & 0xF0F0F0F0u;
+                    ah[r] = dp4a_us(e, xv[wi].x, ah[r]);
+                    ah16[r] = dp4a_us(o, xv[wi].y, ah16[r]);
+                    al[r] = dp4a_us(e, xv[wi].z, al[r]);
+                    al16[r] = dp4a_us(o, xv[wi].w, al16[r]);
+                }
+            }
+        }
+        const uint8_t* meta = slot + ng * 512 + (lane >> 1) * 32;
+        const uint4 sc = *reinterpret_cast<const uint4*>(meta);
+        const uint2 zz = *reinterpret_cast<const uint2*>(meta + 16);
+        const __half* sh = reinterpret_cast<const __half*>(&sc);
+        const float sx = xs_scale[kt * 32 + lane];
+        const int sumx = xs_sum[kt * 32 + lane];
+#pragma unroll
+        for (int r = 0; r < 8; r++) {
+            const int z = (int)(((r < 4 ? zz.x : zz.y) >> (8 * (r & 3))) & 0xFFu);
+            const int ri = ((ah[r] + (ah16[r] >> 4)) << 7) + al[r] + (al16[r] >> 4) - z * sumx;
+            facc[r] = (float)ri * (__half2float(sh[r]) * sx);
+        }
+    }
+    const float tot = transpose_reduce8(facc, lane);
+    if ((lane & 3) == 0) part[lane >> 2] = tot;
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// The kernel
+// ------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ uint64_t full_bar[kSlots], empty_bar[kSlots];
+    __shared__ float red[kCW];
+    __shared__ int s_flag, s_abort;
+
+    uint8_t* ring = smem;
+    uint4* xq = reinterpret_cast<uint4*>(smem + kSlots * kSlotBytes);
+    float* xs_scale = reinterpret_cast<float*>(smem + p.meta_off);
+    int* xs_sum = reinterpret_cast<int*>(smem + p.meta_off) + 32 * 16;   // up to 16 k-tiles... sized by host
+    float* part = reinterpret_cast<float*>(smem + p.part_off);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int cta = blockIdx.x, grid = gridDim.x;
+
+    if (tid == 0) {
+        for (int s = 0; s < kSlots; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == 0) {
+        // ================= producer: stream every phase's weights of this CTA into the ring =================
+        if (lane != 0) return;
+        unsigned seq = 0;
+        for (int pi = 0; pi < p.nphases; pi++) {
+            const FPhase& ph = p.phases[pi];
+            if (ph.type == PH_GEMV) {
+                for (int u = cta; u < ph.nunits; u += grid) {
+                    for (int tt = 0; tt < ph.tpu; tt++) {
+                        int mi, rt;
+                        tile_info(ph, u * ph.tpu + tt, mi, rt);
+                        const uint8_t* base = ph.m[mi].blocks + (size_t)rt * ph.G * kUnitBytes;
+                        for (int kt = 0; kt < ph.nkt; kt++, seq++) {
+                            const int ng = min(kSlotGroups, ph.G - kt * kSlotGroups);
+                            const int slot = seq % kSlots;
+                            if (!mbar_wait(&empty_bar[slot], ((seq / kSlots) & 1) ^ 1, p.status)) return;
+                            mbar_expect_tx(&full_bar[slot], ng * kUnitBytes);
+                            bulk_g2s(ring + slot * kSlotBytes, base + (size_t)kt * kSlotGroups * kUnitBytes, ng * kUnitBytes, &full_bar[slot]);
+                        }
+                    }
+                }
+            } else if (ph.type == PH_CLS) {
+                for (int row = cta; row < ph.nunits; row += grid) {
+                    for (int kc = 0; kc < ph.nkt; kc++, seq++) {
+                        const int len = min(kClsChunk, ph.K - kc * kClsChunk);
+                        const int slot = seq % kSlots;
+                        if (!mbar_wait(&empty_bar[slot], ((seq / kSlots) & 1) ^ 1, p.status)) return;
+                        mbar_expect_tx(&full_bar[slot], len * 2);
+                        bulk_g2s(ring + slot * kSlotBytes, p.wcls + (size_t)row * ph.K + kc * kClsChunk, len * 2, &full_bar[slot]);
+                    }
+                }
+            }
+        }
+        return;
+    }
+
+    // ================= consumers =================
+    const int ctid = tid - 32, cw = warp - 1;
+    unsigned seq = 0, nbar = 0;
+    bool failed = false;  // a bounded wait ran out: skip the remaining slots, keep taking part in the barriers
+    const int pos = *p.pos_dev;
+    const int HS = p.head_size;
+
+    for (int pi = 0; pi < p.nphases; pi++) {
+        const FPhase& ph = p.phases[pi];
+        // all consumer threads leave together (named barriers count live threads), never one by one
+        if (ctid == 0) s_abort = *(volatile int*)p.status;
+        consumer_sync();
+        if (s_abort != 0) return;
+        TRACE(0);
+
+        if (ph.type == PH_EMBED) {
+            // copy_embedding_kernel (gpu_kernels.h:61-69): the token id comes from the pinned host mailbox
+            if (cta * kCT + ctid < p.cfg.dim / 8) {
+                const int token = p.tokens_pinned[pos];
+                const uint4* src = reinterpret_cast<const uint4*>(p.emb + (size_t)token * p.cfg.dim);
+                uint4* dst = reinterpret_cast<uint4*>(p.x);
+                for (int i = cta * kCT + ctid; i < p.cfg.dim / 8; i += grid * kCT) dst[i] = src[i];
+            }
+            grid_barrier(p, nbar, ctid);
+
+        } else if (ph.type == PH_GEMV) {
+            stage_x_quant(ph, xq, xs_scale, xs_sum, red, ctid);
+            TRACE(1);
+            // old value of the residual stream for this thread's first epilogue element: requested now, used after the slots
+            __half resid = __float2half(0.f);
+            if (ph.epi == EPI_RESIDUAL) {
+                const int u = cta + (ctid >> 3) * grid;
+                if (u < ph.nunits) resid = __ldcg(ph.m[0].out + u * 8 + (ctid & 7));
+            }
+            // slots of this CTA, in the producer's order; slot i belongs to consumer warp i % kCW
+            int lt = 0;
+            for (int u = cta; u < ph.nunits; u += grid) {
+                for (int tt = 0; tt < ph.tpu; tt++, lt++) {
+                    for (int kt = 0; kt < ph.nkt; kt++, seq++) {
+                        if ((int)(seq % kCW) != cw) continue;
+                        const int ng = min(kSlotGroups, ph.G - kt * kSlotGroups);
+                        const int slot = seq % kSlots;
+                        if (failed || !mbar_wait(&full_bar[slot], (seq / kSlots) & 1, p.status)) { failed = true; continue; }
+                        if (!(p.debug & 1)) gemv_slot(ring + slot * kSlotBytes, ng, kt, xq, xs_scale, xs_sum, part + (size_t)(lt * ph.nkt + kt) * 8, lane);
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&empty_bar[slot]);
+                    }
+                }
+            }
+            consumer_sync();
+            TRACE(2);
+            // epilogue: one thread per (local tile, column)
+            const int ntl = lt;
+            for (int e = ctid; e < ntl * 8; e += kCT) {
+                const int l2 = e >> 3, r = e & 7;
+                const int u = cta + (l2 / ph.tpu) * grid;
+                int mi, rt;
+                tile_info(ph, u * ph.tpu + (l2 % ph.tpu), mi, rt);
+                float sum = 0.f;
+                for (int kt = 0; kt < ph.nkt; kt++) sum += part[(size_t)(l2 * ph.nkt + kt) * 8 + r];
+                const int n = rt * 8 + r;
+                if (ph.epi == EPI_SILU) {
+                    if (mi == 0) {
+                        float up = 0.f;
+                        for (int kt = 0; kt < ph.nkt; kt++) up += part[(size_t)((l2 + 1) * ph.nkt + kt) * 8 + r];
+                        ph.m[0].out[n] = __float2half(silu_mul(sum, up));
+                    }
+                } else {
+                    const FMat& m = ph.m[mi];
+                    __half* out = m.out;
+                    if (m.kv) out += ph.loff + (long long)pos * m.n;
+                    if (ph.epi == EPI_RESIDUAL) sum += __half2float(e == ctid ? resid : __ldcg(out + n)) / p.gpu_count;
+                    out[n] = __float2half(sum);
+                }
+            }
+            grid_barrier(p, nbar, ctid);
+            TRACE(3);
+
+        } else if (ph.type == PH_ATTN) {
+            // ---- attention of one query per head over positions 0..pos, split over CTAs (llama2_q4.cu:410-427) ----
+            float* sm_m = reinterpret_cast<float*>(xq);          // [32]
+            float* sm_l = sm_m + 32;                             // [32]
+            float* sm_acc = sm_l + 32;                           // [32][128]
+            const int lane8 = ctid & 7, grp = ctid >> 3;
+            const int d0 = lane8 * 16;                           // this lane's 16 head dims; RoPE partner dims are d0 ^ 64
+            const bool upper = d0 >= 64;
+            const int i0 = upper ? d0 - 64 : d0;
+            const int T = pos + 1;
+            const float alpha = (float)(1.0 / sqrt((double)HS));
+            const int nitems = p.n_heads * p.nsplit;
+            const __half* kc = p.kc + ph.loff;
+            const __half* vc = p.vc + ph.loff;
+            // (cos, sin) of this position for dims i0..i0+15: RoPE of gpu_kernels.h:340-363, tabulated at load time
+            float2 cs[16];
+            {
+                const float4* tp = reinterpret_cast<const float4*>(p.rope + ((size_t)pos * (HS / 2) + i0) * 2);
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const float4 t4 = __ldg(tp + j);
+                    cs[2 * j] = make_float2(t4.x, t4.y);
+                    cs[2 * j + 1] = make_float2(t4.z, t4.w);
+                }
+            }
+            for (int id = cta; id < nitems; id += grid) {
+                const int h = id / p.nsplit, split = id % p.nsplit;
+                const int kvh = h / p.kv_mul;
+                const int units = (T + 31) / 32;
+                const int u0 = (int)((long long)units * split / p.nsplit), u1 = (int)((long long)units * (split + 1) / p.nsplit);
+                const int t0 = u0 * 32, t1 = min(u1 * 32, T);
+                const size_t col = (size_t)kvh * HS + d0;
+                // first step's K/V rows are requested before anything else so that their latency overlaps the query set-up
+                uint4 kn[2], vn[2];
+                auto fetch = [&](int tb) {
+                    int t = tb + grp;
+                    if (t >= t1) t = t0;
+                    if (tb < t1) {
+                        const uint4* vr = reinterpret_cast<const uint4*>(vc + (size_t)t * p.kv_n + col);
+                        vn[0] = __ldcg(vr); vn[1] = __ldcg(vr + 1);
+                        if (t != pos) {
+                            const uint4* kr = reinterpret_cast<const uint4*>(kc + (size_t)t * p.kv_n + col);
+                            kn[0] = __ldcg(kr); kn[1] = __ldcg(kr + 1);
+                        }
+                    }
+                };
+                fetch(t0);
+                // rotated query (fp16-rounded like the reference's in-place rotation)
+                float qf[16];
+                {
+                    const uint4* qlo = reinterpret_cast<const uint4*>(p.q + (size_t)h * HS + i0);
+                    const uint4* qhi = reinterpret_cast<const uint4*>(p.q + (size_t)h * HS + i0 + 64);
+                    const uint4 a0 = __ldcg(qlo), a1 = __ldcg(qlo + 1), b0 = __ldcg(qhi), b1 = __ldcg(qhi + 1);
+                    const uint4 lo4[2] = {a0, a1}, hi4[2] = {b0, b1};
+                    const __half* lo = reinterpret_cast<const __half*>(lo4);
+                    const __half* hi = reinterpret_cast<const __half*>(hi4);
+#pragma unroll
+                    for (int j = 0; j < 16; j++) {
+                        const float l0 = __half2float(lo[j]), h0 = __half2float(hi[j]);
+                        const float r = upper ? (l0 * cs[j].y + h0 * cs[j].x) : (l0 * cs[j].x - h0 * cs[j].y);
+                        qf[j] = __half2float(__float2half(r));
+                    }
+                }
+                float m = -CUDART_INF_F, l = 0.f, acc[16];
+#pragma unroll
+                for (int j = 0; j < 16; j++) acc[j] = 0.f;
+                for (int tb = t0; tb < t1; tb += 32) {
+                    const int t = tb + grp;
+                    const bool valid = t < t1;
+                    const int tt = valid ? t : t0;
+                    const uint4 kcur[2] = {kn[0], kn[1]}, vcur[2] = {vn[0], vn[1]};
+                    fetch(tb + 32);  // next step's rows in flight during this step's math
+                    float kf[16], vf[16];
+                    if (tt == pos) {
+                        // the new key is un-rotated in knew: rotate it here; the head group's first query head also files it
+                        const uint4* klo = reinterpret_cast<const uint4*>(p.knew + (size_t)kvh * HS + i0);
+                        const uint4* khi = reinterpret_cast<const uint4*>(p.knew + (size_t)kvh * HS + i0 + 64);
+                        const uint4 lo4[2] = {__ldcg(klo), __ldcg(klo + 1)}, hi4[2] = {__ldcg(khi), __ldcg(khi + 1)};
+                        const __half* lo = reinterpret_cast<const __half*>(lo4);
+                        const __half* hi = reinterpret_cast<const __half*>(hi4);
+                        uint4 store[2];
+                        __half* sh = reinterpret_cast<__half*>(store);
+#pragma unroll
+                        for (int j = 0; j < 16; j++) {
+                            const float l0 = __half2float(lo[j]), h0 = __half2float(hi[j]);
+                            const float r = upper ? (l0 * cs[j].y + h0 * cs[j].x) : (l0 * cs[j].x - h0 * cs[j].y);
+                            sh[j] = __float2half(r);
+                            kf[j] = __half2float(sh[j]);
+                        }
+                        if (valid && (h % p.kv_mul) == 0) {
+                            uint4* dst = reinterpret_cast<uint4*>(p.kc + ph.loff + (size_t)pos * p.kv_n + col);
+                            dst[0] = store[0];
+                            dst[1] = store[1];
+                        }
+                    } else {
+                        const __half2* hh = reinterpret_cast<const __half2*>(kcur);
+#pragma unroll
+                        for (int j = 0; j < 8; j++) { const float2 a = __half22float2(hh[j]); kf[2 * j] = a.x; kf[2 * j + 1] = a.y; }
+                    }
+                    {
+                        const __half2* hh = reinterpret_cast<const __half2*>(vcur);
+#pragma unroll
+                        for (int j = 0; j < 8; j++) { const float2 a = __half22float2(hh[j]); vf[2 * j] = a.x; vf[2 * j + 1] = a.y; }
+                    }
+                    float sc = 0.f;
+#pragma unroll
+                    for (int j = 0; j < 16; j++) sc = fmaf(kf[j], qf[j], sc);
+                    sc += __shfl_xor_sync(0xffffffffu, sc, 1);
+                    sc += __shfl_xor_sync(0xffffffffu, sc, 2);
+                    sc += __shfl_xor_sync(0xffffffffu, sc, 4);
+                    if (valid) {
+                        sc = __half2float(__float2half(sc * alpha));  // scores are fp16 in the reference (gpu_kernels.h:171-175)
+                        const float mn = fmaxf(m, sc);
+                        const float corr = expf(m - mn);
+                        const float pr = expf(sc - mn);
+                        l = l * corr + pr;
+#pragma unroll
+                        for (int j = 0; j < 16; j++) acc[j] = fmaf(pr, vf[j], acc[j] * corr);
+                        m = mn;
+                    }
+                }
+                // merge the 32 lane groups of this CTA
+                if (lane8 == 0) { sm_m[grp] = m; sm_l[grp] = l; }
+#pragma unroll
+                for (int j = 0; j < 16; j++) sm_acc[grp * 128 + d0 + j] = acc[j];
+                consumer_sync();
+                float* outp = p.attn_part + (size_t)id * (HS + 2);
+                if (ctid < HS) {
+                    float M = -CUDART_INF_F;
+                    for (int g2 = 0; g2 < 32; g2++) M = fmaxf(M, sm_m[g2]);
+                    float a = 0.f, L = 0.f;
+                    for (int g2 = 0; g2 < 32; g2++) {
+                        if (sm_m[g2] != -CUDART_INF_F) {
+                            const float w = expf(sm_m[g2] - M);
+                            a += sm_acc[g2 * 128 + ctid] * w;
+                            L += sm_l[g2] * w;
+                        }
+                    }
+                    outp[2 + ctid] = a;
+                    if (ctid == 0) { outp[0] = M; outp[1] = L; }
+                }
+                consumer_sync();  // the partial is complete before thread 0 publishes it (release below)
+                if (ctid == 0) {
+                    unsigned old;
+                    asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(old) : "l"(p.attn_cnt + h) : "memory");
+                    s_flag = (old == (unsigned)p.nsplit - 1);
+                    if (s_flag) p.attn_cnt[h] = 0;
+                }
+                consumer_sync();
+                if (s_flag) {
+                    // last split of this head to finish: merge all splits (fixed order -> deterministic)
+                    const float* base = p.attn_part + (size_t)h * p.nsplit * (HS + 2);
+                    if (ctid < HS) {
+                        float M2 = -CUDART_INF_F;
+                        for (int s2 = 0; s2 < p.nsplit; s2++) M2 = fmaxf(M2, __ldcg(base + (size_t)s2 * (HS + 2)));
+                        float a = 0.f, L = 0.f;
+                        for (int s2 = 0; s2 < p.nsplit; s2++) {
+                            const float ms = __ldcg(base + (size_t)s2 * (HS + 2));
+                            if (ms != -CUDART_INF_F) {
+                                const float w = expf(ms - M2);
+                                a += __ldcg(base + (size_t)s2 * (HS + 2) + 2 + ctid) * w;
+                                L += __ldcg(base + (size_t)s2 * (HS + 2) + 1) * w;
+                            }
+                        }
+                        p.xb[(size_t)h * HS + ctid] = __float2half(a / L);
+                    }
+                }
+                consumer_sync();
+            }
+            TRACE(2);
+            grid_barrier(p, nbar, ctid);
+            TRACE(3);
+
+        } else if (ph.type == PH_CLS) {
+            // ---- classifier: fp16 rows streamed through the same ring; per-CTA argmax candidate ----
+            __half* xf = reinterpret_cast<__half*>(xq);
+            stage_x_f16(ph, xf, red, ctid);
+            TRACE(1);
+            int lt = 0;
+            for (int row = cta; row < ph.nunits; row += grid, lt++) {
+                for (int kc = 0; kc < ph.nkt; kc++, seq++) {
+                    if ((int)(seq % kCW) != cw) continue;
+                    const int len = min(kClsChunk, ph.K - kc * kClsChunk);
+                    const int slot = seq % kSlots;
+                    if (failed || !mbar_wait(&full_bar[slot], (seq / kSlots) & 1, p.status)) { failed = true; continue; }
+                    const uint4* wv = reinterpret_cast<const uint4*>(ring + slot * kSlotBytes);
+                    const uint4* xv = reinterpret_cast<const uint4*>(xf + kc * kClsChunk);
+                    float a = 0.f;
+                    for (int i = lane; i * 8 < len; i += 32) {
+                        const uint4 w = wv[i], xx = xv[i];
+                        const __half* wh = reinterpret_cast<const __half*>(&w);
+                        const __half* xh = reinterpret_cast<const __half*>(&xx);
+#pragma unroll
+                        for (int j = 0; j < 8; j++) a = fma_mixed(wh[j], xh[j], a);
+                    }
+                    a = warp_sum(a);
+                    if (lane == 0) part[lt * ph.nkt + kc] = a;
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&empty_bar[slot]);
+                }
+            }
+            consumer_sync();
+            float best = -CUDART_INF_F;
+            int bi = 0x7fffffff;
+            for (int e = ctid; e < lt; e += kCT) {
+                float sum = 0.f;
+                for (int kc = 0; kc < ph.nkt; kc++) sum += part[e * ph.nkt + kc];
+                const int n = cta + e * grid;
+                const __half hv = __float2half(sum);
+                p.logits[n] = hv;
+                const float v = __half2float(hv);
+                if (v > best || (v == best && n < bi)) { best = v; bi = n; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+            }
+            float* cv = reinterpret_cast<float*>(part);  // reuse after the logits are out
+            consumer_sync();
+            if (lane == 0) { cv[cw] = best; reinterpret_cast<int*>(cv)[kCW + cw] = bi; }
+            consumer_sync();
+            if (ctid == 0) {
+                for (int w2 = 1; w2 < kCW; w2++) {
+                    const float ov = cv[w2];
+                    const int oi = reinterpret_cast<int*>(cv)[kCW + w2];
+                    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+                }
+                p.cand_val[cta] = best;
+                p.cand_idx[cta] = bi;
+            }
+            TRACE(2);
+            grid_barrier(p, nbar, ctid);
+            TRACE(3);
+
+        } else if (ph.type == PH_ARGMAX) {
+            // ---- greedy hand-off (gpu_kernels.h:456-501): lowest index among equal maxima ----
+            if (cta == 0 && cw == 0) {
+                float best = -CUDART_INF_F;
+                int bi = 0x7fffffff;
+                for (int c = lane; c < grid; c += 32) {
+                    const float ov = __ldcg(p.cand_val + c);
+                    const int oi = __ldcg(p.cand_idx + c);
+                    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+                    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+                }
+                if (lane == 0) {
+                    int token_pos = *p.pos_pinned;
+                    token_pos++;
+                    if (p.write_token) p.tokens_pinned[token_pos] = (bi == 0x7fffffff) ? 0 : bi;
+                    *p.pos_pinned = token_pos;
+                    *p.pos_dev = token_pos;
+                }
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// Stream-layout builder (device): one block of 40 threads per (tile, group) unit.
+// ------------------------------------------------------------------------------------------------------------
+__global__ void repack_kernel(uint8_t* dst, const uint32_t* w, const uint32_t* z, const __half* s, int K, int N, int PW, int PZ, int G) {
+    const int rt = blockIdx.y, g = blockIdx.x;
+    const int kt = g / kSlotGroups, gl = g % kSlotGroups;
+    const int ng = min(kSlotGroups, G - kt * kSlotGroups), nl = 2 * ng;
+    uint8_t* block = dst + ((size_t)rt * G + (size_t)kt * kSlotGroups) * kUnitBytes;
+    const int t = threadIdx.x;
+    if (t < 32) {
+        const int r = t >> 2, c = t & 3;  // row, chunk of 32 inputs inside the group
+        const int h = c >> 1, j2 = c & 1, lane = 2 * gl + h;
+        const int word0 = g * 16 + c * 4;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        const uint32_t* src = w + (size_t)(rt * 8 + r) * PW;
+        if (word0 + 0 < PW) v.x = src[word0 + 0];
+        if (word0 + 1 < PW) v.y = src[word0 + 1];
+        if (word0 + 2 < PW) v.z = src[word0 + 2];
+        if (word0 + 3 < PW) v.w = src[word0 + 3];
+        reinterpret_cast<uint4*>(block)[(j2 * 8 + r) * nl + lane] = v;
+    } else if (t < 40) {
+        const int r = t - 32, n = rt * 8 + r;
+        uint8_t* meta = block + ng * 512 + gl * 32;
+        reinterpret_cast<__half*>(meta)[r] = s[(size_t)n * G + g];
+        meta[16 + r] = (uint8_t)((z[(size_t)n * PZ + (g >> 3)] >> (4 * (g & 7))) & 0xFu);
+        meta[24 + r] = 0;
+    }
+}
+
+// (cos, sin) of every position and frequency, with the reference's expressions (gpu_kernels.h:346-350).
+__global__ void rope_table_kernel(float2* out, int seq_len, int head_size, float theta) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    const int half_hs = head_size / 2;
+    if (i >= seq_len * half_hs) return;
+    const int pos = i / half_hs, d = i % half_hs;
+    const int head_dim = (d * 2) % head_size;
+    const float freq = 1.0f / powf(theta, head_dim / (float)head_size);
+    const float val = pos * freq;
+    out[i] = make_float2(cosf(val), sinf(val));
+}
+
+size_t stream_bytes(int K, int N) { return (size_t)(N / 8) * q4_groups(K) * kUnitBytes; }
+
+}  // namespace
+
+struct q4_fused {
+    std::vector<void*> allocs;
+    FPhase* d_phases = nullptr;
+    int nphases = 0;
+    FParams params;
+    size_t smem_bytes = 0;
+    int grid = 0;
+    int barriers_per_launch = 0;
+    unsigned long long launches = 0;
+    bool unsupported = false;
+    unsigned long long* trace = nullptr;
+};
+
+static int fused_alloc(q4_fused* f, void** p, size_t bytes) {
+    Q4_CUDA_TRY(cudaMalloc(p, bytes));
+    f->allocs.push_back(*p);
+    return Q4_OK;
+}
+
+static int make_stream(q4_fused* f, const DevQW& q, const uint8_t** out) {
+    uint8_t* d = nullptr;
+    if (int e = fused_alloc(f, (void**)&d, stream_bytes(q.K, q.N))) return e;
+    repack_kernel<<<dim3(q4_groups(q.K), q.N / 8), 64>>>(d, q.w.weight, q.w.zeros, (const __half*)q.w.scales, q.K, q.N, q4_pw(q.K),
+                                                        q4_pz(q.K), q4_groups(q.K));
+    Q4_CUDA_TRY(cudaGetLastError());
+    *out = d;
+    return Q4_OK;
+}
+
+void q4_fused_free(q4_model* m) {
+    if (!m->fused) return;
+    for (void* p : m->fused->allocs) cudaFree(p);
+    delete m->fused;
+    m->fused = nullptr;
+}
+
+void q4_fused_reset(q4_model* m) {
+    if (!m->fused || m->fused->unsupported) return;
+    q4_fused* f = m->fused;
+    cudaMemset(f->params.bar_counter, 0, sizeof(unsigned long long));
+    cudaMemset(f->params.status, 0, sizeof(int));
+    cudaMemset(f->params.attn_cnt, 0, sizeof(unsigned) * f->params.n_heads);
+    cudaDeviceSynchronize();  // the memsets run on the default stream; forward calls use the caller's stream
+    f->launches = 0;
+}
+
+int q4_fused_status(q4_model* m) {
+    if (!m->fused || m->fused->unsupported) return Q4_OK;
+    int st = 0;
+    Q4_CUDA_TRY(cudaMemcpy(&st, m->fused->params.status, sizeof(int), cudaMemcpyDeviceToHost));
+    return st;
+}
+
+int q4_fused_prepare(q4_model* m) {
+    if (m->fused) return m->fused->unsupported ? Q4_ERR_UNSUPPORTED_SIZE : Q4_OK;
+    q4_fused* f = new q4_fused();
+    m->fused = f;
+    const q4_config& c = m->cfg;
+    if (m->g != 1 || m->head_size != 128 || (c.dim % 128) || (c.hidden_dim % 8) || c.dim > 8 * kCT * 8) {
+        f->unsupported = true;
+        return Q4_ERR_UNSUPPORTED_SIZE;
+    }
+    int dev = 0, sms = 0, coop = 0;
+    Q4_CUDA_TRY(cudaGetDevice(&dev));
+    Q4_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    Q4_CUDA_TRY(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev));
+    if (!coop) { f->unsupported = true; return Q4_ERR_UNSUPPORTED_SIZE; }
+    f->grid = sms;
+
+    FParams& p = f->params;
+    memset(&p, 0, sizeof(p));
+    p.cfg = c;
+    p.head_size = m->head_size;
+    p.kv_n = m->kv_n;
+    p.kv_mul = m->kv_mul;
+    p.n_heads = c.n_heads;
+    p.nsplit = std::max(1, sms / c.n_heads);
+    p.gpu_count = 1.f;
+    p.x = (__half*)m->x; p.xb = (__half*)m->xb; p.hb = (__half*)m->hb; p.q = (__half*)m->q; p.logits = (__half*)m->logits;
+    p.kc = (__half*)m->kc; p.vc = (__half*)m->vc;
+    p.emb = (const __half*)m->emb; p.wcls = (const __half*)m->wcls;
+    p.pos_dev = m->pos;
+    p.tokens_pinned = (int*)m->shared->tokens;
+    p.pos_pinned = &m->shared->pos;
+    int e;
+#define FTRY(expr) do { e = (expr); if (e != Q4_OK) return e; } while (0)
+    FTRY(fused_alloc(f, (void**)&p.knew, 2 * (size_t)m->kv_n));
+    FTRY(fused_alloc(f, (void**)&p.attn_part, sizeof(float) * (size_t)c.n_heads * p.nsplit * (m->head_size + 2)));
+    FTRY(fused_alloc(f, (void**)&p.attn_cnt, sizeof(unsigned) * c.n_heads));
+    {
+        float2* rope = nullptr;
+        const int n = c.seq_len * (m->head_size / 2);
+        FTRY(fused_alloc(f, (void**)&rope, sizeof(float2) * (size_t)n));
+        rope_table_kernel<<<q4_div_up(n, 256), 256>>>(rope, c.seq_len, m->head_size, c.rope_theta);
+        Q4_CUDA_TRY(cudaGetLastError());
+        p.rope = reinterpret_cast<const float*>(rope);
+    }
+    FTRY(fused_alloc(f, (void**)&p.cand_val, sizeof(float) * sms));
+    FTRY(fused_alloc(f, (void**)&p.cand_idx, sizeof(int) * sms));
+    FTRY(fused_alloc(f, (void**)&p.bar_counter, sizeof(unsigned long long)));
+    FTRY(fused_alloc(f, (void**)&p.status, sizeof(int)));
+
+    std::vector<FPhase> ph;
+    int max_K = c.dim, max_part = 0, nbar = 0;
+    auto gemv_phase = [&](int K, const __half* xin, const __half* norm_w, int epi) {
+        FPhase a;
+        memset(&a, 0, sizeof(a));
+        a.type = PH_GEMV;
+        a.K = K;
+        a.G = q4_groups(K);
+        a.nkt = q4_div_up(a.G, kSlotGroups);
+        a.xin = xin;
+        a.norm_w = norm_w;
+        a.epi = epi;
+        a.tpu = 1;
+        return a;
+    };
+    auto finish = [&](FPhase& a) {
+        const int max_units = q4_div_up(a.nunits, sms);
+        max_part = std::max(max_part, max_units * a.tpu * a.nkt * 8);
+        max_K = std::max(max_K, a.K);
+        ph.push_back(a);
+        nbar++;
+    };
+    {
+        FPhase a;
+        memset(&a, 0, sizeof(a));
+        a.type = PH_EMBED;
+        ph.push_back(a);
+        nbar++;
+    }
+    for (int l = 0; l < c.n_layers; l++) {
+        const DevLayer& L = m->layers[l];
+        const long long loff = (long long)l * c.seq_len * m->kv_n;
+        const uint8_t *sq, *sk, *sv, *so, *sg, *su, *sd;
+        FTRY(make_stream(f, L.q, &sq)); FTRY(make_stream(f, L.k, &sk)); FTRY(make_stream(f, L.v, &sv)); FTRY(make_stream(f, L.o, &so));
+        FTRY(make_stream(f, L.gate, &sg)); FTRY(make_stream(f, L.up, &su)); FTRY(make_stream(f, L.down, &sd));
+        {   // QKV (+ attention RMSNorm): q -> q, k -> knew (rotated and filed by the attention phase), v -> cache row
+            FPhase a = gemv_phase(c.dim, p.x, (const __half*)L.rms_att, EPI_STORE);
+            a.nmat = 3;
+            a.m[0] = FMat{sq, p.q, m->q_n, 0, 0};
+            a.m[1] = FMat{sk, p.knew, m->kv_n, m->q_n / 8, 0};
+            a.m[2] = FMat{sv, p.vc, m->kv_n, m->q_n / 8 + m->kv_n / 8, 1};
+            a.nunits = m->q_n / 8 + 2 * (m->kv_n / 8);
+            a.loff = loff;
+            finish(a);
+        }
+        {
+            FPhase a;
+            memset(&a, 0, sizeof(a));
+            a.type = PH_ATTN;
+            a.loff = loff;
+            a.layer = l;
+            ph.push_back(a);
+            nbar++;
+        }
+        {   // O projection + residual
+            FPhase a = gemv_phase(m->o_kc, p.xb, nullptr, EPI_RESIDUAL);
+            a.nmat = 1;
+            a.m[0] = FMat{so, p.x, c.dim, 0, 0};
+            a.nunits = c.dim / 8;
+            finish(a);
+        }
+        {   // gate/up + SiLU (+ ffn RMSNorm): unit = gate tile + the same up tile
+            FPhase a = gemv_phase(c.dim, p.x, (const __half*)L.rms_ffn, EPI_SILU);
+            a.nmat = 2;
+            a.m[0] = FMat{sg, p.hb, m->h_kc, 0, 0};
+            a.m[1] = FMat{su, p.hb, m->h_kc, 0, 0};
+            a.nunits = m->h_kc / 8;
+            a.tpu = 2;
+            finish(a);
+        }
+        {   // down projection + residual
+            FPhase a = gemv_phase(m->h_kc, p.hb, nullptr, EPI_RESIDUAL);
+            a.nmat = 1;
+            a.m[0] = FMat{sd, p.x, c.dim, 0, 0};
+            a.nunits = c.dim / 8;
+            finish(a);
+        }
+    }
+    {
+        FPhase a;
+        memset(&a, 0, sizeof(a));
+        a.type = PH_CLS;
+        a.K = c.dim;
+        a.nkt = q4_div_up(c.dim, kClsChunk);
+        a.xin = p.x;
+        a.norm_w = (const __half*)m->rms_final;
+        a.nunits = m->v_n;
+        max_part = std::max(max_part, q4_div_up(a.nunits, sms) * a.nkt);
+        ph.push_back(a);
+        nbar++;
+        FPhase b;
+        memset(&b, 0, sizeof(b));
+        b.type = PH_ARGMAX;
+        ph.push_back(b);
+    }
+    Q4_CUDA_TRY(cudaDeviceSynchronize());  // repacks done
+    f->nphases = (int)ph.size();
+    FTRY(fused_alloc(f, (void**)&f->d_phases, sizeof(FPhase) * ph.size()));
+    Q4_CUDA_TRY(cudaMemcpy(f->d_phases, ph.data(), sizeof(FPhase) * ph.size(), cudaMemcpyHostToDevice));
+    p.phases = f->d_phases;
+    p.nphases = f->nphases;
+    f->barriers_per_launch = nbar;
+
+    // shared memory: ring | xq (or attention / classifier scratch) | x scales + sums | partial sums
+    const int max_G = q4_groups(max_K), max_kt = q4_div_up(max_G, kSlotGroups);
+    int xq_bytes = max_kt * 2 * 4 * 32 * 16;                                  // quantised activations
+    xq_bytes = std::max(xq_bytes, (int)((64 + 32 * 128) * sizeof(float)));       // attention scratch
+    xq_bytes = std::max(xq_bytes, 2 * c.dim);                                 // classifier x
+    p.xq_bytes = (int)align_up(xq_bytes, 128);
+    p.meta_off = kSlots * kSlotBytes + p.xq_bytes;
+    const int meta_bytes = 32 * 16 * 4 * 2;   // 16 k-tiles x 32 lanes, scale + sum
+    if (max_kt > 16) { f->unsupported = true; return Q4_ERR_UNSUPPORTED_SIZE; }
+    p.part_off = p.meta_off + meta_bytes;
+    p.part_floats = std::max(max_part, 64);
+    f->smem_bytes = (size_t)p.part_off + sizeof(float) * p.part_floats;
+    if (f->smem_bytes > 227 * 1024) { f->unsupported = true; return Q4_ERR_UNSUPPORTED_SIZE; }
+    Q4_CUDA_TRY(cudaFuncSetAttribute(fused_token_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)f->smem_bytes));
+    int per_sm = 0;
+    Q4_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_token_kernel, kThreads, f->smem_bytes));
+    if (per_sm < 1) { f->unsupported = true; return Q4_ERR_UNSUPPORTED_SIZE; }
+    q4_fused_reset(m);
+    Q4_CUDA_TRY(cudaDeviceSynchronize());
+#undef FTRY
+    return Q4_OK;
+}
+
+int q4_fused_forward(q4_model* m, cudaStream_t s, int gen_token) {
+    q4_fused* f = m->fused;
+    if (!f || f->unsupported) return Q4_ERR_UNSUPPORTED_SIZE;
+    FParams p = f->params;
+    p.write_token = gen_token;
+    p.trace = f->trace;
+    {
+        const char* dbg = getenv("Q4_FUSED_DEBUG");
+        p.debug = dbg ? atoi(dbg) : 0;
+    }
+    p.bar_base = f->launches * (unsigned long long)f->barriers_per_launch;
+    f->launches++;
+    void* args[] = {&p};
+    Q4_CUDA_TRY(cudaLaunchCooperativeKernel((void*)fused_token_kernel, dim3(f->grid), dim3(kThreads), args, f->smem_bytes, s));
+    return Q4_OK;
+}
+
+// Profiling hook: arms per-phase timestamps (CTA 0 and the last CTA) for the following fused launches and, when
+// `out` is given, copies the last launch's stamps out. Layout [2][nphases][4] of nanoseconds; also returns the
+// phase types so that the caller can group them.
+extern "C" int q4_model_trace(q4_model* m, unsigned long long* out, int* phase_types, int max_phases) {
+    if (!m) return Q4_ERR_INVALID;
+    if (int e = q4_fused_prepare(m)) return e;
+    q4_fused* f = m->fused;
+    const size_t n = (size_t)2 * f->nphases * 4;
+    if (!f->trace) {
+        if (int e = fused_alloc(f, (void**)&f->trace, n * sizeof(unsigned long long))) return e;
+        Q4_CUDA_TRY(cudaMemset(f->trace, 0, n * sizeof(unsigned long long)));
+    }
+    Q4_CUDA_TRY(cudaDeviceSynchronize());
+    if (out && phase_types && max_phases >= f->nphases) {
+        Q4_CUDA_TRY(cudaMemcpy(out, f->trace, n * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+        std::vector<FPhase> ph(f->nphases);
+        Q4_CUDA_TRY(cudaMemcpy(ph.data(), f->d_phases, sizeof(FPhase) * f->nphases, cudaMemcpyDeviceToHost));
+        for (int i = 0; i < f->nphases; i++) phase_types[i] = ph[i].type * 16 + (ph[i].type == PH_GEMV ? ph[i].epi * 4 + (ph[i].norm_w ? 1 : 0) : 0);
+    }
+    return f->nphases;
+}

@@ -10,7 +10,7 @@
 #include <unistd.h>
 #include <vector>
 
-#include "q4_common.cuh"
+#include "q4_model.h"
 
 // ------------------------------------------------------------------------------------------------------------
 // Shard helpers on host memory
@@ -82,46 +82,6 @@ extern "C" int q4_shard_rows_host(const q4_qweight* src, int K, int N, int gpu_c
 // ------------------------------------------------------------------------------------------------------------
 // Model
 // ------------------------------------------------------------------------------------------------------------
-namespace {
-
-struct DevQW {
-    q4_qweight w;
-    int K, N;  // local (shard) dims
-};
-
-struct DevLayer {
-    DevQW q, k, v, o, gate, up, down;
-    uint16_t *rms_att, *rms_ffn;
-};
-
-size_t qw_bytes(int K, int N) { return (size_t)N * ((size_t)q4_pw(K) * 4 + (size_t)q4_pz(K) * 4 + (size_t)q4_groups(K) * 2); }
-size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
-
-}  // namespace
-
-struct q4_model {
-    q4_config cfg;
-    int rank, g, tp_mode;
-    q4_comm* comm;
-    // shard geometry
-    int head_size, kv_dim, kv_mul;
-    int q_n, kv_n;            // local q / kv outputs
-    int o_kb, o_kc;           // local slice of the attention output vector (inputs of o_proj)
-    int h_kb, h_kc;           // local slice of the hidden vector (outputs of gate/up, inputs of down)
-    int v_n;                  // local classifier rows
-    // device memory
-    char* arena;
-    size_t arena_bytes;
-    uint16_t *emb, *wcls, *rms_final;
-    std::vector<DevLayer> layers;
-    uint16_t *x, *xb, *hb, *q, *logits, *kc, *vc;
-    float* attn_scratch;
-    int* pos;
-    q4_shared_data* shared;
-    cudaGraphExec_t graph[2];
-    bool graph_ready[2];
-};
-
 namespace {
 
 struct FileMap {
@@ -207,6 +167,7 @@ int upload_raw(Arena& a, uint16_t** dst, const void* src, size_t bytes) {
 
 extern "C" int q4_model_free(q4_model* m) {
     if (!m) return Q4_OK;
+    q4_fused_free(m);
     for (int i = 0; i < 2; i++)
         if (m->graph_ready[i]) cudaGraphExecDestroy(m->graph[i]);
     cudaFree(m->arena);
@@ -265,6 +226,7 @@ extern "C" int q4_model_load(q4_model** out, const char* path, int rank, int gpu
     else { m->h_kb = 0; m->h_kc = c.hidden_dim; }
     m->v_n = c.vocab_size / g;
     m->graph_ready[0] = m->graph_ready[1] = false;
+    m->fused = nullptr;
     m->arena = nullptr;
     m->x = m->xb = m->hb = m->q = m->logits = m->kc = m->vc = nullptr;
     m->attn_scratch = nullptr;
@@ -373,6 +335,7 @@ extern "C" int q4_model_reset(q4_model* m, const int* prompt_tokens, int n, int 
     Q4_CUDA_TRY(cudaMemcpy(m->pos, &pos, sizeof(int), cudaMemcpyHostToDevice));
     m->shared->pos = pos;
     if (n > 0 && prompt_tokens) memcpy((void*)m->shared->tokens, prompt_tokens, sizeof(int) * (size_t)n);
+    q4_fused_reset(m);
     return Q4_OK;
 }
 
@@ -427,7 +390,24 @@ extern "C" int q4_model_forward(q4_model* m, void* stream, int gen_token, int pa
         Q4_CUDA_TRY(cudaGraphLaunch(m->graph[gen_token], s));
         return Q4_OK;
     }
+    if (path == 2) {
+        if (int e = q4_fused_prepare(m)) return e;
+        return q4_fused_forward(m, s, gen_token);
+    }
     return Q4_ERR_INVALID;
+}
+
+extern "C" int q4_model_prepare(q4_model* m, int path) {
+    if (!m || path < 0 || path > 2) return Q4_ERR_INVALID;
+    return path == 2 ? q4_fused_prepare(m) : Q4_OK;
+}
+
+extern "C" int q4_model_status(q4_model* m) {
+    if (!m) return Q4_ERR_INVALID;
+    Q4_CUDA_TRY(cudaDeviceSynchronize());
+    int st = q4_fused_status(m);
+    if (st == Q4_OK && m->comm) st = q4_comm_status(m->comm);
+    return st;
 }
 
 extern "C" int q4_generate(q4_model* m, const int* prompt_tokens, int n_prompt, int steps, int path, int* out_tokens, int* timed_tokens,

@@ -1,0 +1,51 @@
+// Internal model structures shared by the host code (q4_model.cu) and the fused decode kernel (q4_fused.cu).
+#pragma once
+#include <vector>
+
+#include "q4_common.cuh"
+
+struct DevQW {
+    q4_qweight w;
+    int K, N;  // local (shard) dims
+};
+
+struct DevLayer {
+    DevQW q, k, v, o, gate, up, down;
+    uint16_t *rms_att, *rms_ffn;
+};
+
+static inline size_t qw_bytes(int K, int N) { return (size_t)N * ((size_t)q4_pw(K) * 4 + (size_t)q4_pz(K) * 4 + (size_t)q4_groups(K) * 2); }
+static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct q4_fused;  // state of the fused (persistent-kernel) path, q4_fused.cu
+
+struct q4_model {
+    q4_config cfg;
+    int rank, g, tp_mode;
+    q4_comm* comm;
+    // shard geometry
+    int head_size, kv_dim, kv_mul;
+    int q_n, kv_n;            // local q / kv outputs
+    int o_kb, o_kc;           // local slice of the attention output vector (inputs of o_proj)
+    int h_kb, h_kc;           // local slice of the hidden vector (outputs of gate/up, inputs of down)
+    int v_n;                  // local classifier rows
+    // device memory
+    char* arena;
+    size_t arena_bytes;
+    uint16_t *emb, *wcls, *rms_final;
+    std::vector<DevLayer> layers;
+    uint16_t *x, *xb, *hb, *q, *logits, *kc, *vc;
+    float* attn_scratch;
+    int* pos;
+    q4_shared_data* shared;
+    cudaGraphExec_t graph[2];
+    bool graph_ready[2];
+    q4_fused* fused;
+};
+
+// q4_fused.cu
+int q4_fused_prepare(q4_model* m);                              // builds the stream-layout weights and the phase table (lazy)
+int q4_fused_forward(q4_model* m, cudaStream_t s, int gen_token);
+void q4_fused_reset(q4_model* m);                               // re-arms barrier counters (after q4_model_reset)
+void q4_fused_free(q4_model* m);
+int q4_fused_status(q4_model* m);

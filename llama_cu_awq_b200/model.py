@@ -26,8 +26,12 @@ class Transformer:
         check(self._L.q4_model_forward(self.h, C.c_void_p(self.stream.cuda_stream), int(bool(gen_token)), path), "run_transformer")
 
     def best_path(self):
-        """The fastest forward path this build offers (1 = CUDA-graph replay of the per-op kernels)."""
-        return 1
+        """The fastest forward path that serves this model: 2 = persistent fused kernel, else 1 = CUDA-graph
+        replay of the per-op kernels."""
+        return 2 if self._L.q4_model_prepare(self.h, 2) == _lib.Q4_OK else 1
+
+    def status(self):
+        return self._L.q4_model_status(self.h)
 
     def synchronize(self):
         self.stream.synchronize()
