@@ -36,8 +36,13 @@ constexpr int kSlotGroups = 16;
 constexpr int kUnitBytes = 544;
 constexpr int kSlotBytes = kSlotGroups * kUnitBytes;  // 8704
 constexpr int kSlots = 16;
-constexpr int kCW = 8;                 // consumer warps
+#ifndef Q4_FUSED_CW
+#define Q4_FUSED_CW 11
+#endif
+constexpr int kCW = Q4_FUSED_CW;       // consumer warps (+1 producer warp: 12 warps = 3 per SM sub-partition)
 constexpr int kCT = kCW * 32;          // consumer threads
+constexpr int kAG = kCT / 8;           // attention lane groups (positions in flight per CTA)
+static_assert(kCT % 16 == 0, "activation staging maps 16 consecutive threads to one group of 128 inputs");
 constexpr int kThreads = 32 + kCT;     // + producer warp
 constexpr int kClsChunk = 4096;        // halfs of one classifier row per slot (8192 B)
 constexpr unsigned kPollLimit = 1u << 26;                        // polls, and
@@ -65,9 +70,10 @@ struct FPhase {
     int nunits, tpu;        // work units of the phase and tiles per unit (2 for gate/up pairs)
     int epi;
     long long loff;         // KV cache layer offset (halfs)
-    // attention
     int layer;
+    int pad_[3];
 };
+static_assert(sizeof(FPhase) % 16 == 0, "FPhase is copied in 16-byte pieces");
 
 struct FParams {
     const FPhase* phases;
@@ -90,7 +96,8 @@ struct FParams {
     unsigned long long bar_base;  // barriers completed by earlier launches
     int* status;
     int write_token;
-    int debug;                   // measurement only: bit 0 = consumers skip the GEMV math (pure streaming)
+    int debug;                   // measurement only: 1 = consumers skip the GEMV math (pure streaming), 2 = no streaming (pure math)
+    int l2_ahead;                // slots each producer keeps requested into L2 beyond the ring
     unsigned long long* trace;   // optional: [2 CTAs][nphases][4] device timestamps (ns), or null
     // shared memory carve-up (bytes)
     int xq_bytes, meta_off, part_off, part_floats;
@@ -139,6 +146,9 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
+__device__ __forceinline__ void prefetch_l2(const void* src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kCT) : "memory"); }
 __device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {
     int d;
@@ -152,20 +162,22 @@ __device__ __forceinline__ float fma_mixed(__half a, __half b, float c) {
 }
 
 // Grid-wide barrier among the consumer threads of all CTAs (the producer warps never wait here).
-__device__ __forceinline__ void grid_barrier(const FParams& p, unsigned& nbar, int ctid) {
+__device__ __forceinline__ void grid_barrier(const FParams& p, unsigned& nbar, int ctid, int* s_abort) {
     consumer_sync();  // orders every consumer thread's stores before thread 0's release below (cumulativity)
     if (ctid == 0) {
         nbar++;
         const unsigned long long target = (p.bar_base + nbar) * (unsigned long long)gridDim.x;
         unsigned long long v;
+        const int st = *(volatile int*)p.status;  // in flight together with the atomic
         asm volatile("atom.add.release.gpu.global.u64 %0, [%1], 1;" : "=l"(v) : "l"(p.bar_counter) : "memory");
+        if (st != 0) *s_abort = 1;
         unsigned spins = 0;
         for (;;) {
             asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p.bar_counter) : "memory");
             if (v >= target) break;
             if ((++spins & 255u) == 0) {
-                if (*(volatile int*)p.status != 0) break;
-                if (spins > kSpinLimit) { atomicExch(p.status, Q4_ERR_TIMEOUT); break; }
+                if (*(volatile int*)p.status != 0) { *s_abort = 1; break; }
+                if (spins > kSpinLimit) { atomicExch(p.status, Q4_ERR_TIMEOUT); *s_abort = 1; break; }
             }
         }
     }
@@ -230,6 +242,51 @@ __device__ __forceinline__ void tile_info(const FPhase& ph, int t, int& mi, int&
     if (ph.nmat > 1 && t >= ph.m[1].tile0) mi = 1;
     if (ph.nmat > 2 && t >= ph.m[2].tile0) mi = 2;
     rt = t - ph.m[mi].tile0;
+}
+
+// Walks the slots of one CTA in issue order: phase by phase, unit by unit (cta, cta + grid, ...), tile by tile,
+// k-tile by k-tile. The consumers enumerate the same order with plain loops.
+struct SlotCursor {
+    int pi, u, tt, kt;
+    int wrapped, count;
+    FPhase* cache;   // shared-memory copy of phases[pi] (the table itself lives in global memory)
+    int cached_pi;
+};
+__device__ __forceinline__ void cursor_init(SlotCursor& c, int cta) { c.pi = 0; c.u = cta; c.tt = 0; c.kt = 0; c.wrapped = 0; c.count = 0; c.cached_pi = -1; }
+__device__ __forceinline__ void copy_phase(FPhase* dst, const FPhase* src) {
+    const int4* s4 = reinterpret_cast<const int4*>(src);
+    int4* d4 = reinterpret_cast<int4*>(dst);
+#pragma unroll
+    for (int i = 0; i < (int)(sizeof(FPhase) / 16); i++) d4[i] = __ldg(s4 + i);
+}
+__device__ __forceinline__ bool cursor_next(SlotCursor& c, const FParams& p, int cta, int grid, const void*& src, uint32_t& bytes) {
+    for (;;) {
+        if (c.pi >= p.nphases) return false;
+        if (c.cached_pi != c.pi) { copy_phase(c.cache, p.phases + c.pi); c.cached_pi = c.pi; }
+        const FPhase& ph = *c.cache;
+        if (ph.type == PH_GEMV && c.u < ph.nunits) {
+            int mi, rt;
+            tile_info(ph, c.u * ph.tpu + c.tt, mi, rt);
+            const int ng = min(kSlotGroups, ph.G - c.kt * kSlotGroups);
+            src = ph.m[mi].blocks + ((size_t)rt * ph.G + (size_t)c.kt * kSlotGroups) * kUnitBytes;
+            bytes = ng * kUnitBytes;
+            if (++c.kt == ph.nkt) { c.kt = 0; if (++c.tt == ph.tpu) { c.tt = 0; c.u += grid; } }
+            c.count++;
+            return true;
+        }
+        if (ph.type == PH_CLS && c.u < ph.nunits) {
+            const int len = min(kClsChunk, ph.K - c.kt * kClsChunk);
+            src = p.wcls + (size_t)c.u * ph.K + (size_t)c.kt * kClsChunk;
+            bytes = len * 2;
+            if (++c.kt == ph.nkt) { c.kt = 0; c.u += grid; }
+            c.count++;
+            return true;
+        }
+        c.pi++;
+        c.u = cta;
+        c.tt = 0;
+        c.kt = 0;
+    }
 }
 
 // ------------------------------------------------------------------------------------------------------------
@@ -343,6 +400,24 @@ __device__ void stage_x_f16(const FPhase& ph, __half* xf, float* red, int ctid) 
     consumer_sync();
 }
 
+// Four columns x 32 inputs: 64 DP4As in 16 independent accumulator chains (columns innermost), so that two warps
+// per scheduler are enough to keep the half-rate DP4A pipe busy.
+template <int RB>
+__device__ __forceinline__ void dot_rows4(const uint4 (&w)[4], const uint4 (&xv)[4], int (&ah)[8], int (&ah16)[8], int (&al)[8], int (&al16)[8]) {
+#pragma unroll
+    for (int wi = 0; wi < 4; wi++) {
+#pragma unroll
+        for (int r = 0; r < 4; r++) {
+            const uint32_t word = wi == 0 ? w[r].x : wi == 1 ? w[r].y : wi == 2 ? w[r].z : w[r].w;
+            const uint32_t e = word & 0x0F0F0F0Fu, o = word & 0xF0F0F0F0u;
+            ah[RB + r] = dp4a_us(e, xv[wi].x, ah[RB + r]);
+            ah16[RB + r] = dp4a_us(o, xv[wi].y, ah16[RB + r]);
+            al[RB + r] = dp4a_us(e, xv[wi].z, al[RB + r]);
+            al16[RB + r] = dp4a_us(o, xv[wi].w, al16[RB + r]);
+        }
+    }
+}
+
 // One slot of a GEMV phase: 8 columns x ng groups. Returns via `part` (8 floats per slot in shared memory).
 __device__ __forceinline__ void gemv_slot(const uint8_t* slot, int ng, int kt, const uint4* xq, const float* xs_scale, const int* xs_sum,
                                           float* part, int lane) {
@@ -357,31 +432,30 @@ __device__ __forceinline__ void gemv_slot(const uint8_t* slot, int ng, int kt, c
         for (int r = 0; r < 8; r++) { ah[r] = 0; ah16[r] = 0; al[r] = 0; al16[r] = 0; }
         const uint4* wb = reinterpret_cast<const uint4*>(slot) + lane;
         const uint4* xb = xq + (kt * 2) * 4 * 32 + lane;
+        // loads run one quarter step (4 columns of one 32-input chunk) ahead of the math
+        uint4 x0[4], x1[4], wa[4], wbuf[4];
 #pragma unroll
-        for (int j2 = 0; j2 < 2; j2++) {
-            uint4 xv[4];
+        for (int wi = 0; wi < 4; wi++) x0[wi] = xb[wi * 32];
 #pragma unroll
-            for (int wi = 0; wi < 4; wi++) xv[wi] = xb[(j2 * 4 + wi) * 32];
+        for (int r = 0; r < 4; r++) wa[r] = wb[r * nl];
 #pragma unroll
-            for (int r = 0; r < 8; r++) {
-                const uint4 w = wb[(j2 * 8 + r) * nl];
-                const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+        for (int r = 0; r < 4; r++) wbuf[r] = wb[(4 + r) * nl];
 #pragma unroll
-                for (int wi = 0; wi < 4; wi++) {
-                    const uint32_t e = ww[wi] & 0x0F0F0F0Fu, o = ww[wi] & 0xF0F0F0F0u;
-                    ah[r] = dp4a_us(e, xv[wi].x, ah[r]);
-                    ah16[r] = dp4a_us(o, xv[wi].y, ah16[r]);
-                    al[r] = dp4a_us(e, xv[wi].z, al[r]);
-                    al16[r] = dp4a_us(o, xv[wi].w, al16[r]);
-                }
-            }
-        }
+        for (int wi = 0; wi < 4; wi++) x1[wi] = xb[(4 + wi) * 32];
+        dot_rows4<0>(wa, x0, ah, ah16, al, al16);
+#pragma unroll
+        for (int r = 0; r < 4; r++) wa[r] = wb[(8 + r) * nl];
+        dot_rows4<4>(wbuf, x0, ah, ah16, al, al16);
+#pragma unroll
+        for (int r = 0; r < 4; r++) wbuf[r] = wb[(12 + r) * nl];
+        dot_rows4<0>(wa, x1, ah, ah16, al, al16);
         const uint8_t* meta = slot + ng * 512 + (lane >> 1) * 32;
         const uint4 sc = *reinterpret_cast<const uint4*>(meta);
         const uint2 zz = *reinterpret_cast<const uint2*>(meta + 16);
-        const __half* sh = reinterpret_cast<const __half*>(&sc);
         const float sx = xs_scale[kt * 32 + lane];
         const int sumx = xs_sum[kt * 32 + lane];
+        dot_rows4<4>(wbuf, x1, ah, ah16, al, al16);
+        const __half* sh = reinterpret_cast<const __half*>(&sc);
 #pragma unroll
         for (int r = 0; r < 8; r++) {
             const int z = (int)(((r < 4 ? zz.x : zz.y) >> (8 * (r & 3))) & 0xFFu);
@@ -401,6 +475,9 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
     __shared__ uint64_t full_bar[kSlots], empty_bar[kSlots];
     __shared__ float red[kCW];
     __shared__ int s_flag, s_abort;
+    __shared__ unsigned s_ring_seq;   // slots the ring cursor has issued (read by the L2 cursor)
+    __shared__ __align__(16) FPhase s_pph[2];  // producer cursors' phase descriptors
+    __shared__ __align__(16) FPhase s_cph;     // consumers' phase descriptor
 
     uint8_t* ring = smem;
     uint4* xq = reinterpret_cast<uint4*>(smem + kSlots * kSlotBytes);
@@ -412,6 +489,8 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
     const int cta = blockIdx.x, grid = gridDim.x;
 
     if (tid == 0) {
+        s_abort = 0;
+        s_ring_seq = 0;
         for (int s = 0; s < kSlots; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -419,37 +498,57 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
 
     if (warp == 0) {
         // ================= producer: stream every phase's weights of this CTA into the ring =================
-        if (lane != 0) return;
-        unsigned seq = 0;
-        for (int pi = 0; pi < p.nphases; pi++) {
-            const FPhase& ph = p.phases[pi];
-            if (ph.type == PH_GEMV) {
-                for (int u = cta; u < ph.nunits; u += grid) {
-                    for (int tt = 0; tt < ph.tpu; tt++) {
-                        int mi, rt;
-                        tile_info(ph, u * ph.tpu + tt, mi, rt);
-                        const uint8_t* base = ph.m[mi].blocks + (size_t)rt * ph.G * kUnitBytes;
-                        for (int kt = 0; kt < ph.nkt; kt++, seq++) {
-                            const int ng = min(kSlotGroups, ph.G - kt * kSlotGroups);
-                            const int slot = seq % kSlots;
-                            if (!mbar_wait(&empty_bar[slot], ((seq / kSlots) & 1) ^ 1, p.status)) return;
-                            mbar_expect_tx(&full_bar[slot], ng * kUnitBytes);
-                            bulk_g2s(ring + slot * kSlotBytes, base + (size_t)kt * kSlotGroups * kUnitBytes, ng * kUnitBytes, &full_bar[slot]);
-                        }
+        // Two cursors walk the same slot list: the ring cursor fills shared memory as slots free up; the L2 cursor runs
+        // p.l2_ahead slots in front of it and only requests the bytes into L2 (fire and forget), so HBM keeps
+        // streaming while the ring is full and the consumers sit in a barrier. After the last slot the L2 cursor wraps
+        // around: the next token's first slots are already on their way when its kernel starts.
+        if (lane > 1 || (p.debug & 2)) return;
+        const void* src;
+        uint32_t bytes;
+        if (lane == 1) {
+            // L2 cursor (own lane, so that a slow prefetch never delays a ring copy)
+            if (p.l2_ahead <= 0) return;
+            SlotCursor c;
+            cursor_init(c, cta);
+            c.cache = &s_pph[1];
+            unsigned issued = 0;
+            unsigned long long t0 = 0;
+            for (;;) {
+                if (!cursor_next(c, p, cta, grid, src, bytes)) {
+                    if (c.wrapped) return;          // second pass done
+                    cursor_init(c, cta);
+                    c.wrapped = 1;
+                    continue;
+                }
+                if (c.wrapped && c.count > p.l2_ahead) return;
+                // stay at most l2_ahead slots in front of the ring cursor
+                unsigned spins = 0;
+                while (!c.wrapped && issued >= *(volatile unsigned*)&s_ring_seq + (unsigned)p.l2_ahead) {
+                    __nanosleep(200);
+                    if ((++spins & 255u) == 0) {
+                        const unsigned long long now = global_ns();
+                        if (t0 == 0) t0 = now;
+                        if (now - t0 > kWaitLimitNs || *(volatile int*)p.status != 0) return;
                     }
                 }
-            } else if (ph.type == PH_CLS) {
-                for (int row = cta; row < ph.nunits; row += grid) {
-                    for (int kc = 0; kc < ph.nkt; kc++, seq++) {
-                        const int len = min(kClsChunk, ph.K - kc * kClsChunk);
-                        const int slot = seq % kSlots;
-                        if (!mbar_wait(&empty_bar[slot], ((seq / kSlots) & 1) ^ 1, p.status)) return;
-                        mbar_expect_tx(&full_bar[slot], len * 2);
-                        bulk_g2s(ring + slot * kSlotBytes, p.wcls + (size_t)row * ph.K + kc * kClsChunk, len * 2, &full_bar[slot]);
-                    }
-                }
+                t0 = 0;
+                prefetch_l2(src, bytes);
+                issued++;
             }
         }
+        SlotCursor ring_c;
+        cursor_init(ring_c, cta);
+        ring_c.cache = &s_pph[0];
+        unsigned seq = 0;
+        while (cursor_next(ring_c, p, cta, grid, src, bytes)) {
+            const int slot = seq % kSlots;
+            if (!mbar_wait(&empty_bar[slot], ((seq / kSlots) & 1) ^ 1, p.status)) return;
+            mbar_expect_tx(&full_bar[slot], bytes);
+            bulk_g2s(ring + slot * kSlotBytes, src, bytes, &full_bar[slot]);
+            seq++;
+            *(volatile unsigned*)&s_ring_seq = seq;
+        }
+        *(volatile unsigned*)&s_ring_seq = 0x7fffffffu;
         return;
     }
 
@@ -461,10 +560,12 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
     const int HS = p.head_size;
 
     for (int pi = 0; pi < p.nphases; pi++) {
-        const FPhase& ph = p.phases[pi];
-        // all consumer threads leave together (named barriers count live threads), never one by one
-        if (ctid == 0) s_abort = *(volatile int*)p.status;
+        if (ctid < (int)(sizeof(FPhase) / 16))
+            reinterpret_cast<int4*>(&s_cph)[ctid] = __ldg(reinterpret_cast<const int4*>(p.phases + pi) + ctid);
         consumer_sync();
+        const FPhase& ph = s_cph;
+        // all consumer threads leave together (named barriers count live threads), never one by one:
+        // s_abort is written by thread 0 inside grid_barrier and read after the barrier's closing consumer_sync
         if (s_abort != 0) return;
         TRACE(0);
 
@@ -476,7 +577,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                 uint4* dst = reinterpret_cast<uint4*>(p.x);
                 for (int i = cta * kCT + ctid; i < p.cfg.dim / 8; i += grid * kCT) dst[i] = src[i];
             }
-            grid_barrier(p, nbar, ctid);
+            grid_barrier(p, nbar, ctid, &s_abort);
 
         } else if (ph.type == PH_GEMV) {
             stage_x_quant(ph, xq, xs_scale, xs_sum, red, ctid);
@@ -487,55 +588,59 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                 const int u = cta + (ctid >> 3) * grid;
                 if (u < ph.nunits) resid = __ldcg(ph.m[0].out + u * 8 + (ctid & 7));
             }
-            // slots of this CTA, in the producer's order; slot i belongs to consumer warp i % kCW
-            int lt = 0;
-            for (int u = cta; u < ph.nunits; u += grid) {
-                for (int tt = 0; tt < ph.tpu; tt++, lt++) {
-                    for (int kt = 0; kt < ph.nkt; kt++, seq++) {
-                        if ((int)(seq % kCW) != cw) continue;
-                        const int ng = min(kSlotGroups, ph.G - kt * kSlotGroups);
-                        const int slot = seq % kSlots;
-                        if (failed || !mbar_wait(&full_bar[slot], (seq / kSlots) & 1, p.status)) { failed = true; continue; }
-                        if (!(p.debug & 1)) gemv_slot(ring + slot * kSlotBytes, ng, kt, xq, xs_scale, xs_sum, part + (size_t)(lt * ph.nkt + kt) * 8, lane);
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(&empty_bar[slot]);
-                    }
+            // slots of this CTA, in the producer's order; slot i belongs to consumer warp i % kCW.
+            // Phase constants live in registers: the descriptor is not re-read inside the loops.
+            const int nunits = ph.nunits, tpu = ph.tpu, nkt = ph.nkt, G = ph.G, dbg = p.debug;
+            const int my_units = nunits > cta ? (nunits - cta + grid - 1) / grid : 0;
+            const int ntl = my_units * tpu, nslots = ntl * nkt;
+            {
+                const unsigned first = seq + ((cw + kCW - (seq % kCW)) % kCW);  // first slot of this warp in the phase
+                for (unsigned sq = first; sq < seq + nslots; sq += kCW) {
+                    const int li = (int)(sq - seq);          // slot index inside the phase = lt * nkt + kt
+                    const int kt = li % nkt;
+                    const int ng = min(kSlotGroups, G - kt * kSlotGroups);
+                    const int slot = sq % kSlots;
+                    if (!(dbg & 2) && (failed || !mbar_wait(&full_bar[slot], (sq / kSlots) & 1, p.status))) { failed = true; continue; }
+                    if (!(dbg & 1)) gemv_slot(ring + slot * kSlotBytes, ng, kt, xq, xs_scale, xs_sum, part + (size_t)li * 8, lane);
+                    __syncwarp();
+                    if (lane == 0 && !(dbg & 2)) mbar_arrive(&empty_bar[slot]);
                 }
+                seq += nslots;
             }
             consumer_sync();
             TRACE(2);
             // epilogue: one thread per (local tile, column)
-            const int ntl = lt;
+            const int epi = ph.epi;
             for (int e = ctid; e < ntl * 8; e += kCT) {
                 const int l2 = e >> 3, r = e & 7;
-                const int u = cta + (l2 / ph.tpu) * grid;
+                const int u = cta + (l2 / tpu) * grid;
                 int mi, rt;
-                tile_info(ph, u * ph.tpu + (l2 % ph.tpu), mi, rt);
+                tile_info(ph, u * tpu + (l2 % tpu), mi, rt);
                 float sum = 0.f;
-                for (int kt = 0; kt < ph.nkt; kt++) sum += part[(size_t)(l2 * ph.nkt + kt) * 8 + r];
+                for (int kt = 0; kt < nkt; kt++) sum += part[(size_t)(l2 * nkt + kt) * 8 + r];
                 const int n = rt * 8 + r;
-                if (ph.epi == EPI_SILU) {
+                if (epi == EPI_SILU) {
                     if (mi == 0) {
                         float up = 0.f;
-                        for (int kt = 0; kt < ph.nkt; kt++) up += part[(size_t)((l2 + 1) * ph.nkt + kt) * 8 + r];
+                        for (int kt = 0; kt < nkt; kt++) up += part[(size_t)((l2 + 1) * nkt + kt) * 8 + r];
                         ph.m[0].out[n] = __float2half(silu_mul(sum, up));
                     }
                 } else {
                     const FMat& m = ph.m[mi];
                     __half* out = m.out;
                     if (m.kv) out += ph.loff + (long long)pos * m.n;
-                    if (ph.epi == EPI_RESIDUAL) sum += __half2float(e == ctid ? resid : __ldcg(out + n)) / p.gpu_count;
+                    if (epi == EPI_RESIDUAL) sum += __half2float(e == ctid ? resid : __ldcg(out + n)) / p.gpu_count;
                     out[n] = __float2half(sum);
                 }
             }
-            grid_barrier(p, nbar, ctid);
+            grid_barrier(p, nbar, ctid, &s_abort);
             TRACE(3);
 
         } else if (ph.type == PH_ATTN) {
             // ---- attention of one query per head over positions 0..pos, split over CTAs (llama2_q4.cu:410-427) ----
-            float* sm_m = reinterpret_cast<float*>(xq);          // [32]
-            float* sm_l = sm_m + 32;                             // [32]
-            float* sm_acc = sm_l + 32;                           // [32][128]
+            float* sm_m = reinterpret_cast<float*>(xq);          // [kAG]
+            float* sm_l = sm_m + kAG;                            // [kAG]
+            float* sm_acc = sm_l + kAG;                          // [kAG][128]
             const int lane8 = ctid & 7, grp = ctid >> 3;
             const int d0 = lane8 * 16;                           // this lane's 16 head dims; RoPE partner dims are d0 ^ 64
             const bool upper = d0 >= 64;
@@ -559,9 +664,9 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
             for (int id = cta; id < nitems; id += grid) {
                 const int h = id / p.nsplit, split = id % p.nsplit;
                 const int kvh = h / p.kv_mul;
-                const int units = (T + 31) / 32;
+                const int units = (T + kAG - 1) / kAG;
                 const int u0 = (int)((long long)units * split / p.nsplit), u1 = (int)((long long)units * (split + 1) / p.nsplit);
-                const int t0 = u0 * 32, t1 = min(u1 * 32, T);
+                const int t0 = u0 * kAG, t1 = min(u1 * kAG, T);
                 const size_t col = (size_t)kvh * HS + d0;
                 // first step's K/V rows are requested before anything else so that their latency overlaps the query set-up
                 uint4 kn[2], vn[2];
@@ -597,12 +702,12 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                 float m = -CUDART_INF_F, l = 0.f, acc[16];
 #pragma unroll
                 for (int j = 0; j < 16; j++) acc[j] = 0.f;
-                for (int tb = t0; tb < t1; tb += 32) {
+                for (int tb = t0; tb < t1; tb += kAG) {
                     const int t = tb + grp;
                     const bool valid = t < t1;
                     const int tt = valid ? t : t0;
                     const uint4 kcur[2] = {kn[0], kn[1]}, vcur[2] = {vn[0], vn[1]};
-                    fetch(tb + 32);  // next step's rows in flight during this step's math
+                    fetch(tb + kAG);  // next step's rows in flight during this step's math
                     float kf[16], vf[16];
                     if (tt == pos) {
                         // the new key is un-rotated in knew: rotate it here; the head group's first query head also files it
@@ -660,9 +765,9 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                 float* outp = p.attn_part + (size_t)id * (HS + 2);
                 if (ctid < HS) {
                     float M = -CUDART_INF_F;
-                    for (int g2 = 0; g2 < 32; g2++) M = fmaxf(M, sm_m[g2]);
+                    for (int g2 = 0; g2 < kAG; g2++) M = fmaxf(M, sm_m[g2]);
                     float a = 0.f, L = 0.f;
-                    for (int g2 = 0; g2 < 32; g2++) {
+                    for (int g2 = 0; g2 < kAG; g2++) {
                         if (sm_m[g2] != -CUDART_INF_F) {
                             const float w = expf(sm_m[g2] - M);
                             a += sm_acc[g2 * 128 + ctid] * w;
@@ -701,7 +806,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                 consumer_sync();
             }
             TRACE(2);
-            grid_barrier(p, nbar, ctid);
+            grid_barrier(p, nbar, ctid, &s_abort);
             TRACE(3);
 
         } else if (ph.type == PH_CLS) {
@@ -709,35 +814,52 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
             __half* xf = reinterpret_cast<__half*>(xq);
             stage_x_f16(ph, xf, red, ctid);
             TRACE(1);
-            int lt = 0;
-            for (int row = cta; row < ph.nunits; row += grid, lt++) {
-                for (int kc = 0; kc < ph.nkt; kc++, seq++) {
-                    if ((int)(seq % kCW) != cw) continue;
-                    const int len = min(kClsChunk, ph.K - kc * kClsChunk);
-                    const int slot = seq % kSlots;
-                    if (failed || !mbar_wait(&full_bar[slot], (seq / kSlots) & 1, p.status)) { failed = true; continue; }
+            const int nunits = ph.nunits, nkt = ph.nkt, K = ph.K;
+            const int lt = nunits > cta ? (nunits - cta + grid - 1) / grid : 0;  // rows of this CTA
+            const int nslots = lt * nkt;
+            const unsigned first = seq + ((cw + kCW - (seq % kCW)) % kCW);
+            for (unsigned sq = first; sq < seq + nslots; sq += kCW) {
+                {
+                    const int li = (int)(sq - seq), kc = li % nkt;
+                    const int len = min(kClsChunk, K - kc * kClsChunk);
+                    const int slot = sq % kSlots;
+                    if (!(p.debug & 2) && (failed || !mbar_wait(&full_bar[slot], (sq / kSlots) & 1, p.status))) { failed = true; continue; }
                     const uint4* wv = reinterpret_cast<const uint4*>(ring + slot * kSlotBytes);
                     const uint4* xv = reinterpret_cast<const uint4*>(xf + kc * kClsChunk);
-                    float a = 0.f;
-                    for (int i = lane; i * 8 < len; i += 32) {
-                        const uint4 w = wv[i], xx = xv[i];
-                        const __half* wh = reinterpret_cast<const __half*>(&w);
-                        const __half* xh = reinterpret_cast<const __half*>(&xx);
+                    float a4[8];
 #pragma unroll
-                        for (int j = 0; j < 8; j++) a = fma_mixed(wh[j], xh[j], a);
+                    for (int j = 0; j < 8; j++) a4[j] = 0.f;
+                    const int nvec = len >> 3;
+                    for (int i = lane; i < nvec; i += 128) {
+                        uint4 w[4], xx[4];
+#pragma unroll
+                        for (int u = 0; u < 4; u++) {
+                            const int ii = i + u * 32;
+                            w[u] = ii < nvec ? wv[ii] : make_uint4(0, 0, 0, 0);
+                            xx[u] = ii < nvec ? xv[ii] : make_uint4(0, 0, 0, 0);
+                        }
+#pragma unroll
+                        for (int u = 0; u < 4; u++) {
+                            const __half* wh = reinterpret_cast<const __half*>(&w[u]);
+                            const __half* xh = reinterpret_cast<const __half*>(&xx[u]);
+#pragma unroll
+                            for (int j = 0; j < 8; j++) a4[j] = fma_mixed(wh[j], xh[j], a4[j]);
+                        }
                     }
+                    float a = ((a4[0] + a4[1]) + (a4[2] + a4[3])) + ((a4[4] + a4[5]) + (a4[6] + a4[7]));
                     a = warp_sum(a);
-                    if (lane == 0) part[lt * ph.nkt + kc] = a;
+                    if (lane == 0) part[li] = a;
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&empty_bar[slot]);
+                    if (lane == 0 && !(p.debug & 2)) mbar_arrive(&empty_bar[slot]);
                 }
             }
+            seq += nslots;
             consumer_sync();
             float best = -CUDART_INF_F;
             int bi = 0x7fffffff;
             for (int e = ctid; e < lt; e += kCT) {
                 float sum = 0.f;
-                for (int kc = 0; kc < ph.nkt; kc++) sum += part[e * ph.nkt + kc];
+                for (int kc = 0; kc < nkt; kc++) sum += part[e * nkt + kc];
                 const int n = cta + e * grid;
                 const __half hv = __float2half(sum);
                 p.logits[n] = hv;
@@ -764,7 +886,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                 p.cand_idx[cta] = bi;
             }
             TRACE(2);
-            grid_barrier(p, nbar, ctid);
+            grid_barrier(p, nbar, ctid, &s_abort);
             TRACE(3);
 
         } else if (ph.type == PH_ARGMAX) {
@@ -898,7 +1020,7 @@ int q4_fused_prepare(q4_model* m) {
     q4_fused* f = new q4_fused();
     m->fused = f;
     const q4_config& c = m->cfg;
-    if (m->g != 1 || m->head_size != 128 || (c.dim % 128) || (c.hidden_dim % 8) || c.dim > 8 * kCT * 8) {
+    if (m->g != 1 || m->head_size != 128 || (c.dim % 128) || (c.hidden_dim % 8) || c.dim > 8 * kCT * 8) {  // 8 = staging batch
         f->unsupported = true;
         return Q4_ERR_UNSUPPORTED_SIZE;
     }
@@ -1048,7 +1170,7 @@ int q4_fused_prepare(q4_model* m) {
     // shared memory: ring | xq (or attention / classifier scratch) | x scales + sums | partial sums
     const int max_G = q4_groups(max_K), max_kt = q4_div_up(max_G, kSlotGroups);
     int xq_bytes = max_kt * 2 * 4 * 32 * 16;                                  // quantised activations
-    xq_bytes = std::max(xq_bytes, (int)((64 + 32 * 128) * sizeof(float)));       // attention scratch
+    xq_bytes = std::max(xq_bytes, (int)((2 * kAG + kAG * 128) * sizeof(float)));  // attention scratch
     xq_bytes = std::max(xq_bytes, 2 * c.dim);                                 // classifier x
     p.xq_bytes = (int)align_up(xq_bytes, 128);
     p.meta_off = kSlots * kSlotBytes + p.xq_bytes;
@@ -1061,7 +1183,11 @@ int q4_fused_prepare(q4_model* m) {
     Q4_CUDA_TRY(cudaFuncSetAttribute(fused_token_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)f->smem_bytes));
     int per_sm = 0;
     Q4_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_token_kernel, kThreads, f->smem_bytes));
-    if (per_sm < 1) { f->unsupported = true; return Q4_ERR_UNSUPPORTED_SIZE; }
+    if (per_sm < 1) {
+        fprintf(stderr, "q4 fused path: kernel does not fit one SM (%zu B shared memory, %d threads)\n", f->smem_bytes, kThreads);
+        f->unsupported = true;
+        return Q4_ERR_UNSUPPORTED_SIZE;
+    }
     q4_fused_reset(m);
     Q4_CUDA_TRY(cudaDeviceSynchronize());
 #undef FTRY
@@ -1077,6 +1203,8 @@ int q4_fused_forward(q4_model* m, cudaStream_t s, int gen_token) {
     {
         const char* dbg = getenv("Q4_FUSED_DEBUG");
         p.debug = dbg ? atoi(dbg) : 0;
+        const char* la = getenv("Q4_FUSED_L2_AHEAD");
+        p.l2_ahead = la ? atoi(la) : 32;
     }
     p.bar_base = f->launches * (unsigned long long)f->barriers_per_launch;
     f->launches++;

@@ -15,6 +15,7 @@ CONFIGS = {
     "tiny-gqa": (512, 768, 2, 4, 2, 512, 64, 10000.0),
     "mid": (1024, 2816, 2, 8, 8, 2048, 128, 10000.0),      # 22 groups in the down projection: a full and a partial k-tile
     "mid-gqa": (1024, 2816, 2, 8, 2, 2048, 128, 10000.0),
+    "llama2-7b-4l": (4096, 11008, 4, 32, 32, 32000, 2048, 10000.0),  # 7B layer shapes, 4 layers: profiling-sized
     "llama2-7b": (4096, 11008, 32, 32, 32, 32000, 2048, 10000.0),
     "llama2-13b": (5120, 13824, 40, 40, 40, 32000, 2048, 10000.0),
     "llama2-70b": (8192, 28672, 80, 64, 8, 32000, 4096, 10000.0),
