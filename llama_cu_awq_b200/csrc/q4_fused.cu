@@ -36,6 +36,8 @@ constexpr int kSlotGroups = 16;
 constexpr int kUnitBytes = 544;
 constexpr int kSlotBytes = kSlotGroups * kUnitBytes;  // 8704
 constexpr int kSlots = 16;
+constexpr int kEntries = kSlots / 2;               // ring entries: two slots each, filled by one bulk copy
+constexpr int kEntryBytes = 2 * kSlotBytes;
 #ifndef Q4_FUSED_CW
 #define Q4_FUSED_CW 11
 #endif
@@ -113,8 +115,8 @@ __device__ __forceinline__ void mbar_init(uint64_t* b, int count) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* b, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(b)), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ void mbar_arrive(uint64_t* b) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(b)) : "memory");
+__device__ __forceinline__ void mbar_arrive(uint64_t* b, int count) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(b)), "r"(count) : "memory");
 }
 __device__ __forceinline__ bool mbar_try(uint64_t* b, uint32_t parity) {
     uint32_t ok;
@@ -146,9 +148,6 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ void prefetch_l2(const void* src, uint32_t bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
-}
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kCT) : "memory"); }
 __device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {
     int d;
@@ -169,7 +168,7 @@ __device__ __forceinline__ void grid_barrier(const FParams& p, unsigned& nbar, i
         const unsigned long long target = (p.bar_base + nbar) * (unsigned long long)gridDim.x;
         unsigned long long v;
         const int st = *(volatile int*)p.status;  // in flight together with the atomic
-        asm volatile("atom.add.release.gpu.global.u64 %0, [%1], 1;" : "=l"(v) : "l"(p.bar_counter) : "memory");
+        asm volatile("red.release.gpu.global.add.u64 [%0], 1;" ::"l"(p.bar_counter) : "memory");  // no return trip needed
         if (st != 0) *s_abort = 1;
         unsigned spins = 0;
         for (;;) {
@@ -244,48 +243,61 @@ __device__ __forceinline__ void tile_info(const FPhase& ph, int t, int& mi, int&
     rt = t - ph.m[mi].tile0;
 }
 
-// Walks the slots of one CTA in issue order: phase by phase, unit by unit (cta, cta + grid, ...), tile by tile,
-// k-tile by k-tile. The consumers enumerate the same order with plain loops.
+// Units of a phase are dealt to the CTAs round-robin (unit i of CTA c is c + i*grid): at any moment the CTAs stream
+// neighbouring tiles, i.e. one contiguous region spread evenly over the memory channels. (Contiguous per-CTA ranges
+// measured slower: 148 streams 170 KB apart.) The classifier's unit is a pair of rows, 16 KB contiguous.
+__device__ __forceinline__ int unit_count(int nunits, int cta, int grid) { return nunits > cta ? (nunits - cta + grid - 1) / grid : 0; }
+__device__ __forceinline__ int unit_at(int i, int cta, int grid) { return cta + i * grid; }
+
+// Walks the slots of one CTA in issue order: phase by phase, unit by unit, tile by tile, k-tile by k-tile.
+// The consumers enumerate the same order with plain arithmetic.
 struct SlotCursor {
-    int pi, u, tt, kt;
+    int pi, u, u_end, tt, kt;   // u, u_end: index of the unit inside this CTA's list
     int wrapped, count;
     FPhase* cache;   // shared-memory copy of phases[pi] (the table itself lives in global memory)
     int cached_pi;
 };
-__device__ __forceinline__ void cursor_init(SlotCursor& c, int cta) { c.pi = 0; c.u = cta; c.tt = 0; c.kt = 0; c.wrapped = 0; c.count = 0; c.cached_pi = -1; }
+__device__ __forceinline__ void cursor_init(SlotCursor& c) { c.pi = -1; c.u = 0; c.u_end = 0; c.tt = 0; c.kt = 0; c.wrapped = 0; c.count = 0; c.cached_pi = -1; }
 __device__ __forceinline__ void copy_phase(FPhase* dst, const FPhase* src) {
     const int4* s4 = reinterpret_cast<const int4*>(src);
     int4* d4 = reinterpret_cast<int4*>(dst);
 #pragma unroll
     for (int i = 0; i < (int)(sizeof(FPhase) / 16); i++) d4[i] = __ldg(s4 + i);
 }
-__device__ __forceinline__ bool cursor_next(SlotCursor& c, const FParams& p, int cta, int grid, const void*& src, uint32_t& bytes) {
+// Next slot: source address, byte count and the phase it belongs to. False after the last phase.
+__device__ __forceinline__ bool cursor_next(SlotCursor& c, const FParams& p, int cta, int grid, const uint8_t*& src, uint32_t& bytes, int& phase) {
     for (;;) {
-        if (c.pi >= p.nphases) return false;
-        if (c.cached_pi != c.pi) { copy_phase(c.cache, p.phases + c.pi); c.cached_pi = c.pi; }
+        if (c.pi >= 0 && c.u < c.u_end) {
+            const FPhase& ph = *c.cache;
+            phase = c.pi;
+            if (ph.type == PH_GEMV) {
+                int mi, rt;
+                tile_info(ph, unit_at(c.u, cta, grid) * ph.tpu + c.tt, mi, rt);
+                const int ng = min(kSlotGroups, ph.G - c.kt * kSlotGroups);
+                src = ph.m[mi].blocks + ((size_t)rt * ph.G + (size_t)c.kt * kSlotGroups) * kUnitBytes;
+                bytes = ng * kUnitBytes;
+                if (++c.kt == ph.nkt) { c.kt = 0; if (++c.tt == ph.tpu) { c.tt = 0; c.u++; } }
+            } else {  // PH_CLS: unit = 2 rows (tt), row chunks kt
+                const int row = unit_at(c.u, cta, grid) * 2 + c.tt;
+                const int len = min(kClsChunk, ph.K - c.kt * kClsChunk);
+                src = reinterpret_cast<const uint8_t*>(p.wcls + (size_t)row * ph.K + (size_t)c.kt * kClsChunk);
+                bytes = len * 2;
+                if (++c.kt == ph.nkt) { c.kt = 0; if (++c.tt == 2) { c.tt = 0; c.u++; } }
+            }
+            c.count++;
+            return true;
+        }
+        if (++c.pi >= p.nphases) return false;
+        copy_phase(c.cache, p.phases + c.pi);
         const FPhase& ph = *c.cache;
-        if (ph.type == PH_GEMV && c.u < ph.nunits) {
-            int mi, rt;
-            tile_info(ph, c.u * ph.tpu + c.tt, mi, rt);
-            const int ng = min(kSlotGroups, ph.G - c.kt * kSlotGroups);
-            src = ph.m[mi].blocks + ((size_t)rt * ph.G + (size_t)c.kt * kSlotGroups) * kUnitBytes;
-            bytes = ng * kUnitBytes;
-            if (++c.kt == ph.nkt) { c.kt = 0; if (++c.tt == ph.tpu) { c.tt = 0; c.u += grid; } }
-            c.count++;
-            return true;
-        }
-        if (ph.type == PH_CLS && c.u < ph.nunits) {
-            const int len = min(kClsChunk, ph.K - c.kt * kClsChunk);
-            src = p.wcls + (size_t)c.u * ph.K + (size_t)c.kt * kClsChunk;
-            bytes = len * 2;
-            if (++c.kt == ph.nkt) { c.kt = 0; c.u += grid; }
-            c.count++;
-            return true;
-        }
-        c.pi++;
-        c.u = cta;
         c.tt = 0;
         c.kt = 0;
+        if (ph.type == PH_GEMV || ph.type == PH_CLS) {
+            c.u = 0;
+            c.u_end = unit_count(ph.nunits, cta, grid);
+        } else {
+            c.u = c.u_end = 0;
+        }
     }
 }
 
@@ -472,7 +484,7 @@ __device__ __forceinline__ void gemv_slot(const uint8_t* slot, int ng, int kt, c
 // ------------------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ uint64_t full_bar[kSlots], empty_bar[kSlots];
+    __shared__ uint64_t full_bar[kEntries], empty_bar[kEntries];
     __shared__ float red[kCW];
     __shared__ int s_flag, s_abort;
     __shared__ unsigned s_ring_seq;   // slots the ring cursor has issued (read by the L2 cursor)
@@ -491,7 +503,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
     if (tid == 0) {
         s_abort = 0;
         s_ring_seq = 0;
-        for (int s = 0; s < kSlots; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        for (int s = 0; s < kEntries; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 2); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -502,28 +514,31 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
         // p.l2_ahead slots in front of it and only requests the bytes into L2 (fire and forget), so HBM keeps
         // streaming while the ring is full and the consumers sit in a barrier. After the last slot the L2 cursor wraps
         // around: the next token's first slots are already on their way when its kernel starts.
-        if (lane > 1 || (p.debug & 2)) return;
-        const void* src;
+        if (p.debug & 2) return;
+        const uint8_t* src;
         uint32_t bytes;
-        if (lane == 1) {
-            // L2 cursor (own lane, so that a slow prefetch never delays a ring copy)
+        int phase;
+        if (lane != 0) {
+            // L2 cursor: lanes 1..31 walk the same slot list p.l2_ahead slots in front of the ring cursor and request the
+            // bytes into L2 with plain prefetch instructions (the bulk-copy engine is kept for the ring: a bulk
+            // prefetch costs it as much as a copy). After the last slot the cursor wraps once, so the next token's
+            // first slots are already on their way when its kernel starts.
             if (p.l2_ahead <= 0) return;
             SlotCursor c;
-            cursor_init(c, cta);
+            cursor_init(c);
             c.cache = &s_pph[1];
             unsigned issued = 0;
             unsigned long long t0 = 0;
             for (;;) {
-                if (!cursor_next(c, p, cta, grid, src, bytes)) {
-                    if (c.wrapped) return;          // second pass done
-                    cursor_init(c, cta);
+                if (!cursor_next(c, p, cta, grid, src, bytes, phase)) {
+                    if (c.wrapped) return;
+                    cursor_init(c);
                     c.wrapped = 1;
                     continue;
                 }
                 if (c.wrapped && c.count > p.l2_ahead) return;
-                // stay at most l2_ahead slots in front of the ring cursor
                 unsigned spins = 0;
-                while (!c.wrapped && issued >= *(volatile unsigned*)&s_ring_seq + (unsigned)p.l2_ahead) {
+                while (!c.wrapped && issued >= 2u * *(volatile unsigned*)&s_ring_seq + (unsigned)p.l2_ahead) {
                     __nanosleep(200);
                     if ((++spins & 255u) == 0) {
                         const unsigned long long now = global_ns();
@@ -532,29 +547,50 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                     }
                 }
                 t0 = 0;
-                prefetch_l2(src, bytes);
+                for (uint32_t off = (lane - 1) * 128u; off < bytes; off += 31u * 128u)
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(src + off));
                 issued++;
             }
         }
-        SlotCursor ring_c;
-        cursor_init(ring_c, cta);
-        ring_c.cache = &s_pph[0];
-        unsigned seq = 0;
-        while (cursor_next(ring_c, p, cta, grid, src, bytes)) {
-            const int slot = seq % kSlots;
-            if (!mbar_wait(&empty_bar[slot], ((seq / kSlots) & 1) ^ 1, p.status)) return;
-            mbar_expect_tx(&full_bar[slot], bytes);
-            bulk_g2s(ring + slot * kSlotBytes, src, bytes, &full_bar[slot]);
-            seq++;
-            *(volatile unsigned*)&s_ring_seq = seq;
+        // Ring cursor: one entry = two consecutive slots of the same phase (one bulk copy when they are adjacent in memory,
+        // which they are inside a CTA's contiguous share of a matrix). The second slot lands right behind the first.
+        SlotCursor rc;
+        cursor_init(rc);
+        rc.cache = &s_pph[0];
+        unsigned ent = 0;
+        bool have = cursor_next(rc, p, cta, grid, src, bytes, phase);
+        while (have) {
+            const uint8_t* srcA = src;
+            const uint32_t bytesA = bytes;
+            const int phaseA = phase;
+            have = cursor_next(rc, p, cta, grid, src, bytes, phase);
+            const bool pair = have && phase == phaseA;
+            const int e = ent % kEntries;
+            if (!mbar_wait(&empty_bar[e], ((ent / kEntries) & 1) ^ 1, p.status)) return;
+            uint8_t* dst = ring + (size_t)e * kEntryBytes;
+            if (pair) {
+                mbar_expect_tx(&full_bar[e], bytesA + bytes);
+                if (src == srcA + bytesA) {
+                    bulk_g2s(dst, srcA, bytesA + bytes, &full_bar[e]);
+                } else {
+                    bulk_g2s(dst, srcA, bytesA, &full_bar[e]);
+                    bulk_g2s(dst + bytesA, src, bytes, &full_bar[e]);
+                }
+                have = cursor_next(rc, p, cta, grid, src, bytes, phase);
+            } else {
+                mbar_expect_tx(&full_bar[e], bytesA);
+                bulk_g2s(dst, srcA, bytesA, &full_bar[e]);
+            }
+            ent++;
+            *(volatile unsigned*)&s_ring_seq = ent;
         }
-        *(volatile unsigned*)&s_ring_seq = 0x7fffffffu;
+        *(volatile unsigned*)&s_ring_seq = 0x3fffffffu;
         return;
     }
 
     // ================= consumers =================
     const int ctid = tid - 32, cw = warp - 1;
-    unsigned seq = 0, nbar = 0;
+    unsigned sbase = 0, ent0 = 0, nbar = 0;   // slots and ring entries consumed by earlier phases
     bool failed = false;  // a bounded wait ran out: skip the remaining slots, keep taking part in the barriers
     const int pos = *p.pos_dev;
     const int HS = p.head_size;
@@ -585,27 +621,30 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
             // old value of the residual stream for this thread's first epilogue element: requested now, used after the slots
             __half resid = __float2half(0.f);
             if (ph.epi == EPI_RESIDUAL) {
-                const int u = cta + (ctid >> 3) * grid;
-                if (u < ph.nunits) resid = __ldcg(ph.m[0].out + u * 8 + (ctid & 7));
+                if ((ctid >> 3) < unit_count(ph.nunits, cta, grid)) resid = __ldcg(ph.m[0].out + unit_at(ctid >> 3, cta, grid) * 8 + (ctid & 7));
             }
             // slots of this CTA, in the producer's order; slot i belongs to consumer warp i % kCW.
             // Phase constants live in registers: the descriptor is not re-read inside the loops.
             const int nunits = ph.nunits, tpu = ph.tpu, nkt = ph.nkt, G = ph.G, dbg = p.debug;
-            const int my_units = nunits > cta ? (nunits - cta + grid - 1) / grid : 0;
+            const int my_units = unit_count(nunits, cta, grid);
             const int ntl = my_units * tpu, nslots = ntl * nkt;
             {
-                const unsigned first = seq + ((cw + kCW - (seq % kCW)) % kCW);  // first slot of this warp in the phase
-                for (unsigned sq = first; sq < seq + nslots; sq += kCW) {
-                    const int li = (int)(sq - seq);          // slot index inside the phase = lt * nkt + kt
+                const unsigned first = (cw + kCW - (sbase % kCW)) % kCW;  // first slot of this warp in the phase
+                for (unsigned li = first; li < (unsigned)nslots; li += kCW) {   // li = lt * nkt + kt
                     const int kt = li % nkt;
                     const int ng = min(kSlotGroups, G - kt * kSlotGroups);
-                    const int slot = sq % kSlots;
-                    if (!(dbg & 2) && (failed || !mbar_wait(&full_bar[slot], (sq / kSlots) & 1, p.status))) { failed = true; continue; }
-                    if (!(dbg & 1)) gemv_slot(ring + slot * kSlotBytes, ng, kt, xq, xs_scale, xs_sum, part + (size_t)li * 8, lane);
+                    const unsigned en = ent0 + (li >> 1);
+                    const int e = en % kEntries;
+                    int off = 0;
+                    if (li & 1) { const int ktp = (li - 1) % nkt; off = min(kSlotGroups, G - ktp * kSlotGroups) * kUnitBytes; }
+                    if (!(dbg & 2) && (failed || !mbar_wait(&full_bar[e], (en / kEntries) & 1, p.status))) { failed = true; continue; }
+                    if (!(dbg & 1)) gemv_slot(ring + (size_t)e * kEntryBytes + off, ng, kt, xq, xs_scale, xs_sum, part + (size_t)li * 8, lane);
                     __syncwarp();
-                    if (lane == 0 && !(dbg & 2)) mbar_arrive(&empty_bar[slot]);
+                    // an entry is released by its two slots; a phase's odd last slot releases it alone
+                    if (lane == 0 && !(dbg & 2)) mbar_arrive(&empty_bar[e], (!(li & 1) && li + 1 == (unsigned)nslots) ? 2 : 1);
                 }
-                seq += nslots;
+                sbase += nslots;
+                ent0 += (nslots + 1) >> 1;
             }
             consumer_sync();
             TRACE(2);
@@ -613,7 +652,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
             const int epi = ph.epi;
             for (int e = ctid; e < ntl * 8; e += kCT) {
                 const int l2 = e >> 3, r = e & 7;
-                const int u = cta + (l2 / tpu) * grid;
+                const int u = unit_at(l2 / tpu, cta, grid);
                 int mi, rt;
                 tile_info(ph, u * tpu + (l2 % tpu), mi, rt);
                 float sum = 0.f;
@@ -815,16 +854,19 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
             stage_x_f16(ph, xf, red, ctid);
             TRACE(1);
             const int nunits = ph.nunits, nkt = ph.nkt, K = ph.K;
-            const int lt = nunits > cta ? (nunits - cta + grid - 1) / grid : 0;  // rows of this CTA
+            const int lt = unit_count(nunits, cta, grid) * 2;        // rows of this CTA (units are row pairs)
             const int nslots = lt * nkt;
-            const unsigned first = seq + ((cw + kCW - (seq % kCW)) % kCW);
-            for (unsigned sq = first; sq < seq + nslots; sq += kCW) {
+            const unsigned first = (cw + kCW - (sbase % kCW)) % kCW;
+            for (unsigned li = first; li < (unsigned)nslots; li += kCW) {
                 {
-                    const int li = (int)(sq - seq), kc = li % nkt;
+                    const int kc = li % nkt;
                     const int len = min(kClsChunk, K - kc * kClsChunk);
-                    const int slot = sq % kSlots;
-                    if (!(p.debug & 2) && (failed || !mbar_wait(&full_bar[slot], (sq / kSlots) & 1, p.status))) { failed = true; continue; }
-                    const uint4* wv = reinterpret_cast<const uint4*>(ring + slot * kSlotBytes);
+                    const unsigned en = ent0 + (li >> 1);
+                    const int e = en % kEntries;
+                    int off = 0;
+                    if (li & 1) { const int kcp = (li - 1) % nkt; off = min(kClsChunk, K - kcp * kClsChunk) * 2; }
+                    if (!(p.debug & 2) && (failed || !mbar_wait(&full_bar[e], (en / kEntries) & 1, p.status))) { failed = true; continue; }
+                    const uint4* wv = reinterpret_cast<const uint4*>(ring + (size_t)e * kEntryBytes + off);
                     const uint4* xv = reinterpret_cast<const uint4*>(xf + kc * kClsChunk);
                     float a4[8];
 #pragma unroll
@@ -850,17 +892,18 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                     a = warp_sum(a);
                     if (lane == 0) part[li] = a;
                     __syncwarp();
-                    if (lane == 0 && !(p.debug & 2)) mbar_arrive(&empty_bar[slot]);
+                    if (lane == 0 && !(p.debug & 2)) mbar_arrive(&empty_bar[e], (!(li & 1) && li + 1 == (unsigned)nslots) ? 2 : 1);
                 }
             }
-            seq += nslots;
+            sbase += nslots;
+            ent0 += (nslots + 1) >> 1;
             consumer_sync();
             float best = -CUDART_INF_F;
             int bi = 0x7fffffff;
             for (int e = ctid; e < lt; e += kCT) {
                 float sum = 0.f;
                 for (int kc = 0; kc < nkt; kc++) sum += part[e * nkt + kc];
-                const int n = cta + e * grid;
+                const int n = unit_at(e >> 1, cta, grid) * 2 + (e & 1);
                 const __half hv = __float2half(sum);
                 p.logits[n] = hv;
                 const float v = __half2float(hv);
@@ -1150,8 +1193,8 @@ int q4_fused_prepare(q4_model* m) {
         a.nkt = q4_div_up(c.dim, kClsChunk);
         a.xin = p.x;
         a.norm_w = (const __half*)m->rms_final;
-        a.nunits = m->v_n;
-        max_part = std::max(max_part, q4_div_up(a.nunits, sms) * a.nkt);
+        a.nunits = m->v_n / 2;  // row pairs
+        max_part = std::max(max_part, q4_div_up(a.nunits, sms) * 2 * a.nkt);
         ph.push_back(a);
         nbar++;
         FPhase b;
@@ -1204,7 +1247,7 @@ int q4_fused_forward(q4_model* m, cudaStream_t s, int gen_token) {
         const char* dbg = getenv("Q4_FUSED_DEBUG");
         p.debug = dbg ? atoi(dbg) : 0;
         const char* la = getenv("Q4_FUSED_L2_AHEAD");
-        p.l2_ahead = la ? atoi(la) : 32;
+        p.l2_ahead = la ? atoi(la) : 0;  // measured: requesting weights into L2 ahead of the ring slows the stream down
     }
     p.bar_base = f->launches * (unsigned long long)f->barriers_per_launch;
     f->launches++;
