@@ -105,6 +105,21 @@ int q4_attention(void* stream, uint16_t* output, const uint16_t* q, const uint16
                  const uint16_t* value_cache, void* scratch, int num_heads, int head_size, int kv_mul, int max_seq_len,
                  const int* pPos);
 
+/* Same computation as q4_attention for callers that cannot provide the scratch buffer because they may not
+ * allocate device memory: hosts whose device memory is completely handed out at start-up, or plugins that only
+ * receive the owning runtime's pointers. No counterpart in the reference (its `att` buffer is allocated by
+ * malloc_run_state). The partial results go to an array of Q4_ATTENTION_STATIC_MAX_BYTES that is part of the
+ * library's device image (every GPU that loads the library holds it until the process exits); shapes that need
+ * more (q4_attention_scratch_bytes) are refused with Q4_ERR_LIMIT. The call allocates and frees nothing.
+ * The first call on each device looks the array's device address up (cudaGetSymbolAddress); make that first call
+ * outside of any stream capture. All calls share the one array: two calls that overlap on the GPU (different
+ * streams) race; calls on one stream are safe. Nothing has to be cleared between calls: each call overwrites
+ * every word it later reads. */
+#define Q4_ATTENTION_STATIC_MAX_BYTES (256 * 1024)
+int q4_attention_static(void* stream, uint16_t* output, const uint16_t* q, const uint16_t* key_cache,
+                        const uint16_t* value_cache, int num_heads, int head_size, int kv_mul, int max_seq_len,
+                        const int* pPos);
+
 /* matmul(half*): llama2_q4.cu:357-365, kernel gpu_kernels.h:117-147. fp16 GEMV used for the classifier:
  * xout[d] = alpha * sum_n w[d][n] * x[n]. n and d must be multiples of 8. */
 int q4_matmul_f16(void* stream, uint16_t* xout, const uint16_t* x, const uint16_t* w, int n, int d, float alpha);

@@ -57,6 +57,7 @@ SIGNATURES = {
     "q4_rope": (_I, [_P, _P, _P, _I, _I, _I, _P, _I, C.c_float]),
     "q4_attention_scratch_bytes": (C.c_size_t, [_I, _I]),
     "q4_attention": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
+    "q4_attention_static": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "q4_matmul_f16": (_I, [_P, _P, _P, _P, _I, _I, C.c_float]),
     "q4_embed": (_I, [_P, _P, _P, _I, _P, _P]),
     "q4_argmax": (_I, [_P, _P, _I, _P, _P, _P, _I]),

@@ -12,6 +12,10 @@
 // The sequence length comes from *pPos on the device; the grid does not depend on it.
 #include <math_constants.h>
 
+#include <stdio.h>
+
+#include <mutex>
+
 #include "q4_common.cuh"
 
 namespace {
@@ -186,4 +190,50 @@ extern "C" int q4_attention(void* stream, uint16_t* output, const uint16_t* q, c
         return Q4_ERR_INVALID;
     if (head_size > kMaxHeadSize) return Q4_ERR_UNSUPPORTED_SIZE;
     return q4_attention_launch((cudaStream_t)stream, output, q, key_cache, value_cache, (float*)scratch, num_heads, head_size, kv_mul, pPos);
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// Attention without a caller-provided scratch buffer.
+//
+// Some hosts of this library hand it nothing but the reference's own buffers and may not allocate device memory
+// themselves: a serving process whose device memory is fully committed to weights and KV cache at start-up (the
+// reference allocates everything once, in malloc_run_state), or a plugin that only receives raw pointers from
+// the runtime that owns the memory. For them the split partial results live in a fixed array inside the
+// library's own device image instead. Every GPU that loads the library carries the array until the process ends.
+// ------------------------------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_attention_static_scratch[Q4_ATTENTION_STATIC_MAX_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+float* g_static_ptr[kMaxDevices];  // device address of the array, per device (the symbol itself is not an address on the host)
+
+int static_scratch(float** out) {
+    int dev = 0;
+    Q4_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return Q4_ERR_LIMIT;
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    if (!g_static_ptr[dev]) {
+        void* p = nullptr;
+        Q4_CUDA_TRY(cudaGetSymbolAddress(&p, g_attention_static_scratch));
+        g_static_ptr[dev] = reinterpret_cast<float*>(p);
+    }
+    *out = g_static_ptr[dev];
+    return Q4_OK;
+}
+}  // namespace
+
+extern "C" int q4_attention_static(void* stream, uint16_t* output, const uint16_t* q, const uint16_t* key_cache,
+                                   const uint16_t* value_cache, int num_heads, int head_size, int kv_mul, int max_seq_len, const int* pPos) {
+    (void)max_seq_len;
+    if (!output || !q || !key_cache || !value_cache || !pPos || num_heads <= 0 || kv_mul <= 0 || num_heads % kv_mul) return Q4_ERR_INVALID;
+    if (head_size > kMaxHeadSize) return Q4_ERR_UNSUPPORTED_SIZE;
+    if (q4_attention_scratch_bytes(num_heads, head_size) > (size_t)Q4_ATTENTION_STATIC_MAX_BYTES) {
+        fprintf(stderr, "q4_attention_static: %d heads of size %d need %zu bytes of scratch, the built-in array holds %d\n", num_heads, head_size,
+                q4_attention_scratch_bytes(num_heads, head_size), Q4_ATTENTION_STATIC_MAX_BYTES);
+        return Q4_ERR_LIMIT;
+    }
+    float* scratch = nullptr;
+    if (int e = static_scratch(&scratch)) return e;
+    return q4_attention_launch((cudaStream_t)stream, output, q, key_cache, value_cache, scratch, num_heads, head_size, kv_mul, pPos);
 }
