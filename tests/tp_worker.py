@@ -1,0 +1,70 @@
+"""Worker of the tensor-parallel GPU test: launched by torchrun, one rank per GPU (see test_tp_gpu.py).
+Loads a synthetic model sharded Megatron-style over the ranks, teacher-forces a token sequence and checks the
+logits against the single-GPU oracle; all ranks must hold bit-identical logits (fixed-order fp32 all-reduce)."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+from llama_cu_awq_b200 import _lib, synth  # noqa: E402
+from llama_cu_awq_b200.comm import ProcessComm  # noqa: E402
+from llama_cu_awq_b200.model import Transformer  # noqa: E402
+
+
+def main():
+    cfg_name, path, fwd_path = sys.argv[1], sys.argv[2], int(sys.argv[3])
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    comm = ProcessComm(rank, world, dist)
+    t = Transformer(path, rank=rank, gpu_count=world, tp_mode=_lib.Q4_TP_HYBRID, comm=comm.handle)
+    vocab = synth.CONFIGS[cfg_name][5]
+    tokens = np.random.default_rng(0).integers(3, vocab, size=24, dtype=np.int32)
+    t.reset(tokens, 0)
+    dist.barrier()
+    torch.cuda.synchronize()
+    logits = []
+    for pos in range(len(tokens)):
+        t.forward(gen_token=False, path=fwd_path)
+        t.synchronize()
+        logits.append(t.logits())
+    assert t.status() == 0 and comm.status() == 0
+    mine = torch.from_numpy(np.stack(logits).view(np.int16).astype(np.int32)).cuda()
+    gathered = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(gathered, mine)
+    ok = 1
+    if rank == 0:
+        from oracle import q4_oracle as O
+        for r in range(1, world):
+            if not torch.equal(gathered[0], gathered[r]):
+                print(f"rank {r} logits differ from rank 0")
+                ok = 0
+        m = O.Model(open(path, "rb").read())
+        worst = 0.0
+        for pos, tok in enumerate(tokens):
+            m.forward(int(tok), pos, order=1)
+            ref = m.logits().astype(np.float64)
+            got = logits[pos].astype(np.float64)
+            err = np.abs(got - ref).max() / np.abs(ref).max()
+            cos = got @ ref / (np.linalg.norm(got) * np.linalg.norm(ref))
+            worst = max(worst, err)
+            if err > 1e-2 or cos < 0.999:
+                print(f"pos {pos}: rel err {err:.3e} cos {cos:.6f}")
+                ok = 0
+        print(f"TP{world} {cfg_name}: worst rel err vs single-GPU oracle {worst:.3e}; ranks identical: {bool(ok)}")
+    flag = torch.tensor([ok], device="cuda")
+    dist.broadcast(flag, 0)
+    t.close()
+    comm.close()
+    dist.barrier()
+    dist.destroy_process_group()
+    sys.exit(0 if int(flag.item()) == 1 else 1)
+
+
+if __name__ == "__main__":
+    main()
