@@ -547,8 +547,16 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                     }
                 }
                 t0 = 0;
-                for (uint32_t off = (lane - 1) * 128u; off < bytes; off += 31u * 128u)
-                    asm volatile("prefetch.global.L2 [%0];" ::"l"(src + off));
+                if (p.debug & 4) {
+                    // experiment: real loads (cannot be dropped) instead of prefetch hints
+                    for (uint32_t off = (lane - 1) * 16u; off < bytes; off += 31u * 16u) {
+                        uint32_t a, b, c2, d;
+                        asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a), "=r"(b), "=r"(c2), "=r"(d) : "l"(src + off));
+                    }
+                } else {
+                    for (uint32_t off = (lane - 1) * 128u; off < bytes; off += 31u * 128u)
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(src + off));
+                }
                 issued++;
             }
         }
