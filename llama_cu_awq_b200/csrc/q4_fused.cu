@@ -46,6 +46,9 @@ constexpr int kCT = kCW * 32;          // consumer threads
 constexpr int kAG = kCT / 8;           // attention lane groups (positions in flight per CTA)
 static_assert(kCT % 16 == 0, "activation staging maps 16 consecutive threads to one group of 128 inputs");
 constexpr int kThreads = 32 + kCT;     // + producer warp
+constexpr int kSplitLen = 48;          // positions per attention split before a head is split further (about one step of a CTA)
+constexpr int kMaxSplit = 4;           // attention splits per head (merged in registers by the next phase)
+constexpr int kAttnPartStride = 64 + 4;   // 4-byte words per partial: acc[128] as fp16 (normalised by the split's own sum), max, sum, 2 pad
 constexpr int kClsChunk = 4096;        // halfs of one classifier row per slot (8192 B)
 constexpr unsigned kPollLimit = 1u << 26;                        // polls, and
 constexpr unsigned long long kWaitLimitNs = 2000ULL * 1000 * 1000;  // two seconds on the global timer, whichever comes first
@@ -73,7 +76,8 @@ struct FPhase {
     int epi;
     long long loff;         // KV cache layer offset (halfs)
     int layer;
-    int pad_[3];
+    int attn_in;            // GEMV: the input vector is the attention output, still split: merge the partials while staging
+    int pad_[2];
 };
 static_assert(sizeof(FPhase) % 16 == 0, "FPhase is copied in 16-byte pieces");
 
@@ -100,6 +104,7 @@ struct FParams {
     int write_token;
     int debug;                   // measurement only: 1 = consumers skip the GEMV math (pure streaming), 2 = no streaming (pure math)
     int l2_ahead;                // slots each producer keeps requested into L2 beyond the ring
+    int split_len;               // positions per attention split (a head is split in ceil(T / split_len) parts, at most nsplit)
     unsigned long long* trace;   // optional: [2 CTAs][nphases][4] device timestamps (ns), or null
     // shared memory carve-up (bytes)
     int xq_bytes, meta_off, part_off, part_floats;
@@ -308,10 +313,109 @@ __device__ __forceinline__ bool cursor_next(SlotCursor& c, const FParams& p, int
 // nibbles, .z/.w = low digit. xs_scale[kt*32 + lane] = sx of the group, xs_sum[kt*32 + lane] = sum X over the
 // lane's 64 inputs.
 // ------------------------------------------------------------------------------------------------------------
-__device__ void stage_x_quant(const FPhase& ph, uint4* xq, float* xs_scale, int* xs_sum, float* red, int ctid) {
+// One word (8 consecutive elements) of the attention output from the per-split partials (max, sum, un-normalised V sum):
+// all splits' loads are issued together, merged in fixed split order, normalised and rounded to fp16 like the
+// reference's attention output (gpu_kernels.h:335-336).
+struct AttnWord {
+    uint4 a[kMaxSplit];      // 8 fp16 values of the split's normalised output
+    float2 ml[kMaxSplit];
+};
+__device__ __forceinline__ void attn_word_load(AttnWord& w, const FParams& p, int ns, int wd, bool valid) {
+    const int h = (wd * 8) / 128, d = (wd * 8) % 128;
+#pragma unroll
+    for (int s = 0; s < kMaxSplit; s++) {
+        w.ml[s] = make_float2(-CUDART_INF_F, 0.f);
+        w.a[s] = make_uint4(0, 0, 0, 0);
+        if (valid && s < ns) {
+            const float* base = p.attn_part + ((size_t)h * ns + s) * kAttnPartStride;
+            w.a[s] = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(base) + d));
+            w.ml[s] = __ldcg(reinterpret_cast<const float2*>(base + 64));
+        }
+    }
+}
+__device__ __forceinline__ void attn_word_merge(const AttnWord& w, float (&v)[8]) {
+    float M = -CUDART_INF_F;
+#pragma unroll
+    for (int s = 0; s < kMaxSplit; s++) M = fmaxf(M, w.ml[s].x);
+    float L = 0.f, a[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) a[j] = 0.f;
+#pragma unroll
+    for (int s = 0; s < kMaxSplit; s++) {
+        if (w.ml[s].x != -CUDART_INF_F) {
+            const float e = w.ml[s].y * expf(w.ml[s].x - M);  // weight of the split = its sum, rescaled to the common max
+            L += e;
+            const __half2* hh = reinterpret_cast<const __half2*>(&w.a[s]);
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const float2 f = __half22float2(hh[j]);
+                a[2 * j] += f.x * e;
+                a[2 * j + 1] += f.y * e;
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; j++) v[j] = L > 0.f ? __half2float(__float2half(a[j] / L)) : 0.f;
+}
+
+// Quantises one word's eight values (already fp16-representable floats) and files it in xq / xs_*.
+__device__ __forceinline__ void quant_word(const float (&v)[8], int wd, int nwords, uint4* xq, float* xs_scale, int* xs_sum) {
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; j++) amax = fmaxf(amax, fabsf(v[j]));
+#pragma unroll
+    for (int o = 1; o < 16; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));  // 16 words = 1 group
+    const float sx = amax * (1.0f / 16256.0f);
+    const float inv = amax > 0.f ? 16256.0f / amax : 0.f;
+    uint32_t he = 0, ho = 0, le = 0, lo = 0;
+    int sum = 0;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const int X = __float2int_rn(v[j] * inv);
+        sum += X;
+        const int hi = (X + 64) >> 7;
+        const int low = X - (hi << 7);
+        const uint32_t hb = (uint32_t)hi & 0xFFu, lb = (uint32_t)low & 0xFFu;
+        if (j & 1) { ho |= hb << (8 * (j >> 1)); lo |= lb << (8 * (j >> 1)); }
+        else       { he |= hb << (8 * (j >> 1)); le |= lb << (8 * (j >> 1)); }
+    }
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 4);  // 8 words = the 64 inputs of one (group, half)
+    if (wd < nwords) {
+        const int g = wd >> 4, c = (wd >> 2) & 3, wi = wd & 3;
+        const int kt = g >> 4, lane = 2 * (g & 15) + (c >> 1), j2 = c & 1;
+        xq[((kt * 2 + j2) * 4 + wi) * 32 + lane] = make_uint4(he, ho, le, lo);
+        if ((wd & 7) == 0) { xs_scale[kt * 32 + lane] = sx; xs_sum[kt * 32 + lane] = sum; }
+    }
+}
+
+// Splits per head at sequence length T: short contexts are not split at all (one CTA per head, no partial traffic).
+__device__ __forceinline__ int attn_splits_for(const FParams& p, int T) { return min(p.nsplit, max(1, (T + p.split_len - 1) / p.split_len)); }
+
+__device__ void stage_x_quant(const FPhase& ph, const FParams& p, int pos, uint4* xq, float* xs_scale, int* xs_sum, float* red, int ctid) {
     constexpr int kBatch = 8;  // words per thread whose loads are in flight together (one L2 round trip per batch)
     const int K = ph.K, nwords = ph.G * 16;
     const int iters = (nwords + kCT - 1) / kCT;
+    if (ph.attn_in) {
+        const int ns = attn_splits_for(p, pos + 1);
+        // two words per thread in flight (all splits of both): one L2 round trip for K <= 2 * kCT * 8
+        for (int it0 = 0; it0 < iters; it0 += 2) {
+            AttnWord w0, w1;
+            const int wd0 = ctid + it0 * kCT, wd1 = wd0 + kCT;
+            attn_word_load(w0, p, ns, wd0, wd0 < nwords && wd0 * 8 < K);
+            attn_word_load(w1, p, ns, wd1, it0 + 1 < iters && wd1 < nwords && wd1 * 8 < K);
+            float v[8];
+            attn_word_merge(w0, v);
+            quant_word(v, wd0, nwords, xq, xs_scale, xs_sum);
+            if (it0 + 1 < iters) {
+                attn_word_merge(w1, v);
+                quant_word(v, wd1, nwords, xq, xs_scale, xs_sum);
+            }
+        }
+        consumer_sync();
+        return;
+    }
     float inv_rms = 1.f;
     for (int it0 = 0; it0 < iters; it0 += kBatch) {
         uint4 xv[kBatch], wv[kBatch];
@@ -361,34 +465,7 @@ __device__ void stage_x_quant(const FPhase& ph, uint4* xq, float* xs_scale, int*
 #pragma unroll
                     for (int j = 0; j < 8; j++) v[j] = __half2float(xh[j]);
                 }
-                float amax = 0.f;
-#pragma unroll
-                for (int j = 0; j < 8; j++) amax = fmaxf(amax, fabsf(v[j]));
-#pragma unroll
-                for (int o = 1; o < 16; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));  // 16 words = 1 group
-                const float sx = amax * (1.0f / 16256.0f);
-                const float inv = amax > 0.f ? 16256.0f / amax : 0.f;
-                uint32_t he = 0, ho = 0, le = 0, lo = 0;
-                int sum = 0;
-#pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    const int X = __float2int_rn(v[j] * inv);
-                    sum += X;
-                    const int hi = (X + 64) >> 7;
-                    const int low = X - (hi << 7);
-                    const uint32_t hb = (uint32_t)hi & 0xFFu, lb = (uint32_t)low & 0xFFu;
-                    if (j & 1) { ho |= hb << (8 * (j >> 1)); lo |= lb << (8 * (j >> 1)); }
-                    else       { he |= hb << (8 * (j >> 1)); le |= lb << (8 * (j >> 1)); }
-                }
-                sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-                sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-                sum += __shfl_xor_sync(0xffffffffu, sum, 4);  // 8 words = the 64 inputs of one (group, half)
-                if (wd < nwords) {
-                    const int g = wd >> 4, c = (wd >> 2) & 3, wi = wd & 3;
-                    const int kt = g >> 4, lane = 2 * (g & 15) + (c >> 1), j2 = c & 1;
-                    xq[((kt * 2 + j2) * 4 + wi) * 32 + lane] = make_uint4(he, ho, le, lo);
-                    if ((wd & 7) == 0) { xs_scale[kt * 32 + lane] = sx; xs_sum[kt * 32 + lane] = sum; }
-                }
+                quant_word(v, wd, nwords, xq, xs_scale, xs_sum);
             }
         }
     }
@@ -624,7 +701,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
             grid_barrier(p, nbar, ctid, &s_abort);
 
         } else if (ph.type == PH_GEMV) {
-            stage_x_quant(ph, xq, xs_scale, xs_sum, red, ctid);
+            stage_x_quant(ph, p, pos, xq, xs_scale, xs_sum, red, ctid);
             TRACE(1);
             // old value of the residual stream for this thread's first epilogue element: requested now, used after the slots
             __half resid = __float2half(0.f);
@@ -694,7 +771,8 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
             const int i0 = upper ? d0 - 64 : d0;
             const int T = pos + 1;
             const float alpha = (float)(1.0 / sqrt((double)HS));
-            const int nitems = p.n_heads * p.nsplit;
+            const int ns = attn_splits_for(p, T);
+            const int nitems = p.n_heads * ns;
             const __half* kc = p.kc + ph.loff;
             const __half* vc = p.vc + ph.loff;
             // (cos, sin) of this position for dims i0..i0+15: RoPE of gpu_kernels.h:340-363, tabulated at load time
@@ -709,10 +787,10 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                 }
             }
             for (int id = cta; id < nitems; id += grid) {
-                const int h = id / p.nsplit, split = id % p.nsplit;
+                const int h = id / ns, split = id % ns;
                 const int kvh = h / p.kv_mul;
                 const int units = (T + kAG - 1) / kAG;
-                const int u0 = (int)((long long)units * split / p.nsplit), u1 = (int)((long long)units * (split + 1) / p.nsplit);
+                const int u0 = (int)((long long)units * split / ns), u1 = (int)((long long)units * (split + 1) / ns);
                 const int t0 = u0 * kAG, t1 = min(u1 * kAG, T);
                 const size_t col = (size_t)kvh * HS + d0;
                 // first step's K/V rows are requested before anything else so that their latency overlaps the query set-up
@@ -804,12 +882,13 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                         m = mn;
                     }
                 }
-                // merge the 32 lane groups of this CTA
+                // merge the lane groups of this CTA; the splits of a head are merged by the consumers of the o projection
+                // while they stage their input (stage_x_quant, attn_in), so no second grid-wide step is needed here
                 if (lane8 == 0) { sm_m[grp] = m; sm_l[grp] = l; }
 #pragma unroll
                 for (int j = 0; j < 16; j++) sm_acc[grp * 128 + d0 + j] = acc[j];
                 consumer_sync();
-                float* outp = p.attn_part + (size_t)id * (HS + 2);
+                float* outp = p.attn_part + (size_t)id * kAttnPartStride;
                 if (ctid < HS) {
                     float M = -CUDART_INF_F;
                     for (int g2 = 0; g2 < kAG; g2++) M = fmaxf(M, sm_m[g2]);
@@ -821,34 +900,9 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                             L += sm_l[g2] * w;
                         }
                     }
-                    outp[2 + ctid] = a;
-                    if (ctid == 0) { outp[0] = M; outp[1] = L; }
-                }
-                consumer_sync();  // the partial is complete before thread 0 publishes it (release below)
-                if (ctid == 0) {
-                    unsigned old;
-                    asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(old) : "l"(p.attn_cnt + h) : "memory");
-                    s_flag = (old == (unsigned)p.nsplit - 1);
-                    if (s_flag) p.attn_cnt[h] = 0;
-                }
-                consumer_sync();
-                if (s_flag) {
-                    // last split of this head to finish: merge all splits (fixed order -> deterministic)
-                    const float* base = p.attn_part + (size_t)h * p.nsplit * (HS + 2);
-                    if (ctid < HS) {
-                        float M2 = -CUDART_INF_F;
-                        for (int s2 = 0; s2 < p.nsplit; s2++) M2 = fmaxf(M2, __ldcg(base + (size_t)s2 * (HS + 2)));
-                        float a = 0.f, L = 0.f;
-                        for (int s2 = 0; s2 < p.nsplit; s2++) {
-                            const float ms = __ldcg(base + (size_t)s2 * (HS + 2));
-                            if (ms != -CUDART_INF_F) {
-                                const float w = expf(ms - M2);
-                                a += __ldcg(base + (size_t)s2 * (HS + 2) + 2 + ctid) * w;
-                                L += __ldcg(base + (size_t)s2 * (HS + 2) + 1) * w;
-                            }
-                        }
-                        p.xb[(size_t)h * HS + ctid] = __float2half(a / L);
-                    }
+                    // the split's own softmax-weighted V average (|.| <= max |V|, safe in fp16) plus its (max, sum)
+                    reinterpret_cast<__half*>(outp)[ctid] = __float2half(L > 0.f ? a / L : 0.f);
+                    if (ctid == 0) { outp[64] = M; outp[65] = L; }
                 }
                 consumer_sync();
             }
@@ -1089,7 +1143,7 @@ int q4_fused_prepare(q4_model* m) {
     p.kv_n = m->kv_n;
     p.kv_mul = m->kv_mul;
     p.n_heads = c.n_heads;
-    p.nsplit = std::max(1, sms / c.n_heads);
+    p.nsplit = std::min(kMaxSplit, std::max(1, sms / c.n_heads));
     p.gpu_count = 1.f;
     p.x = (__half*)m->x; p.xb = (__half*)m->xb; p.hb = (__half*)m->hb; p.q = (__half*)m->q; p.logits = (__half*)m->logits;
     p.kc = (__half*)m->kc; p.vc = (__half*)m->vc;
@@ -1100,7 +1154,7 @@ int q4_fused_prepare(q4_model* m) {
     int e;
 #define FTRY(expr) do { e = (expr); if (e != Q4_OK) return e; } while (0)
     FTRY(fused_alloc(f, (void**)&p.knew, 2 * (size_t)m->kv_n));
-    FTRY(fused_alloc(f, (void**)&p.attn_part, sizeof(float) * (size_t)c.n_heads * p.nsplit * (m->head_size + 2)));
+    FTRY(fused_alloc(f, (void**)&p.attn_part, sizeof(float) * (size_t)c.n_heads * p.nsplit * kAttnPartStride));
     FTRY(fused_alloc(f, (void**)&p.attn_cnt, sizeof(unsigned) * c.n_heads));
     {
         float2* rope = nullptr;
@@ -1171,6 +1225,7 @@ int q4_fused_prepare(q4_model* m) {
         }
         {   // O projection + residual
             FPhase a = gemv_phase(m->o_kc, p.xb, nullptr, EPI_RESIDUAL);
+            a.attn_in = 1;
             a.nmat = 1;
             a.m[0] = FMat{so, p.x, c.dim, 0, 0};
             a.nunits = c.dim / 8;
@@ -1255,6 +1310,8 @@ int q4_fused_forward(q4_model* m, cudaStream_t s, int gen_token) {
         const char* dbg = getenv("Q4_FUSED_DEBUG");
         p.debug = dbg ? atoi(dbg) : 0;
         const char* la = getenv("Q4_FUSED_L2_AHEAD");
+        const char* sl = getenv("Q4_FUSED_SPLIT_LEN");  // tuning / test knob
+        p.split_len = (sl && atoi(sl) > 0) ? atoi(sl) : kSplitLen;
         p.l2_ahead = la ? atoi(la) : 0;  // measured: requesting weights into L2 ahead of the ring slows the stream down
     }
     p.bar_base = f->launches * (unsigned long long)f->barriers_per_launch;

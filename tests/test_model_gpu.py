@@ -100,6 +100,15 @@ def test_greedy_argmax_on_identical_logits(tiny_path, fwd_path):
     t.close()
 
 
+def test_fused_attention_splits(mid_gqa_path, monkeypatch):
+    """Heads split over several CTAs (long contexts): forced here with a tiny split length."""
+    monkeypatch.setenv("Q4_FUSED_SPLIT_LEN", "8")
+    tokens = np.random.default_rng(9).integers(3, 2048, size=60, dtype=np.int32)
+    got, ref = teacher_forced(mid_gqa_path, tokens, 2)
+    for pos in (0, 7, 8, 9, 23, 24, 25, 40, 59):
+        assert_close(got[pos], ref[pos], f"split attention, pos {pos}")
+
+
 def test_fused_and_graph_paths_share_the_kv_cache(mid_path):
     """Both paths file rotated keys and values in the same cache layout: switching paths mid-sequence works."""
     tokens = np.random.default_rng(5).integers(3, 2048, size=24, dtype=np.int32)
