@@ -49,6 +49,7 @@ constexpr int kThreads = 32 + kCT;     // + producer warp
 constexpr int kSplitLen = 48;          // positions per attention split before a head is split further (about one step of a CTA)
 constexpr int kMaxSplit = 4;           // attention splits per head (merged in registers by the next phase)
 constexpr int kAttnPartStride = 64 + 4;   // 4-byte words per partial: acc[128] as fp16 (normalised by the split's own sum), max, sum, 2 pad
+constexpr int kTraceCols = 8;           // timestamps per phase: 0 start, 1 inputs staged, 2 weights consumed, 3 barrier passed, 4-7 staging detail
 constexpr int kClsChunk = 4096;        // halfs of one classifier row per slot (8192 B)
 constexpr unsigned kPollLimit = 1u << 26;                        // polls, and
 constexpr unsigned long long kWaitLimitNs = 2000ULL * 1000 * 1000;  // two seconds on the global timer, whichever comes first
@@ -77,7 +78,10 @@ struct FPhase {
     long long loff;         // KV cache layer offset (halfs)
     int layer;
     int attn_in;            // GEMV: the input vector is the attention output, still split: merge the partials while staging
-    int pad_[2];
+    int next_norm_n;        // elements of next_norm_w
+    int pad_;
+    const __half* next_norm_w;  // RMSNorm weight of the next phase that has one: requested into L2 one phase early
+    long long pad2_;
 };
 static_assert(sizeof(FPhase) % 16 == 0, "FPhase is copied in 16-byte pieces");
 
@@ -192,7 +196,7 @@ __device__ __forceinline__ void grid_barrier(const FParams& p, unsigned& nbar, i
 #define TRACE(k)                                                                                             \
     do {                                                                                                     \
         if (p.trace && ctid == 0 && (cta == 0 || cta == grid - 1))                                           \
-            p.trace[((size_t)(cta == 0 ? 0 : 1) * p.nphases + pi) * 4 + (k)] = global_ns();                  \
+            p.trace[((size_t)(cta == 0 ? 0 : 1) * p.nphases + pi) * kTraceCols + (k)] = global_ns();                  \
     } while (0)
 
 __device__ __forceinline__ float silu_mul(float g, float u) {
@@ -393,7 +397,8 @@ __device__ __forceinline__ void quant_word(const float (&v)[8], int wd, int nwor
 // Splits per head at sequence length T: short contexts are not split at all (one CTA per head, no partial traffic).
 __device__ __forceinline__ int attn_splits_for(const FParams& p, int T) { return min(p.nsplit, max(1, (T + p.split_len - 1) / p.split_len)); }
 
-__device__ void stage_x_quant(const FPhase& ph, const FParams& p, int pos, uint4* xq, float* xs_scale, int* xs_sum, float* red, int ctid) {
+__device__ void stage_x_quant(const FPhase& ph, const FParams& p, int pos, uint4* xq, float* xs_scale, int* xs_sum, float* red, int ctid,
+                              unsigned long long* tr) {
     constexpr int kBatch = 8;  // words per thread whose loads are in flight together (one L2 round trip per batch)
     const int K = ph.K, nwords = ph.G * 16;
     const int iters = (nwords + kCT - 1) / kCT;
@@ -429,6 +434,11 @@ __device__ void stage_x_quant(const FPhase& ph, const FParams& p, int pos, uint4
                 if (ph.norm_w) wv[b] = *reinterpret_cast<const uint4*>(ph.norm_w + wd * 8);
             }
         }
+        if (tr && it0 == 0) {
+            // measurement only: make the stamp wait for the loads
+            if (xv[0].x == 0x7fc07fc0u && xv[0].y == 0x12345u) tr[7] = 1;
+            tr[4] = global_ns();
+        }
         if (ph.norm_w && it0 == 0) {
             // RMSNorm inputs have K = dim <= kBatch * kCT * 8, so the whole vector is in registers now (host-checked)
             float ss = 0.f;
@@ -446,6 +456,7 @@ __device__ void stage_x_quant(const FPhase& ph, const FParams& p, int pos, uint4
             ss /= K;
             ss += 1e-5f;
             inv_rms = 1.0f / sqrtf(ss);
+            if (tr) tr[5] = global_ns();
         }
 #pragma unroll
         for (int b = 0; b < kBatch; b++) {
@@ -469,6 +480,7 @@ __device__ void stage_x_quant(const FPhase& ph, const FParams& p, int pos, uint4
             }
         }
     }
+    if (tr) tr[6] = global_ns();
     consumer_sync();
 }
 
@@ -689,6 +701,9 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
         // s_abort is written by thread 0 inside grid_barrier and read after the barrier's closing consumer_sync
         if (s_abort != 0) return;
         TRACE(0);
+        // the next RMSNorm weight vector is cold in HBM: one CTA requests it into L2 a phase ahead of its use
+        if (ph.next_norm_w && cta == pi % grid && ctid * 64 < ph.next_norm_n)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(ph.next_norm_w + ctid * 64));
 
         if (ph.type == PH_EMBED) {
             // copy_embedding_kernel (gpu_kernels.h:61-69): the token id comes from the pinned host mailbox
@@ -701,7 +716,8 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
             grid_barrier(p, nbar, ctid, &s_abort);
 
         } else if (ph.type == PH_GEMV) {
-            stage_x_quant(ph, p, pos, xq, xs_scale, xs_sum, red, ctid);
+            stage_x_quant(ph, p, pos, xq, xs_scale, xs_sum, red, ctid,
+                          (p.trace && ctid == 0 && cta == 0) ? p.trace + (size_t)pi * kTraceCols : nullptr);
             TRACE(1);
             // old value of the residual stream for this thread's first epilogue element: requested now, used after the slots
             __half resid = __float2half(0.f);
@@ -1265,6 +1281,14 @@ int q4_fused_prepare(q4_model* m) {
         b.type = PH_ARGMAX;
         ph.push_back(b);
     }
+    {
+        const __half* nw = nullptr;
+        for (int i = (int)ph.size() - 1; i >= 0; i--) {
+            ph[i].next_norm_w = nw;
+            ph[i].next_norm_n = c.dim;
+            if (ph[i].norm_w) nw = ph[i].norm_w;
+        }
+    }
     Q4_CUDA_TRY(cudaDeviceSynchronize());  // repacks done
     f->nphases = (int)ph.size();
     FTRY(fused_alloc(f, (void**)&f->d_phases, sizeof(FPhase) * ph.size()));
@@ -1328,7 +1352,7 @@ extern "C" int q4_model_trace(q4_model* m, unsigned long long* out, int* phase_t
     if (!m) return Q4_ERR_INVALID;
     if (int e = q4_fused_prepare(m)) return e;
     q4_fused* f = m->fused;
-    const size_t n = (size_t)2 * f->nphases * 4;
+    const size_t n = (size_t)2 * f->nphases * kTraceCols;
     if (!f->trace) {
         if (int e = fused_alloc(f, (void**)&f->trace, n * sizeof(unsigned long long))) return e;
         Q4_CUDA_TRY(cudaMemset(f->trace, 0, n * sizeof(unsigned long long)));
