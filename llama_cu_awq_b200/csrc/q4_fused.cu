@@ -53,23 +53,24 @@ constexpr int kTraceCols = 8;           // timestamps per phase: 0 start, 1 inpu
 constexpr int kClsChunk = 4096;        // halfs of one classifier row per slot (8192 B)
 constexpr unsigned kPollLimit = 1u << 26;                        // polls, and
 constexpr unsigned long long kWaitLimitNs = 2000ULL * 1000 * 1000;  // two seconds on the global timer, whichever comes first
-constexpr unsigned kSpinLimit = 1u << 23;
 
 enum PhaseType { PH_EMBED = 0, PH_GEMV = 1, PH_ATTN = 2, PH_CLS = 3, PH_ARGMAX = 4 };
 enum EpiKind { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SILU = 2 };
 
 struct FMat {
     const uint8_t* blocks;  // stream layout
-    __half* out;
+    uint32_t* out;          // tagged output vector (value | tag << 16), see "tagged activations" below
+    __half* out_plain;      // V projection only: the KV cache (row pos at loff), written untagged as well
     int n;                  // outputs of this matrix
     int tile0;              // first tile of this matrix in the phase's tile space
-    int kv;                 // 1: out += loff + pos * n
 };
 
 struct FPhase {
     int type;
     int K, G, nkt;          // GEMV: inputs, groups, k-tiles; CLS: K = dim, nkt = chunks per row
-    const __half* xin;      // activations (global fp16)
+    const uint32_t* xin;    // tagged activations (global), written by phase in_phase
+    int in_phase;           // index of the phase that produced xin (its tag is what the readers wait for)
+    int barrier_after;      // 1: grid barrier after this phase (else the consumers of its output wait on the tags)
     const __half* norm_w;   // RMSNorm weight applied while staging x, or null
     int nmat;
     FMat m[3];
@@ -81,7 +82,6 @@ struct FPhase {
     int next_norm_n;        // elements of next_norm_w
     int pad_;
     const __half* next_norm_w;  // RMSNorm weight of the next phase that has one: requested into L2 one phase early
-    long long pad2_;
 };
 static_assert(sizeof(FPhase) % 16 == 0, "FPhase is copied in 16-byte pieces");
 
@@ -92,7 +92,14 @@ struct FParams {
     int head_size, kv_n, kv_mul, n_heads, nsplit;
     float gpu_count;
     // state
-    __half *x, *xb, *hb, *q, *knew, *logits, *kc, *vc;
+    // Tagged activations: every element is a 32-bit word, fp16 value in the low half and the low 16 bits of
+    // (tag_base + producing phase + 1) in the high half. A reader that needs the whole vector polls the words
+    // themselves until all carry the expected tag, so most op boundaries need no grid barrier: one L2 round trip
+    // instead of fence + arrive + poll. A buffer is rewritten only after every CTA has provably read it (the next
+    // writer's own input wait, or the barrier kept after attention, implies it).
+    uint32_t *x, *hb, *q, *knew, *vnew;
+    unsigned tag_base;
+    __half *logits, *kc, *vc;
     const __half *emb, *wcls;
     const float* rope;       // [seq_len][head_size/2] (cos, sin)
     float* attn_part;        // [heads*nsplit][head_size + 2]
@@ -150,7 +157,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, int* sta
             else if (now - t0 > kWaitLimitNs) break;
         }
     }
-    atomicExch(status, Q4_ERR_TIMEOUT);
+    if (atomicCAS(status, 0, Q4_ERR_TIMEOUT) == 0) status[1] = 0x40000 + (int)(smem_u32(b) & 0xFFFF);
     return false;
 }
 __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
@@ -177,15 +184,23 @@ __device__ __forceinline__ void grid_barrier(const FParams& p, unsigned& nbar, i
         const unsigned long long target = (p.bar_base + nbar) * (unsigned long long)gridDim.x;
         unsigned long long v;
         const int st = *(volatile int*)p.status;  // in flight together with the atomic
-        asm volatile("red.release.gpu.global.add.u64 [%0], 1;" ::"l"(p.bar_counter) : "memory");  // no return trip needed
+        asm volatile("atom.add.release.gpu.global.u64 %0, [%1], 1;" : "=l"(v) : "l"(p.bar_counter) : "memory");
+        if (blockIdx.x < 256) p.status[4 + 256 + blockIdx.x] = (int)nbar;
         if (st != 0) *s_abort = 1;
         unsigned spins = 0;
+        unsigned long long t0 = 0;
         for (;;) {
             asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p.bar_counter) : "memory");
             if (v >= target) break;
-            if ((++spins & 255u) == 0) {
+            if ((++spins & 63u) == 0) {
                 if (*(volatile int*)p.status != 0) { *s_abort = 1; break; }
-                if (spins > kSpinLimit) { atomicExch(p.status, Q4_ERR_TIMEOUT); *s_abort = 1; break; }
+                const unsigned long long now = global_ns();
+                if (t0 == 0) t0 = now;
+                else if (now - t0 > 2 * kWaitLimitNs) {   // longer than any single data wait, so that the root cause is what gets recorded
+                    if (atomicCAS(p.status, 0, Q4_ERR_TIMEOUT) == 0) { p.status[1] = 0x50000 + (int)nbar; p.status[2] = (int)v; p.status[3] = (int)target; }
+                    *s_abort = 1;
+                    break;
+                }
             }
         }
     }
@@ -257,6 +272,46 @@ __device__ __forceinline__ void tile_info(const FPhase& ph, int t, int& mi, int&
 // measured slower: 148 streams 170 KB apart.) The classifier's unit is a pair of rows, 16 KB contiguous.
 __device__ __forceinline__ int unit_count(int nunits, int cta, int grid) { return nunits > cta ? (nunits - cta + grid - 1) / grid : 0; }
 __device__ __forceinline__ int unit_at(int i, int cta, int grid) { return cta + i * grid; }
+
+// ---- tagged activations -----------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t tag_of(const FParams& p, int phase) { return ((p.tag_base + (unsigned)phase + 1u) & 0xFFFFu) << 16; }
+__device__ __forceinline__ uint32_t tagged(__half v, uint32_t tag_hi) { return tag_hi | (uint32_t)__half_as_ushort(v); }
+// 8 consecutive tagged elements (two 128-bit loads). Returns the 8 fp16 values as a uint4 and ORs every tag mismatch into `bad`.
+// Tagged words are exchanged between CTAs without a barrier, so both sides use strong (volatile) accesses: a weak load
+// may be served from a stale copy for as long as it likes (observed: polling with ld.global.cg never saw the update),
+// and the compiler may hoist it out of the wait loop.
+__device__ __forceinline__ uint4 ld_poll(const uint4* p) {
+    uint4 r;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p) : "memory");
+    return r;
+}
+__device__ __forceinline__ uint32_t ld_tagged(const uint32_t* p) {
+    uint32_t r;
+    asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(r) : "l"(p) : "memory");
+    return r;
+}
+__device__ __forceinline__ void st_tagged(uint32_t* p, uint32_t v) { asm volatile("st.volatile.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+__device__ __forceinline__ void st_tagged4(uint32_t* p, uint4 v) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ uint4 load_tagged8(const uint32_t* src, uint32_t tag_hi, uint32_t& bad) {
+    const uint4 a = ld_poll(reinterpret_cast<const uint4*>(src)), b = ld_poll(reinterpret_cast<const uint4*>(src) + 1);
+    bad |= ((a.x ^ tag_hi) | (a.y ^ tag_hi) | (a.z ^ tag_hi) | (a.w ^ tag_hi) | (b.x ^ tag_hi) | (b.y ^ tag_hi) | (b.z ^ tag_hi) | (b.w ^ tag_hi)) >> 16;
+    return make_uint4(prmt(a.x, a.y, 0x5410), prmt(a.z, a.w, 0x5410), prmt(b.x, b.y, 0x5410), prmt(b.z, b.w, 0x5410));
+}
+// Bounded retry bookkeeping for the tag polls: returns false when the wait must be given up.
+__device__ __forceinline__ bool keep_polling(unsigned& polls, unsigned long long& t0, int* status, int where = 0) {
+    if ((++polls & 15u) == 0) {
+        if (*(volatile int*)status != 0) return false;
+        const unsigned long long now = global_ns();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > kWaitLimitNs) {
+            if (atomicCAS(status, 0, Q4_ERR_TIMEOUT) == 0) status[1] = where;  // where the first wait ran out (diagnostics)
+            return false;
+        }
+    }
+    return true;
+}
 
 // Walks the slots of one CTA in issue order: phase by phase, unit by unit, tile by tile, k-tile by k-tile.
 // The consumers enumerate the same order with plain arithmetic.
@@ -337,7 +392,7 @@ __device__ __forceinline__ void attn_word_load(AttnWord& w, const FParams& p, in
         }
     }
 }
-__device__ __forceinline__ void attn_word_merge(const AttnWord& w, float (&v)[8]) {
+__device__ __forceinline__ uint4 attn_word_merge(const AttnWord& w) {
     float M = -CUDART_INF_F;
 #pragma unroll
     for (int s = 0; s < kMaxSplit; s++) M = fmaxf(M, w.ml[s].x);
@@ -358,31 +413,49 @@ __device__ __forceinline__ void attn_word_merge(const AttnWord& w, float (&v)[8]
             }
         }
     }
+    uint4 out;
+    __half2* oh = reinterpret_cast<__half2*>(&out);
+    const float rl = L > 0.f ? 1.0f / L : 0.f;
 #pragma unroll
-    for (int j = 0; j < 8; j++) v[j] = L > 0.f ? __half2float(__float2half(a[j] / L)) : 0.f;
+    for (int j = 0; j < 4; j++) oh[j] = __floats2half2_rn(a[2 * j] * rl, a[2 * j + 1] * rl);
+    return out;
 }
 
-// Quantises one word's eight values (already fp16-representable floats) and files it in xq / xs_*.
-__device__ __forceinline__ void quant_word(const float (&v)[8], int wd, int nwords, uint4* xq, float* xs_scale, int* xs_sum) {
-    float amax = 0.f;
-#pragma unroll
-    for (int j = 0; j < 8; j++) amax = fmaxf(amax, fabsf(v[j]));
+// Quantises one word (8 fp16 values, packed in a uint4) to 15-bit block fixed point and files it in xq / xs_*.
+// X = rint(v * 16256 / amax) and its high digit rint(v * 127 / amax) come out of two FMAs with the 1.5 * 2^23 magic
+// constant (the integer sits in the low mantissa bits), the low digit is X - 128 * hi (|lo| <= 64), and the digits
+// are gathered into the DP4A operand words with byte permutes.
+__device__ __forceinline__ void quant_word(const uint4& hv, int wd, int nwords, uint4* xq, float* xs_scale, int* xs_sum) {
+    const __half2* h = reinterpret_cast<const __half2*>(&hv);
+    const __half2 m2 = __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3])));
+    float amax = fmaxf(__low2float(m2), __high2float(m2));
 #pragma unroll
     for (int o = 1; o < 16; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));  // 16 words = 1 group
     const float sx = amax * (1.0f / 16256.0f);
     const float inv = amax > 0.f ? 16256.0f / amax : 0.f;
-    uint32_t he = 0, ho = 0, le = 0, lo = 0;
-    int sum = 0;
+    const float inv128 = inv * (1.0f / 128.0f);
+    constexpr float kMagic = 12582912.0f;      // 1.5 * 2^23
+    constexpr int kMagicBits = 0x4B400000;
+    int xb[8], hb[8], lb[8];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const float2 f = __half22float2(h[j]);
+        xb[2 * j] = __float_as_int(fmaf(f.x, inv, kMagic));
+        xb[2 * j + 1] = __float_as_int(fmaf(f.y, inv, kMagic));
+        hb[2 * j] = __float_as_int(fmaf(f.x, inv128, kMagic));
+        hb[2 * j + 1] = __float_as_int(fmaf(f.y, inv128, kMagic));
+    }
+    int sum = -8 * kMagicBits;
 #pragma unroll
     for (int j = 0; j < 8; j++) {
-        const int X = __float2int_rn(v[j] * inv);
-        sum += X;
-        const int hi = (X + 64) >> 7;
-        const int low = X - (hi << 7);
-        const uint32_t hb = (uint32_t)hi & 0xFFu, lb = (uint32_t)low & 0xFFu;
-        if (j & 1) { ho |= hb << (8 * (j >> 1)); lo |= lb << (8 * (j >> 1)); }
-        else       { he |= hb << (8 * (j >> 1)); le |= lb << (8 * (j >> 1)); }
+        sum += xb[j];
+        lb[j] = xb[j] - (hb[j] << 7);   // low byte = X - 128 * hi (the magic constants cancel in the low byte)
     }
+    // byte 0 of four registers -> one word: (a, b) -> [a.b0, b.b0], then the two halves together
+    const uint32_t he = prmt(prmt(hb[0], hb[2], 0x0040), prmt(hb[4], hb[6], 0x0040), 0x5410);
+    const uint32_t ho = prmt(prmt(hb[1], hb[3], 0x0040), prmt(hb[5], hb[7], 0x0040), 0x5410);
+    const uint32_t le = prmt(prmt(lb[0], lb[2], 0x0040), prmt(lb[4], lb[6], 0x0040), 0x5410);
+    const uint32_t lo = prmt(prmt(lb[1], lb[3], 0x0040), prmt(lb[5], lb[7], 0x0040), 0x5410);
     sum += __shfl_xor_sync(0xffffffffu, sum, 1);
     sum += __shfl_xor_sync(0xffffffffu, sum, 2);
     sum += __shfl_xor_sync(0xffffffffu, sum, 4);  // 8 words = the 64 inputs of one (group, half)
@@ -399,7 +472,7 @@ __device__ __forceinline__ int attn_splits_for(const FParams& p, int T) { return
 
 __device__ void stage_x_quant(const FPhase& ph, const FParams& p, int pos, uint4* xq, float* xs_scale, int* xs_sum, float* red, int ctid,
                               unsigned long long* tr) {
-    constexpr int kBatch = 8;  // words per thread whose loads are in flight together (one L2 round trip per batch)
+    constexpr int kBatch = 4;  // words per thread whose loads are in flight together (one L2 round trip per batch)
     const int K = ph.K, nwords = ph.G * 16;
     const int iters = (nwords + kCT - 1) / kCT;
     if (ph.attn_in) {
@@ -410,29 +483,34 @@ __device__ void stage_x_quant(const FPhase& ph, const FParams& p, int pos, uint4
             const int wd0 = ctid + it0 * kCT, wd1 = wd0 + kCT;
             attn_word_load(w0, p, ns, wd0, wd0 < nwords && wd0 * 8 < K);
             attn_word_load(w1, p, ns, wd1, it0 + 1 < iters && wd1 < nwords && wd1 * 8 < K);
-            float v[8];
-            attn_word_merge(w0, v);
-            quant_word(v, wd0, nwords, xq, xs_scale, xs_sum);
-            if (it0 + 1 < iters) {
-                attn_word_merge(w1, v);
-                quant_word(v, wd1, nwords, xq, xs_scale, xs_sum);
-            }
+            quant_word(attn_word_merge(w0), wd0, nwords, xq, xs_scale, xs_sum);
+            if (it0 + 1 < iters) quant_word(attn_word_merge(w1), wd1, nwords, xq, xs_scale, xs_sum);
         }
         consumer_sync();
         return;
     }
     float inv_rms = 1.f;
+    const uint32_t want = tag_of(p, ph.in_phase);
     for (int it0 = 0; it0 < iters; it0 += kBatch) {
         uint4 xv[kBatch], wv[kBatch];
 #pragma unroll
         for (int b = 0; b < kBatch; b++) {
             const int wd = ctid + (it0 + b) * kCT;
-            xv[b] = make_uint4(0, 0, 0, 0);
             wv[b] = make_uint4(0, 0, 0, 0);
-            if (it0 + b < iters && wd < nwords && wd * 8 < K) {
-                xv[b] = __ldcg(reinterpret_cast<const uint4*>(ph.xin + wd * 8));
-                if (ph.norm_w) wv[b] = *reinterpret_cast<const uint4*>(ph.norm_w + wd * 8);
+            if (ph.norm_w && it0 + b < iters && wd < nwords && wd * 8 < K) wv[b] = *reinterpret_cast<const uint4*>(ph.norm_w + wd * 8);
+        }
+        // the input words carry the producing phase's tag: poll them until all have arrived (this is the op boundary)
+        unsigned polls = 0;
+        unsigned long long t0 = 0;
+        for (;;) {
+            uint32_t bad = 0;
+#pragma unroll
+            for (int b = 0; b < kBatch; b++) {
+                const int wd = ctid + (it0 + b) * kCT;
+                xv[b] = make_uint4(0, 0, 0, 0);
+                if (it0 + b < iters && wd < nwords && wd * 8 < K) xv[b] = load_tagged8(ph.xin + wd * 8, want, bad);
             }
+            if (bad == 0 || !keep_polling(polls, t0, p.status, 0x100 + ph.in_phase)) break;
         }
         if (tr && it0 == 0) {
             // measurement only: make the stamp wait for the loads
@@ -462,21 +540,19 @@ __device__ void stage_x_quant(const FPhase& ph, const FParams& p, int pos, uint4
         for (int b = 0; b < kBatch; b++) {
             if (it0 + b < iters) {  // uniform over the block: the shuffles below see all lanes
                 const int wd = ctid + (it0 + b) * kCT;
-                float v[8];
-                const __half* xh = reinterpret_cast<const __half*>(&xv[b]);
+                uint4 hv = xv[b];
                 if (ph.norm_w) {
-                    const __half* wh = reinterpret_cast<const __half*>(&wv[b]);
+                    // val = x * (inv_rms * w), rounded to fp16 once (gpu_kernels.h:100-102)
+                    const __half2* xh = reinterpret_cast<const __half2*>(&xv[b]);
+                    const __half2* wh = reinterpret_cast<const __half2*>(&wv[b]);
+                    __half2* oh = reinterpret_cast<__half2*>(&hv);
 #pragma unroll
-                    for (int j = 0; j < 8; j++) {
-                        float val = __half2float(xh[j]);
-                        val *= inv_rms * __half2float(wh[j]);
-                        v[j] = __half2float(__float2half(val));
+                    for (int j = 0; j < 4; j++) {
+                        const float2 xf2 = __half22float2(xh[j]), wf2 = __half22float2(wh[j]);
+                        oh[j] = __floats2half2_rn(xf2.x * (inv_rms * wf2.x), xf2.y * (inv_rms * wf2.y));
                     }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 8; j++) v[j] = __half2float(xh[j]);
                 }
-                quant_word(v, wd, nwords, xq, xs_scale, xs_sum);
+                quant_word(hv, wd, nwords, xq, xs_scale, xs_sum);
             }
         }
     }
@@ -485,16 +561,38 @@ __device__ void stage_x_quant(const FPhase& ph, const FParams& p, int pos, uint4
 }
 
 // Classifier input: final RMSNorm, fp16, plain layout.
-__device__ void stage_x_f16(const FPhase& ph, __half* xf, float* red, int ctid) {
+__device__ void stage_x_f16(const FPhase& ph, const FParams& p, __half* xf, float* red, int ctid) {
     const int K = ph.K;
+    const uint32_t want = tag_of(p, ph.in_phase);
     float ss = 0.f;
-    for (int i = ctid; i < K; i += kCT) { const float f = __half2float(__ldcg(ph.xin + i)); ss = fmaf(f, f, ss); }
+    // first pass: wait for the tagged words, keep the values in shared memory, sum the squares
+    for (int wd = ctid; wd * 8 < K; wd += kCT) {
+        uint4 v;
+        unsigned polls = 0;
+        unsigned long long t0 = 0;
+        for (;;) {
+            uint32_t bad = 0;
+            v = load_tagged8(ph.xin + wd * 8, want, bad);
+            if (bad == 0) break;
+            if (!keep_polling(polls, t0, p.status, 0x60000 + ph.in_phase)) {
+                break;
+            }
+        }
+        reinterpret_cast<uint4*>(xf)[wd] = v;
+        const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float2 f = __half22float2(h[j]);
+            ss = fmaf(f.x, f.x, ss);
+            ss = fmaf(f.y, f.y, ss);
+        }
+    }
     ss = consumer_sum(ss, red, ctid);
     ss /= K;
     ss += 1e-5f;
     const float inv_rms = 1.0f / sqrtf(ss);
     for (int i = ctid; i < K; i += kCT) {
-        float val = __half2float(__ldcg(ph.xin + i));
+        float val = __half2float(xf[i]);
         val *= inv_rms * __half2float(ph.norm_w[i]);
         xf[i] = __float2half(val);
     }
@@ -575,7 +673,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ uint64_t full_bar[kEntries], empty_bar[kEntries];
     __shared__ float red[kCW];
-    __shared__ int s_flag, s_abort;
+    __shared__ int s_abort;
     __shared__ unsigned s_ring_seq;   // slots the ring cursor has issued (read by the L2 cursor)
     __shared__ __align__(16) FPhase s_pph[2];  // producer cursors' phase descriptors
     __shared__ __align__(16) FPhase s_cph;     // consumers' phase descriptor
@@ -663,7 +761,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
             have = cursor_next(rc, p, cta, grid, src, bytes, phase);
             const bool pair = have && phase == phaseA;
             const int e = ent % kEntries;
-            if (!mbar_wait(&empty_bar[e], ((ent / kEntries) & 1) ^ 1, p.status)) return;
+            if (!mbar_wait(&empty_bar[e], ((ent / kEntries) & 1) ^ 1, p.status)) break;
             uint8_t* dst = ring + (size_t)e * kEntryBytes;
             if (pair) {
                 mbar_expect_tx(&full_bar[e], bytesA + bytes);
@@ -682,6 +780,18 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
             *(volatile unsigned*)&s_ring_seq = ent;
         }
         *(volatile unsigned*)&s_ring_seq = 0x3fffffffu;
+        // Before this thread (the last owner of the CTA's shared memory as far as the copy engine is concerned) leaves:
+        // every bulk copy it issued must have landed. On the normal path the consumers have waited for all of them
+        // already; after an error the newest copy of each ring entry may still be in flight.
+        if (*(volatile int*)p.status != 0) {
+            const unsigned first = ent > (unsigned)kEntries ? ent - kEntries : 0;
+            for (unsigned i = first; i < ent; i++) {
+                const unsigned long long t0 = global_ns();
+                while (!mbar_try(&full_bar[i % kEntries], (i / kEntries) & 1)) {
+                    if (global_ns() - t0 > 50ULL * 1000 * 1000) break;  // 50 ms: far beyond any copy's flight time
+                }
+            }
+        }
         return;
     }
 
@@ -700,6 +810,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
         // all consumer threads leave together (named barriers count live threads), never one by one:
         // s_abort is written by thread 0 inside grid_barrier and read after the barrier's closing consumer_sync
         if (s_abort != 0) return;
+        if (ctid == 0 && cta < 256) p.status[4 + cta] = pi;  // progress marker (diagnostics after a timeout)
         TRACE(0);
         // the next RMSNorm weight vector is cold in HBM: one CTA requests it into L2 a phase ahead of its use
         if (ph.next_norm_w && cta == pi % grid && ctid * 64 < ph.next_norm_n)
@@ -710,19 +821,24 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
             if (cta * kCT + ctid < p.cfg.dim / 8) {
                 const int token = p.tokens_pinned[pos];
                 const uint4* src = reinterpret_cast<const uint4*>(p.emb + (size_t)token * p.cfg.dim);
-                uint4* dst = reinterpret_cast<uint4*>(p.x);
-                for (int i = cta * kCT + ctid; i < p.cfg.dim / 8; i += grid * kCT) dst[i] = src[i];
+                const uint32_t tg = tag_of(p, pi);
+                for (int i = cta * kCT + ctid; i < p.cfg.dim / 8; i += grid * kCT) {
+                    const uint4 v = src[i];
+                    uint32_t* dst = p.x + (size_t)i * 8;
+                    st_tagged4(dst, make_uint4(tg | (v.x & 0xFFFFu), tg | (v.x >> 16), tg | (v.y & 0xFFFFu), tg | (v.y >> 16)));
+                    st_tagged4(dst + 4, make_uint4(tg | (v.z & 0xFFFFu), tg | (v.z >> 16), tg | (v.w & 0xFFFFu), tg | (v.w >> 16)));
+                }
             }
-            grid_barrier(p, nbar, ctid, &s_abort);
+            consumer_sync();  // nobody may still be reading this phase's descriptor when the next one replaces it
 
         } else if (ph.type == PH_GEMV) {
             stage_x_quant(ph, p, pos, xq, xs_scale, xs_sum, red, ctid,
                           (p.trace && ctid == 0 && cta == 0) ? p.trace + (size_t)pi * kTraceCols : nullptr);
             TRACE(1);
             // old value of the residual stream for this thread's first epilogue element: requested now, used after the slots
-            __half resid = __float2half(0.f);
+            uint32_t resid = 0;
             if (ph.epi == EPI_RESIDUAL) {
-                if ((ctid >> 3) < unit_count(ph.nunits, cta, grid)) resid = __ldcg(ph.m[0].out + unit_at(ctid >> 3, cta, grid) * 8 + (ctid & 7));
+                if ((ctid >> 3) < unit_count(ph.nunits, cta, grid)) resid = ld_tagged(ph.m[0].out + unit_at(ctid >> 3, cta, grid) * 8 + (ctid & 7));
             }
             // slots of this CTA, in the producer's order; slot i belongs to consumer warp i % kCW.
             // Phase constants live in registers: the descriptor is not re-read inside the loops.
@@ -751,6 +867,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
             TRACE(2);
             // epilogue: one thread per (local tile, column)
             const int epi = ph.epi;
+            const uint32_t out_tag = tag_of(p, pi);
             for (int e = ctid; e < ntl * 8; e += kCT) {
                 const int l2 = e >> 3, r = e & 7;
                 const int u = unit_at(l2 / tpu, cta, grid);
@@ -763,17 +880,21 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                     if (mi == 0) {
                         float up = 0.f;
                         for (int kt = 0; kt < nkt; kt++) up += part[(size_t)((l2 + 1) * nkt + kt) * 8 + r];
-                        ph.m[0].out[n] = __float2half(silu_mul(sum, up));
+                        st_tagged(ph.m[0].out + n, tagged(__float2half(silu_mul(sum, up)), out_tag));
                     }
                 } else {
                     const FMat& m = ph.m[mi];
-                    __half* out = m.out;
-                    if (m.kv) out += ph.loff + (long long)pos * m.n;
-                    if (epi == EPI_RESIDUAL) sum += __half2float(e == ctid ? resid : __ldcg(out + n)) / p.gpu_count;
-                    out[n] = __float2half(sum);
+                    if (epi == EPI_RESIDUAL) {
+                        const uint32_t old = (e == ctid) ? resid : ld_tagged(m.out + n);
+                        sum += __half2float(__ushort_as_half((unsigned short)(old & 0xFFFFu))) / p.gpu_count;
+                    }
+                    const __half hv = __float2half(sum);
+                    st_tagged(m.out + n, tagged(hv, out_tag));
+                    if (m.out_plain) m.out_plain[ph.loff + (long long)pos * m.n + n] = hv;   // V row into the cache for later tokens
                 }
             }
-            grid_barrier(p, nbar, ctid, &s_abort);
+            if (ph.barrier_after) grid_barrier(p, nbar, ctid, &s_abort);
+            else consumer_sync();  // the phase descriptor in shared memory is replaced next
             TRACE(3);
 
         } else if (ph.type == PH_ATTN) {
@@ -789,6 +910,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
             const float alpha = (float)(1.0 / sqrt((double)HS));
             const int ns = attn_splits_for(p, T);
             const int nitems = p.n_heads * ns;
+            const uint32_t want = tag_of(p, ph.in_phase);
             const __half* kc = p.kc + ph.loff;
             const __half* vc = p.vc + ph.loff;
             // (cos, sin) of this position for dims i0..i0+15: RoPE of gpu_kernels.h:340-363, tabulated at load time
@@ -814,23 +936,27 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                 auto fetch = [&](int tb) {
                     int t = tb + grp;
                     if (t >= t1) t = t0;
-                    if (tb < t1) {
+                    if (tb < t1 && t != pos) {   // the new position's K and V come from the tagged staging vectors
                         const uint4* vr = reinterpret_cast<const uint4*>(vc + (size_t)t * p.kv_n + col);
                         vn[0] = __ldcg(vr); vn[1] = __ldcg(vr + 1);
-                        if (t != pos) {
-                            const uint4* kr = reinterpret_cast<const uint4*>(kc + (size_t)t * p.kv_n + col);
-                            kn[0] = __ldcg(kr); kn[1] = __ldcg(kr + 1);
-                        }
+                        const uint4* kr = reinterpret_cast<const uint4*>(kc + (size_t)t * p.kv_n + col);
+                        kn[0] = __ldcg(kr); kn[1] = __ldcg(kr + 1);
                     }
                 };
                 fetch(t0);
                 // rotated query (fp16-rounded like the reference's in-place rotation)
                 float qf[16];
                 {
-                    const uint4* qlo = reinterpret_cast<const uint4*>(p.q + (size_t)h * HS + i0);
-                    const uint4* qhi = reinterpret_cast<const uint4*>(p.q + (size_t)h * HS + i0 + 64);
-                    const uint4 a0 = __ldcg(qlo), a1 = __ldcg(qlo + 1), b0 = __ldcg(qhi), b1 = __ldcg(qhi + 1);
-                    const uint4 lo4[2] = {a0, a1}, hi4[2] = {b0, b1};
+                    const uint32_t* qp = p.q + (size_t)h * HS + i0;
+                    uint4 lo4[2], hi4[2];
+                    unsigned polls = 0;
+                    unsigned long long tw = 0;
+                    for (;;) {   // the query arrives tagged from the QKV phase: this poll is the op boundary
+                        uint32_t bad = 0;
+                        lo4[0] = load_tagged8(qp, want, bad); lo4[1] = load_tagged8(qp + 8, want, bad);
+                        hi4[0] = load_tagged8(qp + 64, want, bad); hi4[1] = load_tagged8(qp + 72, want, bad);
+                        if (bad == 0 || !keep_polling(polls, tw, p.status)) break;
+                    }
                     const __half* lo = reinterpret_cast<const __half*>(lo4);
                     const __half* hi = reinterpret_cast<const __half*>(hi4);
 #pragma unroll
@@ -852,9 +978,23 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                     float kf[16], vf[16];
                     if (tt == pos) {
                         // the new key is un-rotated in knew: rotate it here; the head group's first query head also files it
-                        const uint4* klo = reinterpret_cast<const uint4*>(p.knew + (size_t)kvh * HS + i0);
-                        const uint4* khi = reinterpret_cast<const uint4*>(p.knew + (size_t)kvh * HS + i0 + 64);
-                        const uint4 lo4[2] = {__ldcg(klo), __ldcg(klo + 1)}, hi4[2] = {__ldcg(khi), __ldcg(khi + 1)};
+                        const uint32_t* kp = p.knew + (size_t)kvh * HS + i0;
+                        const uint32_t* vp = p.vnew + (size_t)kvh * HS + d0;
+                        uint4 lo4[2], hi4[2], vnew4[2];
+                        unsigned polls = 0;
+                        unsigned long long tw = 0;
+                        for (;;) {
+                            uint32_t bad = 0;
+                            lo4[0] = load_tagged8(kp, want, bad); lo4[1] = load_tagged8(kp + 8, want, bad);
+                            hi4[0] = load_tagged8(kp + 64, want, bad); hi4[1] = load_tagged8(kp + 72, want, bad);
+                            vnew4[0] = load_tagged8(vp, want, bad); vnew4[1] = load_tagged8(vp + 8, want, bad);
+                            if (bad == 0 || !keep_polling(polls, tw, p.status, 0x30000 + pi)) break;
+                        }
+                        {
+                            const __half2* hh = reinterpret_cast<const __half2*>(vnew4);
+#pragma unroll
+                            for (int j = 0; j < 8; j++) { const float2 a = __half22float2(hh[j]); vf[2 * j] = a.x; vf[2 * j + 1] = a.y; }
+                        }
                         const __half* lo = reinterpret_cast<const __half*>(lo4);
                         const __half* hi = reinterpret_cast<const __half*>(hi4);
                         uint4 store[2];
@@ -876,7 +1016,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
 #pragma unroll
                         for (int j = 0; j < 8; j++) { const float2 a = __half22float2(hh[j]); kf[2 * j] = a.x; kf[2 * j + 1] = a.y; }
                     }
-                    {
+                    if (tt != pos) {
                         const __half2* hh = reinterpret_cast<const __half2*>(vcur);
 #pragma unroll
                         for (int j = 0; j < 8; j++) { const float2 a = __half22float2(hh[j]); vf[2 * j] = a.x; vf[2 * j + 1] = a.y; }
@@ -929,7 +1069,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
         } else if (ph.type == PH_CLS) {
             // ---- classifier: fp16 rows streamed through the same ring; per-CTA argmax candidate ----
             __half* xf = reinterpret_cast<__half*>(xq);
-            stage_x_f16(ph, xf, red, ctid);
+            stage_x_f16(ph, p, xf, red, ctid);
             TRACE(1);
             const int nunits = ph.nunits, nkt = ph.nkt, K = ph.K;
             const int lt = unit_count(nunits, cta, grid) * 2;        // rows of this CTA (units are row pairs)
@@ -1119,21 +1259,44 @@ void q4_fused_free(q4_model* m) {
     m->fused = nullptr;
 }
 
+// Called by q4_model_reset. Launch and barrier counters (and with them the activation tags) simply keep counting
+// across generations; only after a recorded error is everything re-armed from zero.
 void q4_fused_reset(q4_model* m) {
     if (!m->fused || m->fused->unsupported) return;
     q4_fused* f = m->fused;
+    int st = 0;
+    cudaDeviceSynchronize();
+    if (f->launches != 0 && cudaMemcpy(&st, f->params.status, sizeof(int), cudaMemcpyDeviceToHost) == cudaSuccess && st == 0) return;
+    const q4_config& c = m->cfg;
     cudaMemset(f->params.bar_counter, 0, sizeof(unsigned long long));
-    cudaMemset(f->params.status, 0, sizeof(int));
-    cudaMemset(f->params.attn_cnt, 0, sizeof(unsigned) * f->params.n_heads);
+    cudaMemset(f->params.status, 0, (4 + 4 * 256) * sizeof(int));
+    cudaMemset(f->params.x, 0, 4 * (size_t)c.dim);
+    cudaMemset(f->params.hb, 0, 4 * (size_t)c.hidden_dim);
+    cudaMemset(f->params.q, 0, 4 * (size_t)c.dim);
+    cudaMemset(f->params.knew, 0, 4 * (size_t)m->kv_n);
+    cudaMemset(f->params.vnew, 0, 4 * (size_t)m->kv_n);
     cudaDeviceSynchronize();  // the memsets run on the default stream; forward calls use the caller's stream
     f->launches = 0;
 }
 
 int q4_fused_status(q4_model* m) {
     if (!m->fused || m->fused->unsupported) return Q4_OK;
-    int st = 0;
-    Q4_CUDA_TRY(cudaMemcpy(&st, m->fused->params.status, sizeof(int), cudaMemcpyDeviceToHost));
-    return st;
+    int st[4] = {0, 0, 0, 0};
+    Q4_CUDA_TRY(cudaMemcpy(st, m->fused->params.status, sizeof(st), cudaMemcpyDeviceToHost));
+    if (st[0] != 0) {
+        fprintf(stderr, "q4 fused path: a bounded device-side wait ran out (status %d, location 0x%x)\n", st[0], st[1]);
+        if (getenv("Q4_FUSED_DEBUG")) {
+            int prog[256];
+            cudaMemcpy(prog, m->fused->params.status + 4, sizeof(prog), cudaMemcpyDeviceToHost);
+            fprintf(stderr, "  phase reached per CTA:");
+            for (int i = 0; i < m->fused->grid && i < 256; i++) fprintf(stderr, " %d", prog[i]);
+            fprintf(stderr, "\n  detail 0x%x 0x%x; barriers arrived per CTA:", st[2], st[3]);
+            cudaMemcpy(prog, m->fused->params.status + 4 + 256, sizeof(prog), cudaMemcpyDeviceToHost);
+            for (int i = 0; i < m->fused->grid && i < 256; i++) fprintf(stderr, " %d", prog[i]);
+            fprintf(stderr, "\n");
+        }
+    }
+    return st[0];
 }
 
 int q4_fused_prepare(q4_model* m) {
@@ -1141,7 +1304,7 @@ int q4_fused_prepare(q4_model* m) {
     q4_fused* f = new q4_fused();
     m->fused = f;
     const q4_config& c = m->cfg;
-    if (m->g != 1 || m->head_size != 128 || (c.dim % 128) || (c.hidden_dim % 8) || c.dim > 8 * kCT * 8) {  // 8 = staging batch
+    if (m->g != 1 || m->head_size != 128 || (c.dim % 128) || (c.hidden_dim % 8) || c.dim > 4 * kCT * 8) {  // 4 = staging batch
         f->unsupported = true;
         return Q4_ERR_UNSUPPORTED_SIZE;
     }
@@ -1161,7 +1324,7 @@ int q4_fused_prepare(q4_model* m) {
     p.n_heads = c.n_heads;
     p.nsplit = std::min(kMaxSplit, std::max(1, sms / c.n_heads));
     p.gpu_count = 1.f;
-    p.x = (__half*)m->x; p.xb = (__half*)m->xb; p.hb = (__half*)m->hb; p.q = (__half*)m->q; p.logits = (__half*)m->logits;
+    p.logits = (__half*)m->logits;
     p.kc = (__half*)m->kc; p.vc = (__half*)m->vc;
     p.emb = (const __half*)m->emb; p.wcls = (const __half*)m->wcls;
     p.pos_dev = m->pos;
@@ -1169,7 +1332,16 @@ int q4_fused_prepare(q4_model* m) {
     p.pos_pinned = &m->shared->pos;
     int e;
 #define FTRY(expr) do { e = (expr); if (e != Q4_OK) return e; } while (0)
-    FTRY(fused_alloc(f, (void**)&p.knew, 2 * (size_t)m->kv_n));
+    FTRY(fused_alloc(f, (void**)&p.x, 4 * (size_t)c.dim));
+    FTRY(fused_alloc(f, (void**)&p.hb, 4 * (size_t)c.hidden_dim));
+    FTRY(fused_alloc(f, (void**)&p.q, 4 * (size_t)c.dim));
+    FTRY(fused_alloc(f, (void**)&p.knew, 4 * (size_t)m->kv_n));
+    FTRY(fused_alloc(f, (void**)&p.vnew, 4 * (size_t)m->kv_n));
+    Q4_CUDA_TRY(cudaMemset(p.x, 0, 4 * (size_t)c.dim));
+    Q4_CUDA_TRY(cudaMemset(p.hb, 0, 4 * (size_t)c.hidden_dim));
+    Q4_CUDA_TRY(cudaMemset(p.q, 0, 4 * (size_t)c.dim));
+    Q4_CUDA_TRY(cudaMemset(p.knew, 0, 4 * (size_t)m->kv_n));
+    Q4_CUDA_TRY(cudaMemset(p.vnew, 0, 4 * (size_t)m->kv_n));
     FTRY(fused_alloc(f, (void**)&p.attn_part, sizeof(float) * (size_t)c.n_heads * p.nsplit * kAttnPartStride));
     FTRY(fused_alloc(f, (void**)&p.attn_cnt, sizeof(unsigned) * c.n_heads));
     {
@@ -1183,11 +1355,12 @@ int q4_fused_prepare(q4_model* m) {
     FTRY(fused_alloc(f, (void**)&p.cand_val, sizeof(float) * sms));
     FTRY(fused_alloc(f, (void**)&p.cand_idx, sizeof(int) * sms));
     FTRY(fused_alloc(f, (void**)&p.bar_counter, sizeof(unsigned long long)));
-    FTRY(fused_alloc(f, (void**)&p.status, sizeof(int)));
+    FTRY(fused_alloc(f, (void**)&p.status, (4 + 4 * 256) * sizeof(int)));
 
     std::vector<FPhase> ph;
     int max_K = c.dim, max_part = 0, nbar = 0;
-    auto gemv_phase = [&](int K, const __half* xin, const __half* norm_w, int epi) {
+    int x_writer = 0;  // index of the phase that last wrote the residual stream x
+    auto gemv_phase = [&](int K, const uint32_t* xin, int in_phase, const __half* norm_w, int epi) {
         FPhase a;
         memset(&a, 0, sizeof(a));
         a.type = PH_GEMV;
@@ -1195,6 +1368,7 @@ int q4_fused_prepare(q4_model* m) {
         a.G = q4_groups(K);
         a.nkt = q4_div_up(a.G, kSlotGroups);
         a.xin = xin;
+        a.in_phase = in_phase;
         a.norm_w = norm_w;
         a.epi = epi;
         a.tpu = 1;
@@ -1205,14 +1379,15 @@ int q4_fused_prepare(q4_model* m) {
         max_part = std::max(max_part, max_units * a.tpu * a.nkt * 8);
         max_K = std::max(max_K, a.K);
         ph.push_back(a);
-        nbar++;
+        if (a.barrier_after) nbar++;
+        return (int)ph.size() - 1;
     };
     {
         FPhase a;
         memset(&a, 0, sizeof(a));
-        a.type = PH_EMBED;
+        a.type = PH_EMBED;  // writes x tagged; no barrier
         ph.push_back(a);
-        nbar++;
+        x_writer = 0;
     }
     for (int l = 0; l < c.n_layers; l++) {
         const DevLayer& L = m->layers[l];
@@ -1220,48 +1395,52 @@ int q4_fused_prepare(q4_model* m) {
         const uint8_t *sq, *sk, *sv, *so, *sg, *su, *sd;
         FTRY(make_stream(f, L.q, &sq)); FTRY(make_stream(f, L.k, &sk)); FTRY(make_stream(f, L.v, &sv)); FTRY(make_stream(f, L.o, &so));
         FTRY(make_stream(f, L.gate, &sg)); FTRY(make_stream(f, L.up, &su)); FTRY(make_stream(f, L.down, &sd));
-        {   // QKV (+ attention RMSNorm): q -> q, k -> knew (rotated and filed by the attention phase), v -> cache row
-            FPhase a = gemv_phase(c.dim, p.x, (const __half*)L.rms_att, EPI_STORE);
+        int qkv_phase;
+        {   // QKV (+ attention RMSNorm): q, k, v -> tagged staging vectors; v also straight into its cache row
+            FPhase a = gemv_phase(c.dim, p.x, x_writer, (const __half*)L.rms_att, EPI_STORE);
             a.nmat = 3;
-            a.m[0] = FMat{sq, p.q, m->q_n, 0, 0};
-            a.m[1] = FMat{sk, p.knew, m->kv_n, m->q_n / 8, 0};
-            a.m[2] = FMat{sv, p.vc, m->kv_n, m->q_n / 8 + m->kv_n / 8, 1};
+            a.m[0] = FMat{sq, p.q, nullptr, m->q_n, 0};
+            a.m[1] = FMat{sk, p.knew, nullptr, m->kv_n, m->q_n / 8};
+            a.m[2] = FMat{sv, p.vnew, p.vc, m->kv_n, m->q_n / 8 + m->kv_n / 8};
             a.nunits = m->q_n / 8 + 2 * (m->kv_n / 8);
             a.loff = loff;
-            finish(a);
+            qkv_phase = finish(a);
         }
-        {
+        {   // attention: waits on the tags of q / knew / vnew; a grid barrier follows (its partials are plain floats)
             FPhase a;
             memset(&a, 0, sizeof(a));
             a.type = PH_ATTN;
             a.loff = loff;
             a.layer = l;
+            a.in_phase = qkv_phase;
+            a.barrier_after = 1;
             ph.push_back(a);
             nbar++;
         }
         {   // O projection + residual
-            FPhase a = gemv_phase(m->o_kc, p.xb, nullptr, EPI_RESIDUAL);
+            FPhase a = gemv_phase(m->o_kc, nullptr, 0, nullptr, EPI_RESIDUAL);
             a.attn_in = 1;
             a.nmat = 1;
-            a.m[0] = FMat{so, p.x, c.dim, 0, 0};
+            a.m[0] = FMat{so, p.x, nullptr, c.dim, 0};
             a.nunits = c.dim / 8;
-            finish(a);
+            x_writer = finish(a);
         }
+        int silu_phase;
         {   // gate/up + SiLU (+ ffn RMSNorm): unit = gate tile + the same up tile
-            FPhase a = gemv_phase(c.dim, p.x, (const __half*)L.rms_ffn, EPI_SILU);
+            FPhase a = gemv_phase(c.dim, p.x, x_writer, (const __half*)L.rms_ffn, EPI_SILU);
             a.nmat = 2;
-            a.m[0] = FMat{sg, p.hb, m->h_kc, 0, 0};
-            a.m[1] = FMat{su, p.hb, m->h_kc, 0, 0};
+            a.m[0] = FMat{sg, p.hb, nullptr, m->h_kc, 0};
+            a.m[1] = FMat{su, p.hb, nullptr, m->h_kc, 0};
             a.nunits = m->h_kc / 8;
             a.tpu = 2;
-            finish(a);
+            silu_phase = finish(a);
         }
         {   // down projection + residual
-            FPhase a = gemv_phase(m->h_kc, p.hb, nullptr, EPI_RESIDUAL);
+            FPhase a = gemv_phase(m->h_kc, p.hb, silu_phase, nullptr, EPI_RESIDUAL);
             a.nmat = 1;
-            a.m[0] = FMat{sd, p.x, c.dim, 0, 0};
+            a.m[0] = FMat{sd, p.x, nullptr, c.dim, 0};
             a.nunits = c.dim / 8;
-            finish(a);
+            x_writer = finish(a);
         }
     }
     {
@@ -1271,8 +1450,10 @@ int q4_fused_prepare(q4_model* m) {
         a.K = c.dim;
         a.nkt = q4_div_up(c.dim, kClsChunk);
         a.xin = p.x;
+        a.in_phase = x_writer;
         a.norm_w = (const __half*)m->rms_final;
         a.nunits = m->v_n / 2;  // row pairs
+        a.barrier_after = 1;
         max_part = std::max(max_part, q4_div_up(a.nunits, sms) * 2 * a.nkt);
         ph.push_back(a);
         nbar++;
@@ -1339,6 +1520,7 @@ int q4_fused_forward(q4_model* m, cudaStream_t s, int gen_token) {
         p.l2_ahead = la ? atoi(la) : 0;  // measured: requesting weights into L2 ahead of the ring slows the stream down
     }
     p.bar_base = f->launches * (unsigned long long)f->barriers_per_launch;
+    p.tag_base = (unsigned)((f->launches * (unsigned long long)f->nphases) & 0xFFFFu);
     f->launches++;
     void* args[] = {&p};
     Q4_CUDA_TRY(cudaLaunchCooperativeKernel((void*)fused_token_kernel, dim3(f->grid), dim3(kThreads), args, f->smem_bytes, s));
