@@ -35,8 +35,8 @@ namespace {
 constexpr int kSlotGroups = 16;
 constexpr int kUnitBytes = 544;
 constexpr int kSlotBytes = kSlotGroups * kUnitBytes;  // 8704
-constexpr int kSlots = 16;
-constexpr int kEntries = kSlots / 2;               // ring entries: two slots each, filled by one bulk copy
+constexpr int kMaxEntries = 12;                    // ring entries: two slots each, filled by one bulk copy; the host picks
+constexpr int kMinEntries = 4;                     // as many as fit next to the activation buffers (p.n_entries)
 constexpr int kEntryBytes = 2 * kSlotBytes;
 #ifndef Q4_FUSED_CW
 #define Q4_FUSED_CW 11
@@ -85,7 +85,20 @@ struct FPhase {
 };
 static_assert(sizeof(FPhase) % 16 == 0, "FPhase is copied in 16-byte pieces");
 
+// One ring entry's copy, precomputed per CTA when the model is prepared (the list is the same for every token):
+// the single producer thread only has to wait for a free entry and issue it.
+struct CopyDesc {
+    const uint8_t* src0;
+    const uint8_t* src1;   // second piece when the entry's two slots are not adjacent in memory, else null
+    uint32_t bytes0, bytes1;
+    uint32_t pad[2];
+};
+static_assert(sizeof(CopyDesc) == 32, "CopyDesc is loaded as two 128-bit words");
+
 struct FParams {
+    const CopyDesc* desc;    // [grid][desc_stride]
+    const int* desc_count;   // [grid]
+    int desc_stride;
     const FPhase* phases;
     int nphases;
     q4_config cfg;
@@ -115,6 +128,7 @@ struct FParams {
     int write_token;
     int debug;                   // measurement only: 1 = consumers skip the GEMV math (pure streaming), 2 = no streaming (pure math)
     int l2_ahead;                // slots each producer keeps requested into L2 beyond the ring
+    int n_entries;               // ring entries of kEntryBytes each
     int split_len;               // positions per attention split (a head is split in ceil(T / split_len) parts, at most nsplit)
     unsigned long long* trace;   // optional: [2 CTAs][nphases][4] device timestamps (ns), or null
     // shared memory carve-up (bytes)
@@ -671,15 +685,14 @@ __device__ __forceinline__ void gemv_slot(const uint8_t* slot, int ng, int kt, c
 // ------------------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ uint64_t full_bar[kEntries], empty_bar[kEntries];
+    __shared__ uint64_t full_bar[kMaxEntries], empty_bar[kMaxEntries];
+    const int kEntries = p.n_entries;
     __shared__ float red[kCW];
     __shared__ int s_abort;
-    __shared__ unsigned s_ring_seq;   // slots the ring cursor has issued (read by the L2 cursor)
-    __shared__ __align__(16) FPhase s_pph[2];  // producer cursors' phase descriptors
     __shared__ __align__(16) FPhase s_cph;     // consumers' phase descriptor
 
     uint8_t* ring = smem;
-    uint4* xq = reinterpret_cast<uint4*>(smem + kSlots * kSlotBytes);
+    uint4* xq = reinterpret_cast<uint4*>(smem + (size_t)p.n_entries * kEntryBytes);
     float* xs_scale = reinterpret_cast<float*>(smem + p.meta_off);
     int* xs_sum = reinterpret_cast<int*>(smem + p.meta_off) + 32 * 16;   // up to 16 k-tiles... sized by host
     float* part = reinterpret_cast<float*>(smem + p.part_off);
@@ -689,8 +702,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
 
     if (tid == 0) {
         s_abort = 0;
-        s_ring_seq = 0;
-        for (int s = 0; s < kEntries; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 2); }
+        for (int s = 0; s < kMaxEntries; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 2); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -702,89 +714,49 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
         // streaming while the ring is full and the consumers sit in a barrier. After the last slot the L2 cursor wraps
         // around: the next token's first slots are already on their way when its kernel starts.
         if (p.debug & 2) return;
-        const uint8_t* src;
-        uint32_t bytes;
-        int phase;
-        if (lane != 0) {
-            // L2 cursor: lanes 1..31 walk the same slot list p.l2_ahead slots in front of the ring cursor and request the
-            // bytes into L2 with plain prefetch instructions (the bulk-copy engine is kept for the ring: a bulk
-            // prefetch costs it as much as a copy). After the last slot the cursor wraps once, so the next token's
-            // first slots are already on their way when its kernel starts.
-            if (p.l2_ahead <= 0) return;
-            SlotCursor c;
-            cursor_init(c);
-            c.cache = &s_pph[1];
-            unsigned issued = 0;
-            unsigned long long t0 = 0;
-            for (;;) {
-                if (!cursor_next(c, p, cta, grid, src, bytes, phase)) {
-                    if (c.wrapped) return;
-                    cursor_init(c);
-                    c.wrapped = 1;
-                    continue;
-                }
-                if (c.wrapped && c.count > p.l2_ahead) return;
-                unsigned spins = 0;
-                while (!c.wrapped && issued >= 2u * *(volatile unsigned*)&s_ring_seq + (unsigned)p.l2_ahead) {
-                    __nanosleep(200);
-                    if ((++spins & 255u) == 0) {
-                        const unsigned long long now = global_ns();
-                        if (t0 == 0) t0 = now;
-                        if (now - t0 > kWaitLimitNs || *(volatile int*)p.status != 0) return;
-                    }
-                }
-                t0 = 0;
-                if (p.debug & 4) {
-                    // experiment: real loads (cannot be dropped) instead of prefetch hints
-                    for (uint32_t off = (lane - 1) * 16u; off < bytes; off += 31u * 16u) {
-                        uint32_t a, b, c2, d;
-                        asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a), "=r"(b), "=r"(c2), "=r"(d) : "l"(src + off));
-                    }
-                } else {
-                    for (uint32_t off = (lane - 1) * 128u; off < bytes; off += 31u * 128u)
-                        asm volatile("prefetch.global.L2 [%0];" ::"l"(src + off));
-                }
-                issued++;
-            }
-        }
-        // Ring cursor: one entry = two consecutive slots of the same phase (one bulk copy when they are adjacent in memory,
-        // which they are inside a CTA's contiguous share of a matrix). The second slot lands right behind the first.
-        SlotCursor rc;
-        cursor_init(rc);
-        rc.cache = &s_pph[0];
+        // The whole warp walks this CTA's precomputed copy list: 32 descriptors are fetched at a time (one per lane),
+        // then lane 0 issues them one by one as ring entries free up. One entry = two consecutive slots of a phase,
+        // one bulk copy when they are adjacent in memory.
+        const CopyDesc* dl = p.desc + (size_t)cta * p.desc_stride;
+        const int nd = p.desc_count[cta];
         unsigned ent = 0;
-        bool have = cursor_next(rc, p, cta, grid, src, bytes, phase);
-        while (have) {
-            const uint8_t* srcA = src;
-            const uint32_t bytesA = bytes;
-            const int phaseA = phase;
-            have = cursor_next(rc, p, cta, grid, src, bytes, phase);
-            const bool pair = have && phase == phaseA;
-            const int e = ent % kEntries;
-            if (!mbar_wait(&empty_bar[e], ((ent / kEntries) & 1) ^ 1, p.status)) break;
-            uint8_t* dst = ring + (size_t)e * kEntryBytes;
-            if (pair) {
-                mbar_expect_tx(&full_bar[e], bytesA + bytes);
-                if (src == srcA + bytesA) {
-                    bulk_g2s(dst, srcA, bytesA + bytes, &full_bar[e]);
-                } else {
-                    bulk_g2s(dst, srcA, bytesA, &full_bar[e]);
-                    bulk_g2s(dst + bytesA, src, bytes, &full_bar[e]);
-                }
-                have = cursor_next(rc, p, cta, grid, src, bytes, phase);
-            } else {
-                mbar_expect_tx(&full_bar[e], bytesA);
-                bulk_g2s(dst, srcA, bytesA, &full_bar[e]);
+        bool ok = true;
+        for (int base = 0; base < nd && ok; base += 32) {
+            uint4 d0 = make_uint4(0, 0, 0, 0), d1 = d0;
+            if (base + lane < nd) {
+                const uint4* dp = reinterpret_cast<const uint4*>(dl + base + lane);
+                d0 = __ldg(dp);
+                d1 = __ldg(dp + 1);
             }
-            ent++;
-            *(volatile unsigned*)&s_ring_seq = ent;
+            const int cnt = min(32, nd - base);
+            for (int i = 0; i < cnt; i++) {
+                const uint32_t s0l = __shfl_sync(0xffffffffu, d0.x, i), s0h = __shfl_sync(0xffffffffu, d0.y, i);
+                const uint32_t s1l = __shfl_sync(0xffffffffu, d0.z, i), s1h = __shfl_sync(0xffffffffu, d0.w, i);
+                const uint32_t b0 = __shfl_sync(0xffffffffu, d1.x, i), b1 = __shfl_sync(0xffffffffu, d1.y, i);
+                int good = 1;
+                if (lane == 0) {
+                    const int e = ent % kEntries;
+                    if (!mbar_wait(&empty_bar[e], ((ent / kEntries) & 1) ^ 1, p.status)) {
+                        good = 0;
+                    } else {
+                        uint8_t* dst = ring + (size_t)e * kEntryBytes;
+                        const uint8_t* src0 = reinterpret_cast<const uint8_t*>(((unsigned long long)s0h << 32) | s0l);
+                        mbar_expect_tx(&full_bar[e], b0 + b1);
+                        bulk_g2s(dst, src0, b0, &full_bar[e]);
+                        if (b1) bulk_g2s(dst + b0, reinterpret_cast<const uint8_t*>(((unsigned long long)s1h << 32) | s1l), b1, &full_bar[e]);
+                        ent++;
+                    }
+                }
+                good = __shfl_sync(0xffffffffu, good, 0);
+                if (!good) { ok = false; break; }
+            }
         }
-        *(volatile unsigned*)&s_ring_seq = 0x3fffffffu;
+        if (lane != 0) return;
         // Before this thread (the last owner of the CTA's shared memory as far as the copy engine is concerned) leaves:
         // every bulk copy it issued must have landed. On the normal path the consumers have waited for all of them
         // already; after an error the newest copy of each ring entry may still be in flight.
         if (*(volatile int*)p.status != 0) {
-            const unsigned first = ent > (unsigned)kEntries ? ent - kEntries : 0;
+            const unsigned first = ent > (unsigned)kEntries ? ent - (unsigned)kEntries : 0;
             for (unsigned i = first; i < ent; i++) {
                 const unsigned long long t0 = global_ns();
                 while (!mbar_try(&full_bar[i % kEntries], (i / kEntries) & 1)) {
@@ -816,6 +788,24 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
         if (ph.next_norm_w && cta == pi % grid && ctid * 64 < ph.next_norm_n)
             asm volatile("prefetch.global.L2 [%0];" ::"l"(ph.next_norm_w + ctid * 64));
 
+        if (p.debug & 8) {
+            // measurement only: raw ring throughput over the real weight layout (no staging, no math, no barriers)
+            if (ph.type == PH_GEMV || ph.type == PH_CLS) {
+                const int tpu = ph.type == PH_GEMV ? ph.tpu : 2;
+                const int nslots = unit_count(ph.nunits, cta, grid) * tpu * ph.nkt;
+                const unsigned first = (cw + kCW - (sbase % kCW)) % kCW;
+                for (unsigned li = first; li < (unsigned)nslots; li += kCW) {
+                    const unsigned en = ent0 + (li >> 1);
+                    const int e = en % kEntries;
+                    if (failed || !mbar_wait(&full_bar[e], (en / kEntries) & 1, p.status)) { failed = true; continue; }
+                    if (lane == 0) mbar_arrive(&empty_bar[e], (!(li & 1) && li + 1 == (unsigned)nslots) ? 2 : 1);
+                }
+                sbase += nslots;
+                ent0 += (nslots + 1) >> 1;
+            }
+            consumer_sync();
+            continue;
+        }
         if (ph.type == PH_EMBED) {
             // copy_embedding_kernel (gpu_kernels.h:61-69): the token id comes from the pinned host mailbox
             if (cta * kCT + ctid < p.cfg.dim / 8) {
@@ -1219,6 +1209,39 @@ __global__ void rope_table_kernel(float2* out, int seq_len, int head_size, float
     out[i] = make_float2(cosf(val), sinf(val));
 }
 
+// Builds the per-CTA copy lists with the same cursor the consumers' slot arithmetic mirrors: entries never span a
+// phase, two consecutive slots of a phase share an entry. One thread per CTA of the decode kernel; runs once.
+__global__ void build_desc_kernel(const FParams p, CopyDesc* desc, int* desc_count, int grid) {
+    __shared__ __align__(16) FPhase cache;
+    const int cta = blockIdx.x;
+    SlotCursor rc;
+    cursor_init(rc);
+    rc.cache = &cache;
+    const uint8_t* src;
+    uint32_t bytes;
+    int phase;
+    CopyDesc* out = desc + (size_t)cta * p.desc_stride;
+    int n = 0;
+    bool have = cursor_next(rc, p, cta, grid, src, bytes, phase);
+    while (have && n < p.desc_stride) {
+        CopyDesc d;
+        d.src0 = src;
+        d.bytes0 = bytes;
+        d.src1 = nullptr;
+        d.bytes1 = 0;
+        d.pad[0] = d.pad[1] = 0;
+        const int phaseA = phase;
+        have = cursor_next(rc, p, cta, grid, src, bytes, phase);
+        if (have && phase == phaseA) {
+            if (src == d.src0 + d.bytes0) d.bytes0 += bytes;
+            else { d.src1 = src; d.bytes1 = bytes; }
+            have = cursor_next(rc, p, cta, grid, src, bytes, phase);
+        }
+        out[n++] = d;
+    }
+    desc_count[cta] = have ? -1 : n;  // -1: list too short (host bug)
+}
+
 size_t stream_bytes(int K, int N) { return (size_t)(N / 8) * q4_groups(K) * kUnitBytes; }
 
 }  // namespace
@@ -1477,6 +1500,26 @@ int q4_fused_prepare(q4_model* m) {
     p.phases = f->d_phases;
     p.nphases = f->nphases;
     f->barriers_per_launch = nbar;
+    {   // per-CTA copy lists
+        long long max_slots = 0;
+        for (const FPhase& a : ph) {
+            if (a.type == PH_GEMV) max_slots += ((long long)q4_div_up(a.nunits, sms) * a.tpu * a.nkt + 1) / 2 + 1;
+            if (a.type == PH_CLS) max_slots += ((long long)q4_div_up(a.nunits, sms) * 2 * a.nkt + 1) / 2 + 1;
+        }
+        p.desc_stride = (int)max_slots + 8;
+        CopyDesc* d = nullptr;
+        int* dc = nullptr;
+        FTRY(fused_alloc(f, (void**)&d, sizeof(CopyDesc) * (size_t)p.desc_stride * sms));
+        FTRY(fused_alloc(f, (void**)&dc, sizeof(int) * sms));
+        build_desc_kernel<<<sms, 1>>>(p, d, dc, sms);
+        Q4_CUDA_TRY(cudaGetLastError());
+        std::vector<int> counts(sms);
+        Q4_CUDA_TRY(cudaMemcpy(counts.data(), dc, sizeof(int) * sms, cudaMemcpyDeviceToHost));
+        for (int cnt : counts)
+            if (cnt < 0) { f->unsupported = true; return Q4_ERR_UNSUPPORTED_SIZE; }
+        p.desc = d;
+        p.desc_count = dc;
+    }
 
     // shared memory: ring | xq (or attention / classifier scratch) | x scales + sums | partial sums
     const int max_G = q4_groups(max_K), max_kt = q4_div_up(max_G, kSlotGroups);
@@ -1484,13 +1527,20 @@ int q4_fused_prepare(q4_model* m) {
     xq_bytes = std::max(xq_bytes, (int)((2 * kAG + kAG * 128) * sizeof(float)));  // attention scratch
     xq_bytes = std::max(xq_bytes, 2 * c.dim);                                 // classifier x
     p.xq_bytes = (int)align_up(xq_bytes, 128);
-    p.meta_off = kSlots * kSlotBytes + p.xq_bytes;
     const int meta_bytes = 32 * 16 * 4 * 2;   // 16 k-tiles x 32 lanes, scale + sum
     if (max_kt > 16) { f->unsupported = true; return Q4_ERR_UNSUPPORTED_SIZE; }
-    p.part_off = p.meta_off + meta_bytes;
     p.part_floats = std::max(max_part, 64);
+    // the ring gets whatever shared memory the activation buffers leave (227 KB per CTA, 1 KB kept for static data)
+    const size_t other = (size_t)p.xq_bytes + meta_bytes + sizeof(float) * p.part_floats;
+    const size_t budget = 226 * 1024;
+    int n_entries = other < budget ? (int)((budget - other) / kEntryBytes) : 0;
+    n_entries = std::min(n_entries, kMaxEntries);
+    if (n_entries < kMinEntries) { f->unsupported = true; return Q4_ERR_UNSUPPORTED_SIZE; }
+    if (const char* ne = getenv("Q4_FUSED_ENTRIES")) n_entries = std::max(kMinEntries, std::min(n_entries, atoi(ne)));
+    p.n_entries = n_entries;
+    p.meta_off = n_entries * kEntryBytes + p.xq_bytes;
+    p.part_off = p.meta_off + meta_bytes;
     f->smem_bytes = (size_t)p.part_off + sizeof(float) * p.part_floats;
-    if (f->smem_bytes > 227 * 1024) { f->unsupported = true; return Q4_ERR_UNSUPPORTED_SIZE; }
     Q4_CUDA_TRY(cudaFuncSetAttribute(fused_token_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)f->smem_bytes));
     int per_sm = 0;
     Q4_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_token_kernel, kThreads, f->smem_bytes));
