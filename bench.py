@@ -222,6 +222,14 @@ def main():
     t = Transformer(path, rank=rank, gpu_count=world, tp_mode=_lib.Q4_TP_HYBRID if world > 1 else _lib.Q4_TP_NONE,
                     comm=comm.handle if comm else None)
     fwd_path = args.path if args.path >= 0 else t.best_path()
+    if fwd_path == 2 and t.best_path() != 2:
+        raise SystemExit("--path 2: the fused path does not serve this model")
+    if dist is not None:
+        # all ranks take the same path, and with the fused path (whose kernels exchange activations between the
+        # ranks) every rank is prepared before any rank launches
+        fp = torch.tensor([fwd_path], device="cuda")
+        dist.all_reduce(fp, op=dist.ReduceOp.MIN)
+        fwd_path = int(fp.item())
 
     def barrier():
         if dist is not None:

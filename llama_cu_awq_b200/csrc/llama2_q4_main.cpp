@@ -3,10 +3,11 @@
 // through its C ABI only. One host thread per GPU, as in the reference (llama2_q4.cu:776-779).
 //
 // Extra flags (not in the reference): -k <file> reads whitespace-separated prompt token ids instead of text,
-// -g <0|1> picks the forward path (per-op launches / CUDA-graph replay).
+// -g <0|1|2> picks the forward path (per-op launches / CUDA-graph replay / persistent fused kernel).
 #include <cuda_runtime_api.h>
 
 #include <algorithm>
+#include <atomic>
 #include <chrono>
 #include <cstdio>
 #include <cstdlib>
@@ -113,7 +114,7 @@ private:
     fprintf(stderr, "  -q <string> dataset file for computing perplexity\n");
     fprintf(stderr, "  -x <string> tensor parallel mode: none|column|hybrid, default none\n");
     fprintf(stderr, "  -k <string> path to a file of prompt token ids (replaces -i/-f)\n");
-    fprintf(stderr, "  -g <int>    forward path: 0 per-op launches, 1 CUDA graph (default)\n");
+    fprintf(stderr, "  -g <int>    forward path: 0 per-op launches, 1 CUDA graph, 2 persistent fused kernel (default; falls back to 1)\n");
     exit(EXIT_FAILURE);
 }
 
@@ -147,9 +148,10 @@ struct Shared {
     q4_comm_id* id = nullptr;
     std::vector<q4_model*> models;
     std::vector<q4_comm*> comms;
+    std::atomic<int> fused_ok{1};   // cleared by any rank whose model the fused path does not serve
 };
 
-void load_thread(Shared* sh, const char* path, int rank, int gpu_count, int tp_mode) {
+void load_thread(Shared* sh, const char* path, int rank, int gpu_count, int tp_mode, int fwd_path) {
     cudaSetDevice(rank);
     q4_comm* comm = nullptr;
     if (gpu_count > 1) {
@@ -159,6 +161,9 @@ void load_thread(Shared* sh, const char* path, int rank, int gpu_count, int tp_m
     sh->comms[rank] = comm;
     int e = q4_model_load(&sh->models[rank], path, rank, gpu_count, tp_mode, comm);
     if (e) die(e, "build_transformer");
+    // The fused path is prepared here, before the join that all ranks pass: its kernels exchange activations between
+    // the ranks, so every rank must be ready before any rank launches.
+    if (fwd_path == 2 && q4_model_prepare(sh->models[rank], 2) != Q4_OK) sh->fused_ok = 0;
 }
 
 // The token loop of generate_thread (llama2_q4.cu:683-757) with rank 0 streaming the text.
@@ -207,7 +212,7 @@ int main(int argc, char* argv[]) {
     const char* tokenizer_path = "tokenizer.bin";
     const char* dataset_path = nullptr;
     const char* token_file = nullptr;
-    int steps = 0, fwd_path = 1;
+    int steps = 0, fwd_path = 2;
     std::string prompt;
     bool have_prompt = false;
     float temperature = 0.5f, topp = 0.6f;  // the reference's defaults in code (llama2_q4.cu:852-853)
@@ -283,9 +288,10 @@ int main(int argc, char* argv[]) {
     }
     {
         std::vector<std::thread> th;
-        for (int r = 0; r < gpu_count; r++) th.emplace_back(load_thread, &sh, checkpoint_path, r, gpu_count, tp_mode);
+        for (int r = 0; r < gpu_count; r++) th.emplace_back(load_thread, &sh, checkpoint_path, r, gpu_count, tp_mode, fwd_path);
         for (auto& t : th) t.join();
     }
+    if (fwd_path == 2 && !sh.fused_ok) fwd_path = 1;   // shapes the fused kernel does not serve: CUDA-graph replay
     if (steps <= 0 || steps > cfg.seq_len) steps = cfg.seq_len;
 
     Vocab vocab;

@@ -16,7 +16,7 @@
 #include <mutex>
 #include <string.h>
 
-#include "q4_common.cuh"
+#include "q4_comm_internal.h"
 
 namespace {
 constexpr unsigned long long kWaitLimitNs = 2000ULL * 1000 * 1000;  // 2 s on the device's global timer
@@ -28,6 +28,7 @@ struct Inbox {
     uint32_t status;   // 0 or Q4_ERR_TIMEOUT
     uint32_t pad[14];
     __half slots[2][Q4_MAX_GPUS][Q4_COMM_MAX_HALFS];
+    Q4LLArea ll;       // exchange area of the fused decode kernel
 };
 
 struct PeerPtrs { Inbox* p[Q4_MAX_GPUS]; };
@@ -126,6 +127,13 @@ int alloc_inbox(Inbox** out) {
 }
 
 }  // namespace
+
+int q4_comm_world(const q4_comm* c) { return c ? c->gpu_count : 1; }
+int q4_comm_rank(const q4_comm* c) { return c ? c->rank : 0; }
+Q4LLArea* q4_comm_ll_area(const q4_comm* c, int peer) {
+    if (!c || peer < 0 || peer >= c->gpu_count || !c->peers.p[peer]) return nullptr;
+    return &c->peers.p[peer]->ll;
+}
 
 extern "C" int q4_comm_id_create(q4_comm_id** id, int gpu_count) {
     if (!id || gpu_count < 1 || gpu_count > Q4_MAX_GPUS) return Q4_ERR_INVALID;

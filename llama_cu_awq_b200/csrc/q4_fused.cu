@@ -28,6 +28,7 @@
 #include <stdio.h>
 #include <stdlib.h>
 
+#include "q4_comm_internal.h"
 #include "q4_model.h"
 
 namespace {
@@ -73,6 +74,7 @@ struct FPhase {
     int barrier_after;      // 1: grid barrier after this phase (else the consumers of its output wait on the tags)
     const __half* norm_w;   // RMSNorm weight applied while staging x, or null
     int nmat;
+    int xbuf_out;           // EPI_RESIDUAL: residual-stream buffer this phase writes (it reads the other one)
     FMat m[3];
     int nunits, tpu;        // work units of the phase and tiles per unit (2 for gate/up pairs)
     int epi;
@@ -80,7 +82,7 @@ struct FPhase {
     int layer;
     int attn_in;            // GEMV: the input vector is the attention output, still split: merge the partials while staging
     int next_norm_n;        // elements of next_norm_w
-    int pad_;
+    int xbuf_in;            // 0/1: the input is that buffer of the residual stream (sum of the ranks' partials); -1: xin
     const __half* next_norm_w;  // RMSNorm weight of the next phase that has one: requested into L2 one phase early
 };
 static_assert(sizeof(FPhase) % 16 == 0, "FPhase is copied in 16-byte pieces");
@@ -110,13 +112,26 @@ struct FParams {
     // themselves until all carry the expected tag, so most op boundaries need no grid barrier: one L2 round trip
     // instead of fence + arrive + poll. A buffer is rewritten only after every CTA has provably read it (the next
     // writer's own input wait, or the barrier kept after attention, implies it).
-    uint32_t *x, *hb, *q, *knew, *vnew;
+    //
+    // The residual stream is the one vector that all ranks of a tensor-parallel group share. It lives in the exchange
+    // area of the communicator as g partial vectors ("slots", one per source rank) in two alternating buffers:
+    // buffer 1 is written by the embedding and by every down projection, buffer 0 by every o projection. A rank's
+    // epilogue stores half(own partial sum + old x / g) into its slot on EVERY rank (plain peer stores, tagged), and
+    // a reader sums the g slots in rank order in fp32: that is the all-reduce of cuda_comm.h:203-300 without a
+    // separate step, and every rank computes bit-identical sums. A buffer is rewritten only after all ranks have
+    // provably read it: a writer of buffer b has consumed, from every rank, data that those ranks produced after
+    // their last read of b (see the ordering notes at the epilogue).
+    uint32_t* xb[2][Q4_MAX_GPUS];      // [buffer][rank p]: buffer base (g slots of kLLMaxDim words) in rank p's exchange area
+    unsigned long long* cand[Q4_MAX_GPUS];  // rank p's candidate mailbox [2][Q4_MAX_GPUS][2]
+    uint16_t* ll_logits[Q4_MAX_GPUS];  // rank p's gathered logits
+    int g, rank, vocab_off;
+    unsigned launch_parity;
+    uint32_t *hb, *q, *knew, *vnew;
     unsigned tag_base;
     __half *logits, *kc, *vc;
     const __half *emb, *wcls;
     const float* rope;       // [seq_len][head_size/2] (cos, sin)
-    float* attn_part;        // [heads*nsplit][head_size + 2]
-    unsigned* attn_cnt;      // [heads]
+    float* attn_part;        // [heads*nsplit][kAttnPartStride]
     float* cand_val;         // [grid]
     int* cand_idx;           // [grid]
     int* pos_dev;
@@ -127,7 +142,6 @@ struct FParams {
     int* status;
     int write_token;
     int debug;                   // measurement only: 1 = consumers skip the GEMV math (pure streaming), 2 = no streaming (pure math)
-    int l2_ahead;                // slots each producer keeps requested into L2 beyond the ring
     int n_entries;               // ring entries of kEntryBytes each
     int split_len;               // positions per attention split (a head is split in ceil(T / split_len) parts, at most nsplit)
     unsigned long long* trace;   // optional: [2 CTAs][nphases][4] device timestamps (ns), or null
@@ -327,6 +341,66 @@ __device__ __forceinline__ bool keep_polling(unsigned& polls, unsigned long long
     return true;
 }
 
+// Words wd[b] (8 elements each) of the residual stream: waits for the g partial vectors (one per source rank) and sums
+// them in rank order in fp32, rounded to fp16 once - the arithmetic of a fixed-order all-reduce. Two slots are in
+// flight per round trip, so the registers stay bounded for any g.
+template <int NB>
+__device__ __forceinline__ void load_x_batch(uint4 (&xv)[NB], const bool (&valid)[NB], const int (&wd)[NB], const uint32_t* base, int g,
+                                             uint32_t want, int* status, int where) {
+    unsigned polls = 0;
+    unsigned long long t0 = 0;
+    if (g == 1) {
+        for (;;) {
+            uint32_t bad = 0;
+#pragma unroll
+            for (int b = 0; b < NB; b++) {
+                xv[b] = make_uint4(0, 0, 0, 0);
+                if (valid[b]) xv[b] = load_tagged8(base + wd[b] * 8, want, bad);
+            }
+            if (bad == 0 || !keep_polling(polls, t0, status, where)) break;
+        }
+        return;
+    }
+    float acc[NB][8];
+#pragma unroll
+    for (int b = 0; b < NB; b++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[b][j] = 0.f;
+    for (int r0 = 0; r0 < g; r0 += 2) {
+        const bool two = r0 + 1 < g;
+        uint4 a[NB], c[NB];
+        for (;;) {
+            uint32_t bad = 0;
+#pragma unroll
+            for (int b = 0; b < NB; b++) {
+                a[b] = c[b] = make_uint4(0, 0, 0, 0);
+                if (valid[b]) {
+                    a[b] = load_tagged8(base + (size_t)r0 * kLLMaxDim + wd[b] * 8, want, bad);
+                    if (two) c[b] = load_tagged8(base + (size_t)(r0 + 1) * kLLMaxDim + wd[b] * 8, want, bad);
+                }
+            }
+            if (bad == 0 || !keep_polling(polls, t0, status, where)) break;
+        }
+#pragma unroll
+        for (int b = 0; b < NB; b++) {
+            const __half2* ha = reinterpret_cast<const __half2*>(&a[b]);
+            const __half2* hc = reinterpret_cast<const __half2*>(&c[b]);
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const float2 fa = __half22float2(ha[j]), fc = __half22float2(hc[j]);
+                acc[b][2 * j] += fa.x; acc[b][2 * j + 1] += fa.y;
+                if (two) { acc[b][2 * j] += fc.x; acc[b][2 * j + 1] += fc.y; }
+            }
+        }
+    }
+#pragma unroll
+    for (int b = 0; b < NB; b++) {
+        __half2* oh = reinterpret_cast<__half2*>(&xv[b]);
+#pragma unroll
+        for (int j = 0; j < 4; j++) oh[j] = __floats2half2_rn(acc[b][2 * j], acc[b][2 * j + 1]);
+    }
+}
+
 // Walks the slots of one CTA in issue order: phase by phase, unit by unit, tile by tile, k-tile by k-tile.
 // The consumers enumerate the same order with plain arithmetic.
 struct SlotCursor {
@@ -514,17 +588,16 @@ __device__ void stage_x_quant(const FPhase& ph, const FParams& p, int pos, uint4
             if (ph.norm_w && it0 + b < iters && wd < nwords && wd * 8 < K) wv[b] = *reinterpret_cast<const uint4*>(ph.norm_w + wd * 8);
         }
         // the input words carry the producing phase's tag: poll them until all have arrived (this is the op boundary)
-        unsigned polls = 0;
-        unsigned long long t0 = 0;
-        for (;;) {
-            uint32_t bad = 0;
+        {
+            bool valid[kBatch];
+            int wds[kBatch];
 #pragma unroll
             for (int b = 0; b < kBatch; b++) {
-                const int wd = ctid + (it0 + b) * kCT;
-                xv[b] = make_uint4(0, 0, 0, 0);
-                if (it0 + b < iters && wd < nwords && wd * 8 < K) xv[b] = load_tagged8(ph.xin + wd * 8, want, bad);
+                wds[b] = ctid + (it0 + b) * kCT;
+                valid[b] = it0 + b < iters && wds[b] < nwords && wds[b] * 8 < K;
             }
-            if (bad == 0 || !keep_polling(polls, t0, p.status, 0x100 + ph.in_phase)) break;
+            if (ph.xbuf_in >= 0) load_x_batch<kBatch>(xv, valid, wds, p.xb[ph.xbuf_in][p.rank], p.g, want, p.status, 0x100 + ph.in_phase);
+            else load_x_batch<kBatch>(xv, valid, wds, ph.xin, 1, want, p.status, 0x100 + ph.in_phase);
         }
         if (tr && it0 == 0) {
             // measurement only: make the stamp wait for the loads
@@ -581,17 +654,11 @@ __device__ void stage_x_f16(const FPhase& ph, const FParams& p, __half* xf, floa
     float ss = 0.f;
     // first pass: wait for the tagged words, keep the values in shared memory, sum the squares
     for (int wd = ctid; wd * 8 < K; wd += kCT) {
-        uint4 v;
-        unsigned polls = 0;
-        unsigned long long t0 = 0;
-        for (;;) {
-            uint32_t bad = 0;
-            v = load_tagged8(ph.xin + wd * 8, want, bad);
-            if (bad == 0) break;
-            if (!keep_polling(polls, t0, p.status, 0x60000 + ph.in_phase)) {
-                break;
-            }
-        }
+        uint4 xv1[1];
+        const bool valid1[1] = {true};
+        const int wd1[1] = {wd};
+        load_x_batch<1>(xv1, valid1, wd1, p.xb[ph.xbuf_in][p.rank], p.g, want, p.status, 0x60000 + ph.in_phase);
+        const uint4 v = xv1[0];
         reinterpret_cast<uint4*>(xf)[wd] = v;
         const __half2* h = reinterpret_cast<const __half2*>(&v);
 #pragma unroll
@@ -709,10 +776,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
 
     if (warp == 0) {
         // ================= producer: stream every phase's weights of this CTA into the ring =================
-        // Two cursors walk the same slot list: the ring cursor fills shared memory as slots free up; the L2 cursor runs
-        // p.l2_ahead slots in front of it and only requests the bytes into L2 (fire and forget), so HBM keeps
-        // streaming while the ring is full and the consumers sit in a barrier. After the last slot the L2 cursor wraps
-        // around: the next token's first slots are already on their way when its kernel starts.
+        // (Requesting weights into L2 ahead of the ring was measured and dropped: it slows the stream down.)
         if (p.debug & 2) return;
         // The whole warp walks this CTA's precomputed copy list: 32 descriptors are fetched at a time (one per lane),
         // then lane 0 issues them one by one as ring entries free up. One entry = two consecutive slots of a phase,
@@ -812,11 +876,16 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                 const int token = p.tokens_pinned[pos];
                 const uint4* src = reinterpret_cast<const uint4*>(p.emb + (size_t)token * p.cfg.dim);
                 const uint32_t tg = tag_of(p, pi);
+                // every rank files the row as slot 0 of its own buffer 1 and zeros as the other ranks' partials
                 for (int i = cta * kCT + ctid; i < p.cfg.dim / 8; i += grid * kCT) {
                     const uint4 v = src[i];
-                    uint32_t* dst = p.x + (size_t)i * 8;
+                    uint32_t* dst = p.xb[1][p.rank] + (size_t)i * 8;
                     st_tagged4(dst, make_uint4(tg | (v.x & 0xFFFFu), tg | (v.x >> 16), tg | (v.y & 0xFFFFu), tg | (v.y >> 16)));
                     st_tagged4(dst + 4, make_uint4(tg | (v.z & 0xFFFFu), tg | (v.z >> 16), tg | (v.w & 0xFFFFu), tg | (v.w >> 16)));
+                    for (int r = 1; r < p.g; r++) {
+                        st_tagged4(dst + (size_t)r * kLLMaxDim, make_uint4(tg, tg, tg, tg));
+                        st_tagged4(dst + (size_t)r * kLLMaxDim + 4, make_uint4(tg, tg, tg, tg));
+                    }
                 }
             }
             consumer_sync();  // nobody may still be reading this phase's descriptor when the next one replaces it
@@ -827,8 +896,9 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
             TRACE(1);
             // old value of the residual stream for this thread's first epilogue element: requested now, used after the slots
             uint32_t resid = 0;
-            if (ph.epi == EPI_RESIDUAL) {
-                if ((ctid >> 3) < unit_count(ph.nunits, cta, grid)) resid = ld_tagged(ph.m[0].out + unit_at(ctid >> 3, cta, grid) * 8 + (ctid & 7));
+            if (ph.epi == EPI_RESIDUAL && p.g == 1) {
+                if ((ctid >> 3) < unit_count(ph.nunits, cta, grid))
+                    resid = ld_tagged(p.xb[ph.xbuf_out ^ 1][0] + unit_at(ctid >> 3, cta, grid) * 8 + (ctid & 7));
             }
             // slots of this CTA, in the producer's order; slot i belongs to consumer warp i % kCW.
             // Phase constants live in registers: the descriptor is not re-read inside the loops.
@@ -875,12 +945,36 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                 } else {
                     const FMat& m = ph.m[mi];
                     if (epi == EPI_RESIDUAL) {
-                        const uint32_t old = (e == ctid) ? resid : ld_tagged(m.out + n);
-                        sum += __half2float(__ushort_as_half((unsigned short)(old & 0xFFFFu))) / p.gpu_count;
+                        // Old x = the other buffer's g partials (this CTA staged that whole buffer in an earlier phase,
+                        // so they have arrived), summed as every reader sums them. This rank's partial of the new x goes
+                        // into its slot on every rank. Ordering: a rank that writes buffer b has, for every other rank,
+                        // consumed data which that rank produced after its last read of b (o projection: the peer's
+                        // down-projection partials of the previous layer, read while staging QKV; down projection: the
+                        // peer's o-projection partials, read while staging gate/up), so no reader is overtaken.
+                        const uint32_t* ob = p.xb[ph.xbuf_out ^ 1][p.rank] + n;
+                        float oldf;
+                        if (p.g == 1) {
+                            const uint32_t old = (e == ctid) ? resid : ld_tagged(ob);
+                            oldf = __half2float(__ushort_as_half((unsigned short)(old & 0xFFFFu)));
+                        } else {
+                            uint32_t ow[Q4_MAX_GPUS];
+#pragma unroll
+                            for (int r2 = 0; r2 < Q4_MAX_GPUS; r2++) ow[r2] = r2 < p.g ? ld_tagged(ob + (size_t)r2 * kLLMaxDim) : 0u;
+                            float o = 0.f;
+#pragma unroll
+                            for (int r2 = 0; r2 < Q4_MAX_GPUS; r2++)
+                                if (r2 < p.g) o += __half2float(__ushort_as_half((unsigned short)(ow[r2] & 0xFFFFu)));
+                            oldf = __half2float(__float2half(o));
+                        }
+                        sum += oldf / p.gpu_count;   // each rank adds x / g (gpu_kernels.h:237-238)
+                        const uint32_t word = tagged(__float2half(sum), out_tag);
+                        const size_t off = (size_t)p.rank * kLLMaxDim + n;
+                        for (int peer = 0; peer < p.g; peer++) st_tagged(p.xb[ph.xbuf_out][peer] + off, word);
+                    } else {
+                        const __half hv = __float2half(sum);
+                        st_tagged(m.out + n, tagged(hv, out_tag));
+                        if (m.out_plain) m.out_plain[ph.loff + (long long)pos * m.n + n] = hv;   // V row into the cache for later tokens
                     }
-                    const __half hv = __float2half(sum);
-                    st_tagged(m.out + n, tagged(hv, out_tag));
-                    if (m.out_plain) m.out_plain[ph.loff + (long long)pos * m.n + n] = hv;   // V row into the cache for later tokens
                 }
             }
             if (ph.barrier_after) grid_barrier(p, nbar, ctid, &s_abort);
@@ -1111,9 +1205,11 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
             for (int e = ctid; e < lt; e += kCT) {
                 float sum = 0.f;
                 for (int kc = 0; kc < nkt; kc++) sum += part[e * nkt + kc];
-                const int n = unit_at(e >> 1, cta, grid) * 2 + (e & 1);
+                const int n = p.vocab_off + unit_at(e >> 1, cta, grid) * 2 + (e & 1);   // global vocabulary index
                 const __half hv = __float2half(sum);
-                p.logits[n] = hv;
+                if (p.g == 1) p.logits[n] = hv;
+                else   // the all-gather of the logits: this rank's slice goes to every rank (plain peer stores)
+                    for (int peer = 0; peer < p.g; peer++) p.ll_logits[peer][n] = __half_as_ushort(hv);
                 const float v = __half2float(hv);
                 if (v > best || (v == best && n < bi)) { best = v; bi = n; }
             }
@@ -1156,6 +1252,42 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                     const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
                     if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
                 }
+                if (p.g > 1) {
+                    // Exchange of the ranks' candidates: two tagged 64-bit words per rank, stored into every rank's
+                    // mailbox. The system-scope fence orders this rank's logits slice (stored by all its CTAs before
+                    // the grid barrier above) before the candidate, so a rank that holds all candidates also holds all
+                    // logits. Every rank picks the same winner (highest value, lowest index).
+                    const unsigned long long tg = (unsigned long long)(tag_of(p, pi) >> 16) << 32;
+                    const size_t slot = ((size_t)p.launch_parity * Q4_MAX_GPUS + p.rank) * 2;
+                    if (lane == 0) {
+                        __threadfence_system();
+                        for (int peer = 0; peer < p.g; peer++) {
+                            asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(p.cand[peer] + slot), "l"(tg | __float_as_uint(best)) : "memory");
+                            asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(p.cand[peer] + slot + 1), "l"(tg | (unsigned)bi) : "memory");
+                        }
+                    }
+                    best = -CUDART_INF_F;
+                    bi = 0x7fffffff;
+                    if (lane < p.g) {
+                        const unsigned long long* src = p.cand[p.rank] + ((size_t)p.launch_parity * Q4_MAX_GPUS + lane) * 2;
+                        unsigned long long w0, w1;
+                        unsigned polls = 0;
+                        unsigned long long t0 = 0;
+                        for (;;) {
+                            asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(w0) : "l"(src) : "memory");
+                            asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(w1) : "l"(src + 1) : "memory");
+                            if (((w0 ^ tg) >> 32) == 0 && ((w1 ^ tg) >> 32) == 0) { best = __uint_as_float((unsigned)w0); bi = (int)(unsigned)w1; break; }
+                            if (!keep_polling(polls, t0, p.status, 0x70000 + lane)) break;
+                        }
+                    }
+                    __threadfence_system();
+#pragma unroll
+                    for (int o = 4; o > 0; o >>= 1) {
+                        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+                        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+                    }
+                }
                 if (lane == 0) {
                     int token_pos = *p.pos_pinned;
                     token_pos++;
@@ -1163,6 +1295,15 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                     *p.pos_pinned = token_pos;
                     *p.pos_dev = token_pos;
                 }
+            }
+            if (cta == 0 && p.g > 1) {
+                // all candidates are in, hence all logits slices: copy the gathered vector where the host reads it
+                consumer_sync();
+                const uint4* src = reinterpret_cast<const uint4*>(p.ll_logits[p.rank]);
+                uint4* dst = reinterpret_cast<uint4*>(p.logits);
+                for (int i = ctid; i < p.cfg.vocab_size / 8; i += kCT) dst[i] = __ldcg(src + i);
+                for (int i = (p.cfg.vocab_size / 8) * 8 + ctid; i < p.cfg.vocab_size; i += kCT)
+                    p.logits[i] = __ushort_as_half(__ldcg(p.ll_logits[p.rank] + i));
             }
         }
     }
@@ -1257,6 +1398,8 @@ struct q4_fused {
     unsigned long long launches = 0;
     bool unsupported = false;
     unsigned long long* trace = nullptr;
+    Q4LLArea* ll_local = nullptr;   // this rank's exchange area (inside the communicator's inbox, or own allocation at g = 1)
+    bool armed = false;             // buffers and counters are in their initial state or in step with the launches so far
 };
 
 static int fused_alloc(q4_fused* f, void** p, size_t bytes) {
@@ -1283,17 +1426,22 @@ void q4_fused_free(q4_model* m) {
 }
 
 // Called by q4_model_reset. Launch and barrier counters (and with them the activation tags) simply keep counting
-// across generations; only after a recorded error is everything re-armed from zero.
+// across generations; only after a recorded error is everything re-armed from zero. In a tensor-parallel group the
+// ranks' tags must stay in step and a rank's exchange area is written by its peers, so after an error (as after
+// q4_model_prepare) every rank has to finish its reset before any rank launches again: the callers put a host
+// barrier there.
 void q4_fused_reset(q4_model* m) {
     if (!m->fused || m->fused->unsupported) return;
     q4_fused* f = m->fused;
     int st = 0;
     cudaDeviceSynchronize();
-    if (f->launches != 0 && cudaMemcpy(&st, f->params.status, sizeof(int), cudaMemcpyDeviceToHost) == cudaSuccess && st == 0) return;
+    if (f->armed && cudaMemcpy(&st, f->params.status, sizeof(int), cudaMemcpyDeviceToHost) == cudaSuccess && st == 0) return;
+    f->armed = true;
     const q4_config& c = m->cfg;
     cudaMemset(f->params.bar_counter, 0, sizeof(unsigned long long));
     cudaMemset(f->params.status, 0, (4 + 4 * 256) * sizeof(int));
-    cudaMemset(f->params.x, 0, 4 * (size_t)c.dim);
+    cudaMemset(f->ll_local->x, 0, sizeof(f->ll_local->x));
+    cudaMemset(f->ll_local->cand, 0, sizeof(f->ll_local->cand));
     cudaMemset(f->params.hb, 0, 4 * (size_t)c.hidden_dim);
     cudaMemset(f->params.q, 0, 4 * (size_t)c.dim);
     cudaMemset(f->params.knew, 0, 4 * (size_t)m->kv_n);
@@ -1327,7 +1475,10 @@ int q4_fused_prepare(q4_model* m) {
     q4_fused* f = new q4_fused();
     m->fused = f;
     const q4_config& c = m->cfg;
-    if (m->g != 1 || m->head_size != 128 || (c.dim % 128) || (c.hidden_dim % 8) || c.dim > 4 * kCT * 8) {  // 4 = staging batch
+    const int g = m->g;
+    if (m->head_size != 128 || (c.dim % 128) || (m->h_kc % 8) || c.dim > 4 * kCT * 8 ||   // 4 = staging batch
+        c.dim > kLLMaxDim || c.vocab_size > kLLMaxVocab || (m->v_n % 2) || (m->kv_n % 128) || (m->q_n % 128) ||
+        (g > 1 && (!m->comm || q4_comm_world(m->comm) != g || q4_comm_rank(m->comm) != m->rank))) {
         f->unsupported = true;
         return Q4_ERR_UNSUPPORTED_SIZE;
     }
@@ -1344,9 +1495,12 @@ int q4_fused_prepare(q4_model* m) {
     p.head_size = m->head_size;
     p.kv_n = m->kv_n;
     p.kv_mul = m->kv_mul;
-    p.n_heads = c.n_heads;
-    p.nsplit = std::min(kMaxSplit, std::max(1, sms / c.n_heads));
-    p.gpu_count = 1.f;
+    p.n_heads = c.n_heads / g;    // this rank's query heads
+    p.nsplit = std::min(kMaxSplit, std::max(1, sms / p.n_heads));
+    p.gpu_count = (float)g;
+    p.g = g;
+    p.rank = m->rank;
+    p.vocab_off = m->rank * m->v_n;
     p.logits = (__half*)m->logits;
     p.kc = (__half*)m->kc; p.vc = (__half*)m->vc;
     p.emb = (const __half*)m->emb; p.wcls = (const __half*)m->wcls;
@@ -1355,18 +1509,32 @@ int q4_fused_prepare(q4_model* m) {
     p.pos_pinned = &m->shared->pos;
     int e;
 #define FTRY(expr) do { e = (expr); if (e != Q4_OK) return e; } while (0)
-    FTRY(fused_alloc(f, (void**)&p.x, 4 * (size_t)c.dim));
+    if (g > 1) {
+        for (int r = 0; r < g; r++) {
+            Q4LLArea* a = q4_comm_ll_area(m->comm, r);
+            if (!a) { f->unsupported = true; return Q4_ERR_UNSUPPORTED_SIZE; }
+            p.xb[0][r] = &a->x[0][0][0];
+            p.xb[1][r] = &a->x[1][0][0];
+            p.cand[r] = &a->cand[0][0][0];
+            p.ll_logits[r] = a->logits;
+        }
+        f->ll_local = q4_comm_ll_area(m->comm, m->rank);
+    } else {
+        FTRY(fused_alloc(f, (void**)&f->ll_local, sizeof(Q4LLArea)));
+        p.xb[0][0] = &f->ll_local->x[0][0][0];
+        p.xb[1][0] = &f->ll_local->x[1][0][0];
+        p.cand[0] = &f->ll_local->cand[0][0][0];
+        p.ll_logits[0] = f->ll_local->logits;
+    }
     FTRY(fused_alloc(f, (void**)&p.hb, 4 * (size_t)c.hidden_dim));
     FTRY(fused_alloc(f, (void**)&p.q, 4 * (size_t)c.dim));
     FTRY(fused_alloc(f, (void**)&p.knew, 4 * (size_t)m->kv_n));
     FTRY(fused_alloc(f, (void**)&p.vnew, 4 * (size_t)m->kv_n));
-    Q4_CUDA_TRY(cudaMemset(p.x, 0, 4 * (size_t)c.dim));
     Q4_CUDA_TRY(cudaMemset(p.hb, 0, 4 * (size_t)c.hidden_dim));
     Q4_CUDA_TRY(cudaMemset(p.q, 0, 4 * (size_t)c.dim));
     Q4_CUDA_TRY(cudaMemset(p.knew, 0, 4 * (size_t)m->kv_n));
     Q4_CUDA_TRY(cudaMemset(p.vnew, 0, 4 * (size_t)m->kv_n));
-    FTRY(fused_alloc(f, (void**)&p.attn_part, sizeof(float) * (size_t)c.n_heads * p.nsplit * kAttnPartStride));
-    FTRY(fused_alloc(f, (void**)&p.attn_cnt, sizeof(unsigned) * c.n_heads));
+    FTRY(fused_alloc(f, (void**)&p.attn_part, sizeof(float) * (size_t)p.n_heads * p.nsplit * kAttnPartStride));
     {
         float2* rope = nullptr;
         const int n = c.seq_len * (m->head_size / 2);
@@ -1383,6 +1551,8 @@ int q4_fused_prepare(q4_model* m) {
     std::vector<FPhase> ph;
     int max_K = c.dim, max_part = 0, nbar = 0;
     int x_writer = 0;  // index of the phase that last wrote the residual stream x
+    const uint32_t* const kXbuf0 = reinterpret_cast<const uint32_t*>(1);  // markers for "the residual stream, buffer 0 / 1"
+    const uint32_t* const kXbuf1 = reinterpret_cast<const uint32_t*>(2);
     auto gemv_phase = [&](int K, const uint32_t* xin, int in_phase, const __half* norm_w, int epi) {
         FPhase a;
         memset(&a, 0, sizeof(a));
@@ -1391,6 +1561,8 @@ int q4_fused_prepare(q4_model* m) {
         a.G = q4_groups(K);
         a.nkt = q4_div_up(a.G, kSlotGroups);
         a.xin = xin;
+        a.xbuf_in = -1;
+        if (xin == kXbuf0 || xin == kXbuf1) { a.xbuf_in = xin == kXbuf1; a.xin = nullptr; }
         a.in_phase = in_phase;
         a.norm_w = norm_w;
         a.epi = epi;
@@ -1420,7 +1592,7 @@ int q4_fused_prepare(q4_model* m) {
         FTRY(make_stream(f, L.gate, &sg)); FTRY(make_stream(f, L.up, &su)); FTRY(make_stream(f, L.down, &sd));
         int qkv_phase;
         {   // QKV (+ attention RMSNorm): q, k, v -> tagged staging vectors; v also straight into its cache row
-            FPhase a = gemv_phase(c.dim, p.x, x_writer, (const __half*)L.rms_att, EPI_STORE);
+            FPhase a = gemv_phase(c.dim, kXbuf1, x_writer, (const __half*)L.rms_att, EPI_STORE);
             a.nmat = 3;
             a.m[0] = FMat{sq, p.q, nullptr, m->q_n, 0};
             a.m[1] = FMat{sk, p.knew, nullptr, m->kv_n, m->q_n / 8};
@@ -1444,13 +1616,14 @@ int q4_fused_prepare(q4_model* m) {
             FPhase a = gemv_phase(m->o_kc, nullptr, 0, nullptr, EPI_RESIDUAL);
             a.attn_in = 1;
             a.nmat = 1;
-            a.m[0] = FMat{so, p.x, nullptr, c.dim, 0};
+            a.xbuf_out = 0;
+            a.m[0] = FMat{so, nullptr, nullptr, c.dim, 0};
             a.nunits = c.dim / 8;
             x_writer = finish(a);
         }
         int silu_phase;
         {   // gate/up + SiLU (+ ffn RMSNorm): unit = gate tile + the same up tile
-            FPhase a = gemv_phase(c.dim, p.x, x_writer, (const __half*)L.rms_ffn, EPI_SILU);
+            FPhase a = gemv_phase(c.dim, kXbuf0, x_writer, (const __half*)L.rms_ffn, EPI_SILU);
             a.nmat = 2;
             a.m[0] = FMat{sg, p.hb, nullptr, m->h_kc, 0};
             a.m[1] = FMat{su, p.hb, nullptr, m->h_kc, 0};
@@ -1461,7 +1634,8 @@ int q4_fused_prepare(q4_model* m) {
         {   // down projection + residual
             FPhase a = gemv_phase(m->h_kc, p.hb, silu_phase, nullptr, EPI_RESIDUAL);
             a.nmat = 1;
-            a.m[0] = FMat{sd, p.x, nullptr, c.dim, 0};
+            a.xbuf_out = 1;
+            a.m[0] = FMat{sd, nullptr, nullptr, c.dim, 0};
             a.nunits = c.dim / 8;
             x_writer = finish(a);
         }
@@ -1472,7 +1646,7 @@ int q4_fused_prepare(q4_model* m) {
         a.type = PH_CLS;
         a.K = c.dim;
         a.nkt = q4_div_up(c.dim, kClsChunk);
-        a.xin = p.x;
+        a.xbuf_in = 1;
         a.in_phase = x_writer;
         a.norm_w = (const __half*)m->rms_final;
         a.nunits = m->v_n / 2;  // row pairs
@@ -1564,13 +1738,12 @@ int q4_fused_forward(q4_model* m, cudaStream_t s, int gen_token) {
     {
         const char* dbg = getenv("Q4_FUSED_DEBUG");
         p.debug = dbg ? atoi(dbg) : 0;
-        const char* la = getenv("Q4_FUSED_L2_AHEAD");
         const char* sl = getenv("Q4_FUSED_SPLIT_LEN");  // tuning / test knob
         p.split_len = (sl && atoi(sl) > 0) ? atoi(sl) : kSplitLen;
-        p.l2_ahead = la ? atoi(la) : 0;  // measured: requesting weights into L2 ahead of the ring slows the stream down
     }
     p.bar_base = f->launches * (unsigned long long)f->barriers_per_launch;
     p.tag_base = (unsigned)((f->launches * (unsigned long long)f->nphases) & 0xFFFFu);
+    p.launch_parity = (unsigned)(f->launches & 1);
     f->launches++;
     void* args[] = {&p};
     Q4_CUDA_TRY(cudaLaunchCooperativeKernel((void*)fused_token_kernel, dim3(f->grid), dim3(kThreads), args, f->smem_bytes, s));

@@ -14,7 +14,7 @@ pytestmark = [pytest.mark.gpu, pytest.mark.skipif(torch.cuda.device_count() < 2,
 
 
 @pytest.mark.parametrize("cfg", ["mid", "mid-gqa"])
-@pytest.mark.parametrize("fwd_path", [0, 1])
+@pytest.mark.parametrize("fwd_path", [0, 1, 2])
 def test_tp2_logits_match_single_gpu_oracle(cfg, fwd_path, tmp_path):
     path = str(tmp_path / f"{cfg}.bin")
     synth.write_model_file(path, cfg, seed=7)

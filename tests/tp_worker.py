@@ -26,7 +26,9 @@ def main():
     vocab = synth.CONFIGS[cfg_name][5]
     tokens = np.random.default_rng(0).integers(3, vocab, size=24, dtype=np.int32)
     t.reset(tokens, 0)
-    dist.barrier()
+    if fwd_path == 2:
+        assert t.best_path() == 2, "the fused path must serve this sharded model"
+    dist.barrier()   # the fused path exchanges activations between the ranks' kernels: all ranks prepared before any launches
     torch.cuda.synchronize()
     logits = []
     for pos in range(len(tokens)):
