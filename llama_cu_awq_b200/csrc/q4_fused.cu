@@ -49,8 +49,10 @@ static_assert(kCT % 16 == 0, "activation staging maps 16 consecutive threads to 
 constexpr int kThreads = 32 + kCT;     // + producer warp
 constexpr int kSplitLen = 48;          // positions per attention split before a head is split further (about one step of a CTA)
 constexpr int kMaxSplit = 4;           // attention splits per head (merged in registers by the next phase)
-constexpr int kAttnPartStride = 64 + 4;   // 4-byte words per partial: acc[128] as fp16 (normalised by the split's own sum), max, sum, 2 pad
+constexpr int kAttnPartStride = 128 + 4;   // tagged words per attention partial: 128 outputs as fp16 (normalised by the split's own sum),
+                                           // then max and sum as two 16-bit pieces each
 constexpr int kTraceCols = 8;           // timestamps per phase: 0 start, 1 inputs staged, 2 weights consumed, 3 barrier passed, 4-7 staging detail
+constexpr int kMaxUnitsPerCta = 64;    // units of one phase per CTA (host-checked)
 constexpr int kClsChunk = 4096;        // halfs of one classifier row per slot (8192 B)
 constexpr unsigned kPollLimit = 1u << 26;                        // polls, and
 constexpr unsigned long long kWaitLimitNs = 2000ULL * 1000 * 1000;  // two seconds on the global timer, whichever comes first
@@ -131,7 +133,7 @@ struct FParams {
     __half *logits, *kc, *vc;
     const __half *emb, *wcls;
     const float* rope;       // [seq_len][head_size/2] (cos, sin)
-    float* attn_part;        // [heads*nsplit][kAttnPartStride]
+    uint32_t* attn_part;     // [heads*nsplit][kAttnPartStride], tagged with the attention phase
     float* cand_val;         // [grid]
     int* cand_idx;           // [grid]
     int* pos_dev;
@@ -203,6 +205,9 @@ __device__ __forceinline__ float fma_mixed(__half a, __half b, float c) {
     asm("fma.rn.f32.f16 %0, %1, %2, %3;" : "=f"(d) : "h"(__half_as_ushort(a)), "h"(__half_as_ushort(b)), "f"(c));
     return d;
 }
+
+// a / d for small operands (a * d < 2^22) without the integer-division sequence: inv = 1.0f / d.
+__device__ __forceinline__ int fast_div(unsigned a, float inv) { return (int)(((float)a + 0.5f) * inv); }
 
 // Grid-wide barrier among the consumer threads of all CTAs (the producer warps never wait here).
 __device__ __forceinline__ void grid_barrier(const FParams& p, unsigned& nbar, int ctid, int* s_abort) {
@@ -467,16 +472,19 @@ struct AttnWord {
     uint4 a[kMaxSplit];      // 8 fp16 values of the split's normalised output
     float2 ml[kMaxSplit];
 };
-__device__ __forceinline__ void attn_word_load(AttnWord& w, const FParams& p, int ns, int wd, bool valid) {
+// The partials arrive tagged (no grid barrier after the attention phase): every tag mismatch is ORed into `bad`.
+__device__ __forceinline__ void attn_word_load(AttnWord& w, const FParams& p, int ns, int wd, bool valid, uint32_t want, uint32_t& bad) {
     const int h = (wd * 8) / 128, d = (wd * 8) % 128;
 #pragma unroll
     for (int s = 0; s < kMaxSplit; s++) {
         w.ml[s] = make_float2(-CUDART_INF_F, 0.f);
         w.a[s] = make_uint4(0, 0, 0, 0);
         if (valid && s < ns) {
-            const float* base = p.attn_part + ((size_t)h * ns + s) * kAttnPartStride;
-            w.a[s] = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(base) + d));
-            w.ml[s] = __ldcg(reinterpret_cast<const float2*>(base + 64));
+            const uint32_t* base = p.attn_part + ((size_t)h * ns + s) * kAttnPartStride;
+            w.a[s] = load_tagged8(base + d, want, bad);
+            const uint4 t = ld_poll(reinterpret_cast<const uint4*>(base + 128));
+            bad |= ((t.x ^ want) | (t.y ^ want) | (t.z ^ want) | (t.w ^ want)) >> 16;
+            w.ml[s] = make_float2(__uint_as_float((t.x & 0xFFFFu) | (t.y << 16)), __uint_as_float((t.z & 0xFFFFu) | (t.w << 16)));
         }
     }
 }
@@ -566,11 +574,19 @@ __device__ void stage_x_quant(const FPhase& ph, const FParams& p, int pos, uint4
     if (ph.attn_in) {
         const int ns = attn_splits_for(p, pos + 1);
         // two words per thread in flight (all splits of both): one L2 round trip for K <= 2 * kCT * 8
+        const uint32_t want = tag_of(p, ph.in_phase);
         for (int it0 = 0; it0 < iters; it0 += 2) {
             AttnWord w0, w1;
             const int wd0 = ctid + it0 * kCT, wd1 = wd0 + kCT;
-            attn_word_load(w0, p, ns, wd0, wd0 < nwords && wd0 * 8 < K);
-            attn_word_load(w1, p, ns, wd1, it0 + 1 < iters && wd1 < nwords && wd1 * 8 < K);
+            unsigned polls = 0;
+            unsigned long long t0 = 0;
+            for (;;) {   // this poll is the op boundary between the attention phase and the o projection
+                uint32_t bad = 0;
+                attn_word_load(w0, p, ns, wd0, wd0 < nwords && wd0 * 8 < K, want, bad);
+                attn_word_load(w1, p, ns, wd1, it0 + 1 < iters && wd1 < nwords && wd1 * 8 < K, want, bad);
+                if (bad == 0 || !keep_polling(polls, t0, p.status, 0x80000 + ph.in_phase)) break;
+            }
+            if (tr && it0 == 0) tr[4] = global_ns();
             quant_word(attn_word_merge(w0), wd0, nwords, xq, xs_scale, xs_sum);
             if (it0 + 1 < iters) quant_word(attn_word_merge(w1), wd1, nwords, xq, xs_scale, xs_sum);
         }
@@ -757,6 +773,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
     __shared__ float red[kCW];
     __shared__ int s_abort;
     __shared__ __align__(16) FPhase s_cph;     // consumers' phase descriptor
+    __shared__ int s_unit_cnt[kMaxUnitsPerCta];  // slots done per unit of the current phase
 
     uint8_t* ring = smem;
     uint4* xq = reinterpret_cast<uint4*>(smem + (size_t)p.n_entries * kEntryBytes);
@@ -783,7 +800,8 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
         // one bulk copy when they are adjacent in memory.
         const CopyDesc* dl = p.desc + (size_t)cta * p.desc_stride;
         const int nd = p.desc_count[cta];
-        unsigned ent = 0;
+        unsigned ent = 0, pround = 0;   // entries issued; ring position pe and the parity of its round
+        int pe = 0;
         bool ok = true;
         for (int base = 0; base < nd && ok; base += 32) {
             uint4 d0 = make_uint4(0, 0, 0, 0), d1 = d0;
@@ -799,8 +817,8 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                 const uint32_t b0 = __shfl_sync(0xffffffffu, d1.x, i), b1 = __shfl_sync(0xffffffffu, d1.y, i);
                 int good = 1;
                 if (lane == 0) {
-                    const int e = ent % kEntries;
-                    if (!mbar_wait(&empty_bar[e], ((ent / kEntries) & 1) ^ 1, p.status)) {
+                    const int e = pe;
+                    if (!mbar_wait(&empty_bar[e], pround ^ 1u, p.status)) {
                         good = 0;
                     } else {
                         uint8_t* dst = ring + (size_t)e * kEntryBytes;
@@ -809,6 +827,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                         bulk_g2s(dst, src0, b0, &full_bar[e]);
                         if (b1) bulk_g2s(dst + b0, reinterpret_cast<const uint8_t*>(((unsigned long long)s1h << 32) | s1l), b1, &full_bar[e]);
                         ent++;
+                        if (++pe == kEntries) { pe = 0; pround ^= 1u; }
                     }
                 }
                 good = __shfl_sync(0xffffffffu, good, 0);
@@ -837,6 +856,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
     bool failed = false;  // a bounded wait ran out: skip the remaining slots, keep taking part in the barriers
     const int pos = *p.pos_dev;
     const int HS = p.head_size;
+    const float inv_entries = 1.0f / (float)kEntries;
 
     for (int pi = 0; pi < p.nphases; pi++) {
         if (ctid < (int)(sizeof(FPhase) / 16))
@@ -891,60 +911,72 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
             consumer_sync();  // nobody may still be reading this phase's descriptor when the next one replaces it
 
         } else if (ph.type == PH_GEMV) {
+            if (ctid < kMaxUnitsPerCta) s_unit_cnt[ctid] = 0;   // ordered before the first count by the staging's closing barrier
             stage_x_quant(ph, p, pos, xq, xs_scale, xs_sum, red, ctid,
                           (p.trace && ctid == 0 && cta == 0) ? p.trace + (size_t)pi * kTraceCols : nullptr);
             TRACE(1);
-            // old value of the residual stream for this thread's first epilogue element: requested now, used after the slots
-            uint32_t resid = 0;
-            if (ph.epi == EPI_RESIDUAL && p.g == 1) {
-                if ((ctid >> 3) < unit_count(ph.nunits, cta, grid))
-                    resid = ld_tagged(p.xb[ph.xbuf_out ^ 1][0] + unit_at(ctid >> 3, cta, grid) * 8 + (ctid & 7));
-            }
-            // slots of this CTA, in the producer's order; slot i belongs to consumer warp i % kCW.
+            // Slots of this CTA, in the producer's order; slot i belongs to consumer warp i % kCW. A unit (tile, or gate
+            // tile + up tile) is finished by the warp that owns its LAST slot: it waits until the unit's other slots have
+            // been counted in (they were started earlier by other warps), sums the per-slot partials in slot order and
+            // writes the outputs at once - no CTA-wide step between the math and the stores.
             // Phase constants live in registers: the descriptor is not re-read inside the loops.
-            const int nunits = ph.nunits, tpu = ph.tpu, nkt = ph.nkt, G = ph.G, dbg = p.debug;
+            const int nunits = ph.nunits, tpu = ph.tpu, nkt = ph.nkt, G = ph.G, dbg = p.debug, epi = ph.epi;
             const int my_units = unit_count(nunits, cta, grid);
-            const int ntl = my_units * tpu, nslots = ntl * nkt;
-            {
-                const unsigned first = (cw + kCW - (sbase % kCW)) % kCW;  // first slot of this warp in the phase
-                for (unsigned li = first; li < (unsigned)nslots; li += kCW) {   // li = lt * nkt + kt
-                    const int kt = li % nkt;
-                    const int ng = min(kSlotGroups, G - kt * kSlotGroups);
-                    const unsigned en = ent0 + (li >> 1);
-                    const int e = en % kEntries;
-                    int off = 0;
-                    if (li & 1) { const int ktp = (li - 1) % nkt; off = min(kSlotGroups, G - ktp * kSlotGroups) * kUnitBytes; }
-                    if (!(dbg & 2) && (failed || !mbar_wait(&full_bar[e], (en / kEntries) & 1, p.status))) { failed = true; continue; }
-                    if (!(dbg & 1)) gemv_slot(ring + (size_t)e * kEntryBytes + off, ng, kt, xq, xs_scale, xs_sum, part + (size_t)li * 8, lane);
-                    __syncwarp();
-                    // an entry is released by its two slots; a phase's odd last slot releases it alone
-                    if (lane == 0 && !(dbg & 2)) mbar_arrive(&empty_bar[e], (!(li & 1) && li + 1 == (unsigned)nslots) ? 2 : 1);
-                }
-                sbase += nslots;
-                ent0 += (nslots + 1) >> 1;
-            }
-            consumer_sync();
-            TRACE(2);
-            // epilogue: one thread per (local tile, column)
-            const int epi = ph.epi;
+            const int spu = tpu * nkt, nslots = my_units * spu;
+            const unsigned first = (cw + kCW - (sbase % kCW)) % kCW;  // first slot of this warp in the phase
             const uint32_t out_tag = tag_of(p, pi);
-            for (int e = ctid; e < ntl * 8; e += kCT) {
-                const int l2 = e >> 3, r = e & 7;
-                const int u = unit_at(l2 / tpu, cta, grid);
-                int mi, rt;
-                tile_info(ph, u * tpu + (l2 % tpu), mi, rt);
-                float sum = 0.f;
-                for (int kt = 0; kt < nkt; kt++) sum += part[(size_t)(l2 * nkt + kt) * 8 + r];
-                const int n = rt * 8 + r;
-                if (epi == EPI_SILU) {
-                    if (mi == 0) {
-                        float up = 0.f;
-                        for (int kt = 0; kt < nkt; kt++) up += part[(size_t)((l2 + 1) * nkt + kt) * 8 + r];
-                        st_tagged(ph.m[0].out + n, tagged(__float2half(silu_mul(sum, up)), out_tag));
+            const float inv_nkt = 1.0f / (float)nkt, inv_spu = 1.0f / (float)spu;
+            // old value of the residual stream for the first unit this warp will finish: requested now, used after the math
+            uint32_t resid = 0;
+            int resid_unit = -1;
+            if (epi == EPI_RESIDUAL && p.g == 1) {
+                for (int ul = 0; ul < my_units && resid_unit < 0; ul++)
+                    if ((unsigned)((ul + 1) * spu - 1) % kCW == first) resid_unit = ul;
+                if (resid_unit >= 0 && lane < 8) resid = ld_tagged(p.xb[ph.xbuf_out ^ 1][0] + unit_at(resid_unit, cta, grid) * 8 + lane);
+            }
+            for (unsigned li = first; li < (unsigned)nslots; li += kCW) {   // li = (local unit * tpu + tile) * nkt + kt
+                const int kt = li - fast_div(li, inv_nkt) * nkt;
+                const int ng = min(kSlotGroups, G - kt * kSlotGroups);
+                const unsigned en = ent0 + (li >> 1);
+                const int eq = fast_div(en, inv_entries), e = (int)en - eq * kEntries;
+                int off = 0;
+                if (li & 1) { const int ktp = kt > 0 ? kt - 1 : nkt - 1; off = min(kSlotGroups, G - ktp * kSlotGroups) * kUnitBytes; }
+                if (!(dbg & 2) && (failed || !mbar_wait(&full_bar[e], eq & 1, p.status))) { failed = true; continue; }
+                if (!(dbg & 1)) gemv_slot(ring + (size_t)e * kEntryBytes + off, ng, kt, xq, xs_scale, xs_sum, part + (size_t)li * 8, lane);
+                __syncwarp();
+                const int ul = fast_div(li, inv_spu);
+                if (lane == 0) {
+                    // an entry is released by its two slots; a phase's odd last slot releases it alone
+                    if (!(dbg & 2)) mbar_arrive(&empty_bar[e], (!(li & 1) && li + 1 == (unsigned)nslots) ? 2 : 1);
+                    __threadfence_block();   // the slot's partials before the count
+                    atomicAdd(&s_unit_cnt[ul], 1);
+                }
+                if ((int)li - ul * spu != spu - 1) continue;
+                // ---- this warp finishes unit ul ----
+                if (lane == 0 && spu > 1) {
+                    unsigned polls = 0;
+                    while (*(volatile int*)&s_unit_cnt[ul] < spu) {
+                        if ((++polls & 1023u) == 0 && (*(volatile int*)p.status != 0 || polls > (1u << 24))) {
+                            if (atomicCAS(p.status, 0, Q4_ERR_TIMEOUT) == 0) p.status[1] = 0x90000 + pi;
+                            break;
+                        }
                     }
-                } else {
-                    const FMat& m = ph.m[mi];
-                    if (epi == EPI_RESIDUAL) {
+                }
+                __syncwarp();
+                __threadfence_block();
+                if (lane < 8) {
+                    const int r = lane;
+                    int mi, rt;
+                    tile_info(ph, unit_at(ul, cta, grid) * tpu, mi, rt);
+                    const float* pu = part + (size_t)ul * spu * 8 + r;
+                    float sum = 0.f;
+                    for (int k2 = 0; k2 < nkt; k2++) sum += pu[k2 * 8];
+                    const int n = rt * 8 + r;
+                    if (epi == EPI_SILU) {
+                        float up = 0.f;
+                        for (int k2 = 0; k2 < nkt; k2++) up += pu[(nkt + k2) * 8];
+                        st_tagged(ph.m[0].out + n, tagged(__float2half(silu_mul(sum, up)), out_tag));
+                    } else if (epi == EPI_RESIDUAL) {
                         // Old x = the other buffer's g partials (this CTA staged that whole buffer in an earlier phase,
                         // so they have arrived), summed as every reader sums them. This rank's partial of the new x goes
                         // into its slot on every rank. Ordering: a rank that writes buffer b has, for every other rank,
@@ -954,7 +986,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                         const uint32_t* ob = p.xb[ph.xbuf_out ^ 1][p.rank] + n;
                         float oldf;
                         if (p.g == 1) {
-                            const uint32_t old = (e == ctid) ? resid : ld_tagged(ob);
+                            const uint32_t old = (ul == resid_unit) ? resid : ld_tagged(ob);
                             oldf = __half2float(__ushort_as_half((unsigned short)(old & 0xFFFFu)));
                         } else {
                             uint32_t ow[Q4_MAX_GPUS];
@@ -968,15 +1000,19 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                         }
                         sum += oldf / p.gpu_count;   // each rank adds x / g (gpu_kernels.h:237-238)
                         const uint32_t word = tagged(__float2half(sum), out_tag);
-                        const size_t off = (size_t)p.rank * kLLMaxDim + n;
-                        for (int peer = 0; peer < p.g; peer++) st_tagged(p.xb[ph.xbuf_out][peer] + off, word);
+                        const size_t off2 = (size_t)p.rank * kLLMaxDim + n;
+                        for (int peer = 0; peer < p.g; peer++) st_tagged(p.xb[ph.xbuf_out][peer] + off2, word);
                     } else {
+                        const FMat& m = ph.m[mi];
                         const __half hv = __float2half(sum);
                         st_tagged(m.out + n, tagged(hv, out_tag));
                         if (m.out_plain) m.out_plain[ph.loff + (long long)pos * m.n + n] = hv;   // V row into the cache for later tokens
                     }
                 }
             }
+            sbase += nslots;
+            ent0 += (nslots + 1) >> 1;
+            TRACE(2);
             if (ph.barrier_after) grid_barrier(p, nbar, ctid, &s_abort);
             else consumer_sync();  // the phase descriptor in shared memory is replaced next
             TRACE(3);
@@ -994,7 +1030,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
             const float alpha = (float)(1.0 / sqrt((double)HS));
             const int ns = attn_splits_for(p, T);
             const int nitems = p.n_heads * ns;
-            const uint32_t want = tag_of(p, ph.in_phase);
+            const uint32_t want = tag_of(p, ph.in_phase), out_tag = tag_of(p, pi);
             const __half* kc = p.kc + ph.loff;
             const __half* vc = p.vc + ph.loff;
             // (cos, sin) of this position for dims i0..i0+15: RoPE of gpu_kernels.h:340-363, tabulated at load time
@@ -1124,16 +1160,31 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                 }
                 // merge the lane groups of this CTA; the splits of a head are merged by the consumers of the o projection
                 // while they stage their input (stage_x_quant, attn_in), so no second grid-wide step is needed here
-                if (lane8 == 0) { sm_m[grp] = m; sm_l[grp] = l; }
+                // first the four lane groups of each warp (lanes 8 and 16 apart) in registers, then the warps through shared memory
 #pragma unroll
-                for (int j = 0; j < 16; j++) sm_acc[grp * 128 + d0 + j] = acc[j];
+                for (int o = 8; o <= 16; o <<= 1) {
+                    const float mo = __shfl_xor_sync(0xffffffffu, m, o), lo2 = __shfl_xor_sync(0xffffffffu, l, o);
+                    const float mn = fmaxf(m, mo);
+                    const float ca = m == -CUDART_INF_F ? 0.f : expf(m - mn), cb = mo == -CUDART_INF_F ? 0.f : expf(mo - mn);
+                    l = l * ca + lo2 * cb;
+#pragma unroll
+                    for (int j = 0; j < 16; j++) acc[j] = acc[j] * ca + __shfl_xor_sync(0xffffffffu, acc[j], o) * cb;
+                    m = mn;
+                }
+                if (lane == 0) { sm_m[cw] = m; sm_l[cw] = l; }
+                if (lane < 8) {
+#pragma unroll
+                    for (int j = 0; j < 16; j++) sm_acc[cw * 128 + d0 + j] = acc[j];
+                }
                 consumer_sync();
-                float* outp = p.attn_part + (size_t)id * kAttnPartStride;
+                uint32_t* outp = p.attn_part + (size_t)id * kAttnPartStride;
                 if (ctid < HS) {
                     float M = -CUDART_INF_F;
-                    for (int g2 = 0; g2 < kAG; g2++) M = fmaxf(M, sm_m[g2]);
+#pragma unroll
+                    for (int g2 = 0; g2 < kCW; g2++) M = fmaxf(M, sm_m[g2]);
                     float a = 0.f, L = 0.f;
-                    for (int g2 = 0; g2 < kAG; g2++) {
+#pragma unroll
+                    for (int g2 = 0; g2 < kCW; g2++) {
                         if (sm_m[g2] != -CUDART_INF_F) {
                             const float w = expf(sm_m[g2] - M);
                             a += sm_acc[g2 * 128 + ctid] * w;
@@ -1141,13 +1192,16 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                         }
                     }
                     // the split's own softmax-weighted V average (|.| <= max |V|, safe in fp16) plus its (max, sum)
-                    reinterpret_cast<__half*>(outp)[ctid] = __float2half(L > 0.f ? a / L : 0.f);
-                    if (ctid == 0) { outp[64] = M; outp[65] = L; }
+                    st_tagged(outp + ctid, tagged(__float2half(L > 0.f ? a / L : 0.f), out_tag));
+                    if (ctid == 0) {
+                        const uint32_t mb = __float_as_uint(M), lb = __float_as_uint(L);
+                        st_tagged4(outp + 128, make_uint4(out_tag | (mb & 0xFFFFu), out_tag | (mb >> 16), out_tag | (lb & 0xFFFFu), out_tag | (lb >> 16)));
+                    }
                 }
                 consumer_sync();
             }
             TRACE(2);
-            grid_barrier(p, nbar, ctid, &s_abort);
+            consumer_sync();   // no grid barrier: the partials are tagged and the o projection polls them
             TRACE(3);
 
         } else if (ph.type == PH_CLS) {
@@ -1156,18 +1210,19 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
             stage_x_f16(ph, p, xf, red, ctid);
             TRACE(1);
             const int nunits = ph.nunits, nkt = ph.nkt, K = ph.K;
+            const float inv_nkt = 1.0f / (float)nkt;
             const int lt = unit_count(nunits, cta, grid) * 2;        // rows of this CTA (units are row pairs)
             const int nslots = lt * nkt;
             const unsigned first = (cw + kCW - (sbase % kCW)) % kCW;
             for (unsigned li = first; li < (unsigned)nslots; li += kCW) {
                 {
-                    const int kc = li % nkt;
+                    const int kc = li - fast_div(li, inv_nkt) * nkt;
                     const int len = min(kClsChunk, K - kc * kClsChunk);
                     const unsigned en = ent0 + (li >> 1);
-                    const int e = en % kEntries;
+                    const int eq = fast_div(en, inv_entries), e = (int)en - eq * kEntries;
                     int off = 0;
-                    if (li & 1) { const int kcp = (li - 1) % nkt; off = min(kClsChunk, K - kcp * kClsChunk) * 2; }
-                    if (!(p.debug & 2) && (failed || !mbar_wait(&full_bar[e], (en / kEntries) & 1, p.status))) { failed = true; continue; }
+                    if (li & 1) { const int kcp = kc > 0 ? kc - 1 : nkt - 1; off = min(kClsChunk, K - kcp * kClsChunk) * 2; }
+                    if (!(p.debug & 2) && (failed || !mbar_wait(&full_bar[e], eq & 1, p.status))) { failed = true; continue; }
                     const uint4* wv = reinterpret_cast<const uint4*>(ring + (size_t)e * kEntryBytes + off);
                     const uint4* xv = reinterpret_cast<const uint4*>(xf + kc * kClsChunk);
                     float a4[8];
@@ -1399,6 +1454,7 @@ struct q4_fused {
     bool unsupported = false;
     unsigned long long* trace = nullptr;
     Q4LLArea* ll_local = nullptr;   // this rank's exchange area (inside the communicator's inbox, or own allocation at g = 1)
+    size_t attn_part_bytes = 0;
     bool armed = false;             // buffers and counters are in their initial state or in step with the launches so far
 };
 
@@ -1444,6 +1500,7 @@ void q4_fused_reset(q4_model* m) {
     cudaMemset(f->ll_local->cand, 0, sizeof(f->ll_local->cand));
     cudaMemset(f->params.hb, 0, 4 * (size_t)c.hidden_dim);
     cudaMemset(f->params.q, 0, 4 * (size_t)c.dim);
+    cudaMemset(f->params.attn_part, 0, f->attn_part_bytes);
     cudaMemset(f->params.knew, 0, 4 * (size_t)m->kv_n);
     cudaMemset(f->params.vnew, 0, 4 * (size_t)m->kv_n);
     cudaDeviceSynchronize();  // the memsets run on the default stream; forward calls use the caller's stream
@@ -1534,7 +1591,9 @@ int q4_fused_prepare(q4_model* m) {
     Q4_CUDA_TRY(cudaMemset(p.q, 0, 4 * (size_t)c.dim));
     Q4_CUDA_TRY(cudaMemset(p.knew, 0, 4 * (size_t)m->kv_n));
     Q4_CUDA_TRY(cudaMemset(p.vnew, 0, 4 * (size_t)m->kv_n));
-    FTRY(fused_alloc(f, (void**)&p.attn_part, sizeof(float) * (size_t)p.n_heads * p.nsplit * kAttnPartStride));
+    f->attn_part_bytes = sizeof(uint32_t) * (size_t)p.n_heads * p.nsplit * kAttnPartStride;
+    FTRY(fused_alloc(f, (void**)&p.attn_part, f->attn_part_bytes));
+    Q4_CUDA_TRY(cudaMemset(p.attn_part, 0, f->attn_part_bytes));
     {
         float2* rope = nullptr;
         const int n = c.seq_len * (m->head_size / 2);
@@ -1550,6 +1609,7 @@ int q4_fused_prepare(q4_model* m) {
 
     std::vector<FPhase> ph;
     int max_K = c.dim, max_part = 0, nbar = 0;
+    bool too_many_units = false;
     int x_writer = 0;  // index of the phase that last wrote the residual stream x
     const uint32_t* const kXbuf0 = reinterpret_cast<const uint32_t*>(1);  // markers for "the residual stream, buffer 0 / 1"
     const uint32_t* const kXbuf1 = reinterpret_cast<const uint32_t*>(2);
@@ -1571,6 +1631,7 @@ int q4_fused_prepare(q4_model* m) {
     };
     auto finish = [&](FPhase& a) {
         const int max_units = q4_div_up(a.nunits, sms);
+        if (max_units > kMaxUnitsPerCta) too_many_units = true;
         max_part = std::max(max_part, max_units * a.tpu * a.nkt * 8);
         max_K = std::max(max_K, a.K);
         ph.push_back(a);
@@ -1601,19 +1662,17 @@ int q4_fused_prepare(q4_model* m) {
             a.loff = loff;
             qkv_phase = finish(a);
         }
-        {   // attention: waits on the tags of q / knew / vnew; a grid barrier follows (its partials are plain floats)
+        {   // attention: waits on the tags of q / knew / vnew and writes tagged per-split partials (no grid barrier)
             FPhase a;
             memset(&a, 0, sizeof(a));
             a.type = PH_ATTN;
             a.loff = loff;
             a.layer = l;
             a.in_phase = qkv_phase;
-            a.barrier_after = 1;
             ph.push_back(a);
-            nbar++;
         }
-        {   // O projection + residual
-            FPhase a = gemv_phase(m->o_kc, nullptr, 0, nullptr, EPI_RESIDUAL);
+        {   // O projection + residual: polls the attention partials (tagged by the attention phase)
+            FPhase a = gemv_phase(m->o_kc, nullptr, (int)ph.size() - 1, nullptr, EPI_RESIDUAL);
             a.attn_in = 1;
             a.nmat = 1;
             a.xbuf_out = 0;
@@ -1667,6 +1726,7 @@ int q4_fused_prepare(q4_model* m) {
             if (ph[i].norm_w) nw = ph[i].norm_w;
         }
     }
+    if (too_many_units) { f->unsupported = true; return Q4_ERR_UNSUPPORTED_SIZE; }
     Q4_CUDA_TRY(cudaDeviceSynchronize());  // repacks done
     f->nphases = (int)ph.size();
     FTRY(fused_alloc(f, (void**)&f->d_phases, sizeof(FPhase) * ph.size()));
