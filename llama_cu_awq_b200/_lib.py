@@ -7,7 +7,8 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libq4b200.so")
+# Q4B200_LIB selects another build of the same library (A/B timing of two builds in one session).
+LIB_PATH = os.environ.get("Q4B200_LIB") or os.path.join(HERE, "libq4b200.so")
 
 Q4_OK = 0
 Q4_ERR_UNSUPPORTED_SIZE = 1

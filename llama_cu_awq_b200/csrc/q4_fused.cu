@@ -347,8 +347,8 @@ __device__ __forceinline__ bool keep_polling(unsigned& polls, unsigned long long
 }
 
 // Words wd[b] (8 elements each) of the residual stream: waits for the g partial vectors (one per source rank) and sums
-// them in rank order in fp32, rounded to fp16 once - the arithmetic of a fixed-order all-reduce. Two slots are in
-// flight per round trip, so the registers stay bounded for any g.
+// them in rank order in fp32, rounded to fp16 once - the arithmetic of a fixed-order all-reduce. Up to four slots of two
+// words are in flight per round trip (64 registers), so an 8-rank group costs two round trips per pair of words.
 template <int NB>
 __device__ __forceinline__ void load_x_batch(uint4 (&xv)[NB], const bool (&valid)[NB], const int (&wd)[NB], const uint32_t* base, int g,
                                              uint32_t want, int* status, int where) {
@@ -366,43 +366,51 @@ __device__ __forceinline__ void load_x_batch(uint4 (&xv)[NB], const bool (&valid
         }
         return;
     }
-    float acc[NB][8];
+    constexpr int SB = NB < 2 ? NB : 2;   // words per sub-batch
 #pragma unroll
-    for (int b = 0; b < NB; b++)
+    for (int b0 = 0; b0 < NB; b0 += SB) {
+        float acc[SB][8];
 #pragma unroll
-        for (int j = 0; j < 8; j++) acc[b][j] = 0.f;
-    for (int r0 = 0; r0 < g; r0 += 2) {
-        const bool two = r0 + 1 < g;
-        uint4 a[NB], c[NB];
-        for (;;) {
-            uint32_t bad = 0;
+        for (int b = 0; b < SB; b++)
 #pragma unroll
-            for (int b = 0; b < NB; b++) {
-                a[b] = c[b] = make_uint4(0, 0, 0, 0);
-                if (valid[b]) {
-                    a[b] = load_tagged8(base + (size_t)r0 * kLLMaxDim + wd[b] * 8, want, bad);
-                    if (two) c[b] = load_tagged8(base + (size_t)(r0 + 1) * kLLMaxDim + wd[b] * 8, want, bad);
+            for (int j = 0; j < 8; j++) acc[b][j] = 0.f;
+        bool any = false;
+#pragma unroll
+        for (int b = 0; b < SB; b++) any |= valid[b0 + b];
+        for (int r0 = 0; r0 < g && any; r0 += 4) {
+            uint4 a[SB][4];
+            for (;;) {
+                uint32_t bad = 0;
+#pragma unroll
+                for (int b = 0; b < SB; b++)
+#pragma unroll
+                    for (int c = 0; c < 4; c++) {
+                        a[b][c] = make_uint4(0, 0, 0, 0);
+                        if (valid[b0 + b] && r0 + c < g) a[b][c] = load_tagged8(base + (size_t)(r0 + c) * kLLMaxDim + wd[b0 + b] * 8, want, bad);
+                    }
+                if (bad == 0 || !keep_polling(polls, t0, status, where)) break;
+            }
+#pragma unroll
+            for (int b = 0; b < SB; b++)
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    if (r0 + c < g) {
+                        const __half2* ha = reinterpret_cast<const __half2*>(&a[b][c]);
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            const float2 fa = __half22float2(ha[j]);
+                            acc[b][2 * j] += fa.x;
+                            acc[b][2 * j + 1] += fa.y;
+                        }
+                    }
                 }
-            }
-            if (bad == 0 || !keep_polling(polls, t0, status, where)) break;
         }
 #pragma unroll
-        for (int b = 0; b < NB; b++) {
-            const __half2* ha = reinterpret_cast<const __half2*>(&a[b]);
-            const __half2* hc = reinterpret_cast<const __half2*>(&c[b]);
+        for (int b = 0; b < SB; b++) {
+            __half2* oh = reinterpret_cast<__half2*>(&xv[b0 + b]);
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const float2 fa = __half22float2(ha[j]), fc = __half22float2(hc[j]);
-                acc[b][2 * j] += fa.x; acc[b][2 * j + 1] += fa.y;
-                if (two) { acc[b][2 * j] += fc.x; acc[b][2 * j + 1] += fc.y; }
-            }
+            for (int j = 0; j < 4; j++) oh[j] = __floats2half2_rn(acc[b][2 * j], acc[b][2 * j + 1]);
         }
-    }
-#pragma unroll
-    for (int b = 0; b < NB; b++) {
-        __half2* oh = reinterpret_cast<__half2*>(&xv[b]);
-#pragma unroll
-        for (int j = 0; j < 4; j++) oh[j] = __floats2half2_rn(acc[b][2 * j], acc[b][2 * j + 1]);
     }
 }
 
@@ -566,15 +574,102 @@ __device__ __forceinline__ void quant_word(const uint4& hv, int wd, int nwords, 
 // Splits per head at sequence length T: short contexts are not split at all (one CTA per head, no partial traffic).
 __device__ __forceinline__ int attn_splits_for(const FParams& p, int T) { return min(p.nsplit, max(1, (T + p.split_len - 1) / p.split_len)); }
 
+// Words b0.. of one batch: SB words per thread in flight, CH rank slots per round trip. A word is processed as soon as
+// the whole warp has it (the 16 threads of a group share a scale), so the words that are there early are done while the
+// late ones - the outputs of the slowest CTA or rank - are still being polled. Plain inputs are quantised at once.
+// RMSNorm inputs (DEFER) need the whole vector first: their words are summed over the ranks, squared into ss and
+// handed back in xout (the reference rounds x * (w / rms) to fp16, gpu_kernels.h:100-102, and so does the caller).
+template <int SB, int CH, bool MULTI, bool DEFER>
+__device__ __forceinline__ void stage_words(const FPhase& ph, const FParams& p, const uint32_t* base, int g, uint32_t want, int it0, int iters,
+                                            int nwords, uint4* xq, float* xs_scale, int* xs_sum, int ctid, float& ss, bool& gave_up,
+                                            uint4* xout) {
+    const int K = ph.K;
+    int wds[SB];
+    bool valid[SB];
+    unsigned pending = 0;
+#pragma unroll
+    for (int b = 0; b < SB; b++) {
+        wds[b] = ctid + (it0 + b) * kCT;
+        valid[b] = it0 + b < iters && wds[b] < nwords && wds[b] * 8 < K;
+        if (it0 + b < iters) pending |= 1u << b;   // uniform over the CTA
+    }
+    float acc[MULTI ? SB : 1][8];
+#pragma unroll
+    for (int b = 0; b < (MULTI ? SB : 1); b++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[b][j] = 0.f;
+    unsigned polls = 0;
+    unsigned long long t0 = 0;
+    for (int r0 = 0; r0 < g && !gave_up; r0 += CH) {
+        const bool last = r0 + CH >= g;
+        unsigned pend = pending;
+        while (pend) {
+            uint4 a[SB][CH];
+            uint32_t bad[SB];
+#pragma unroll
+            for (int b = 0; b < SB; b++) {
+                bad[b] = 0;
+#pragma unroll
+                for (int c = 0; c < CH; c++) {
+                    a[b][c] = make_uint4(0, 0, 0, 0);
+                    if (((pend >> b) & 1u) && valid[b] && r0 + c < g) a[b][c] = load_tagged8(base + (size_t)(r0 + c) * kLLMaxDim + wds[b] * 8, want, bad[b]);
+                }
+            }
+#pragma unroll
+            for (int b = 0; b < SB; b++) {
+                if (!((pend >> b) & 1u)) continue;
+                if (!__all_sync(0xffffffffu, bad[b] == 0)) continue;
+                pend &= ~(1u << b);
+                uint4 hv = a[b][0];
+                if (MULTI) {   // sum of the ranks' partials in rank order, fp32, rounded to fp16 once
+                    constexpr int bb = MULTI ? 1 : 0;
+#pragma unroll
+                    for (int c = 0; c < CH; c++) {
+                        if (r0 + c < g) {
+                            const __half2* ha = reinterpret_cast<const __half2*>(&a[b][c]);
+#pragma unroll
+                            for (int j = 0; j < 4; j++) {
+                                const float2 fa = __half22float2(ha[j]);
+                                acc[b * bb][2 * j] += fa.x;
+                                acc[b * bb][2 * j + 1] += fa.y;
+                            }
+                        }
+                    }
+                    if (!last) continue;
+                    __half2* oh = reinterpret_cast<__half2*>(&hv);
+#pragma unroll
+                    for (int j = 0; j < 4; j++) oh[j] = __floats2half2_rn(acc[b * bb][2 * j], acc[b * bb][2 * j + 1]);
+                }
+                if (DEFER) {
+                    const __half2* oh = reinterpret_cast<const __half2*>(&hv);
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const float2 xf2 = __half22float2(oh[j]);
+                        ss = fmaf(xf2.x, xf2.x, ss);
+                        ss = fmaf(xf2.y, xf2.y, ss);
+                    }
+                    xout[b] = hv;
+                } else {
+                    quant_word(hv, wds[b], nwords, xq, xs_scale, xs_sum);
+                }
+            }
+            if (pend) {
+                int go = keep_polling(polls, t0, p.status, 0x100 + ph.in_phase) ? 1 : 0;
+                go = __all_sync(0xffffffffu, go);
+                if (!go) { gave_up = true; break; }
+            }
+        }
+    }
+}
+
 __device__ void stage_x_quant(const FPhase& ph, const FParams& p, int pos, uint4* xq, float* xs_scale, int* xs_sum, float* red, int ctid,
                               unsigned long long* tr) {
-    constexpr int kBatch = 4;  // words per thread whose loads are in flight together (one L2 round trip per batch)
     const int K = ph.K, nwords = ph.G * 16;
     const int iters = (nwords + kCT - 1) / kCT;
+    const uint32_t want = tag_of(p, ph.in_phase);
     if (ph.attn_in) {
         const int ns = attn_splits_for(p, pos + 1);
         // two words per thread in flight (all splits of both): one L2 round trip for K <= 2 * kCT * 8
-        const uint32_t want = tag_of(p, ph.in_phase);
         for (int it0 = 0; it0 < iters; it0 += 2) {
             AttnWord w0, w1;
             const int wd0 = ctid + it0 * kCT, wd1 = wd0 + kCT;
@@ -593,70 +688,55 @@ __device__ void stage_x_quant(const FPhase& ph, const FParams& p, int pos, uint4
         consumer_sync();
         return;
     }
-    float inv_rms = 1.f;
-    const uint32_t want = tag_of(p, ph.in_phase);
-    for (int it0 = 0; it0 < iters; it0 += kBatch) {
-        uint4 xv[kBatch], wv[kBatch];
+    const uint32_t* base = ph.xbuf_in >= 0 ? p.xb[ph.xbuf_in][p.rank] : ph.xin;
+    const int g = ph.xbuf_in >= 0 ? p.g : 1;
+    float ss = 0.f;
+    bool gave_up = false;
+    if (!ph.norm_w) {
+        if (g == 1)
+            for (int it0 = 0; it0 < iters; it0 += 4)
+                stage_words<4, 1, false, false>(ph, p, base, 1, want, it0, iters, nwords, xq, xs_scale, xs_sum, ctid, ss, gave_up, nullptr);
+        else
+            for (int it0 = 0; it0 < iters; it0 += 2)
+                stage_words<2, 4, true, false>(ph, p, base, g, want, it0, iters, nwords, xq, xs_scale, xs_sum, ctid, ss, gave_up, nullptr);
+        if (tr) tr[6] = global_ns();
+        consumer_sync();
+        return;
+    }
+    // RMSNorm inputs have K = dim <= 4 * kCT * 8 (host-checked): the whole vector fits the threads' registers
+    uint4 xv[4], wv[4];
 #pragma unroll
-        for (int b = 0; b < kBatch; b++) {
-            const int wd = ctid + (it0 + b) * kCT;
-            wv[b] = make_uint4(0, 0, 0, 0);
-            if (ph.norm_w && it0 + b < iters && wd < nwords && wd * 8 < K) wv[b] = *reinterpret_cast<const uint4*>(ph.norm_w + wd * 8);
-        }
-        // the input words carry the producing phase's tag: poll them until all have arrived (this is the op boundary)
-        {
-            bool valid[kBatch];
-            int wds[kBatch];
+    for (int b = 0; b < 4; b++) {
+        const int wd = ctid + b * kCT;
+        xv[b] = wv[b] = make_uint4(0, 0, 0, 0);
+        if (b < iters && wd < nwords && wd * 8 < K) wv[b] = *reinterpret_cast<const uint4*>(ph.norm_w + wd * 8);
+    }
+    if (g == 1) {
+        stage_words<4, 1, false, true>(ph, p, base, 1, want, 0, iters, nwords, xq, xs_scale, xs_sum, ctid, ss, gave_up, xv);
+    } else {
+        stage_words<2, 4, true, true>(ph, p, base, g, want, 0, iters, nwords, xq, xs_scale, xs_sum, ctid, ss, gave_up, xv);
+        if (iters > 2) stage_words<2, 4, true, true>(ph, p, base, g, want, 2, iters, nwords, xq, xs_scale, xs_sum, ctid, ss, gave_up, xv + 2);
+    }
+    if (tr) tr[4] = global_ns();
+    ss = consumer_sum(ss, red, ctid);
+    ss /= K;
+    ss += 1e-5f;
+    const float inv_rms = 1.0f / sqrtf(ss);
+    if (tr) tr[5] = global_ns();
 #pragma unroll
-            for (int b = 0; b < kBatch; b++) {
-                wds[b] = ctid + (it0 + b) * kCT;
-                valid[b] = it0 + b < iters && wds[b] < nwords && wds[b] * 8 < K;
+    for (int b = 0; b < 4; b++) {
+        if (b < iters) {  // uniform over the block: the shuffles in quant_word see all lanes
+            // val = x * (inv_rms * w), rounded to fp16 once (gpu_kernels.h:100-102)
+            uint4 hv;
+            const __half2* xh = reinterpret_cast<const __half2*>(&xv[b]);
+            const __half2* wh = reinterpret_cast<const __half2*>(&wv[b]);
+            __half2* oh = reinterpret_cast<__half2*>(&hv);
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const float2 xf2 = __half22float2(xh[j]), wf2 = __half22float2(wh[j]);
+                oh[j] = __floats2half2_rn(xf2.x * (inv_rms * wf2.x), xf2.y * (inv_rms * wf2.y));
             }
-            if (ph.xbuf_in >= 0) load_x_batch<kBatch>(xv, valid, wds, p.xb[ph.xbuf_in][p.rank], p.g, want, p.status, 0x100 + ph.in_phase);
-            else load_x_batch<kBatch>(xv, valid, wds, ph.xin, 1, want, p.status, 0x100 + ph.in_phase);
-        }
-        if (tr && it0 == 0) {
-            // measurement only: make the stamp wait for the loads
-            if (xv[0].x == 0x7fc07fc0u && xv[0].y == 0x12345u) tr[7] = 1;
-            tr[4] = global_ns();
-        }
-        if (ph.norm_w && it0 == 0) {
-            // RMSNorm inputs have K = dim <= kBatch * kCT * 8, so the whole vector is in registers now (host-checked)
-            float ss = 0.f;
-#pragma unroll
-            for (int b = 0; b < kBatch; b++) {
-                const __half2* h = reinterpret_cast<const __half2*>(&xv[b]);
-#pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    const float2 f = __half22float2(h[j]);
-                    ss = fmaf(f.x, f.x, ss);
-                    ss = fmaf(f.y, f.y, ss);
-                }
-            }
-            ss = consumer_sum(ss, red, ctid);
-            ss /= K;
-            ss += 1e-5f;
-            inv_rms = 1.0f / sqrtf(ss);
-            if (tr) tr[5] = global_ns();
-        }
-#pragma unroll
-        for (int b = 0; b < kBatch; b++) {
-            if (it0 + b < iters) {  // uniform over the block: the shuffles below see all lanes
-                const int wd = ctid + (it0 + b) * kCT;
-                uint4 hv = xv[b];
-                if (ph.norm_w) {
-                    // val = x * (inv_rms * w), rounded to fp16 once (gpu_kernels.h:100-102)
-                    const __half2* xh = reinterpret_cast<const __half2*>(&xv[b]);
-                    const __half2* wh = reinterpret_cast<const __half2*>(&wv[b]);
-                    __half2* oh = reinterpret_cast<__half2*>(&hv);
-#pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        const float2 xf2 = __half22float2(xh[j]), wf2 = __half22float2(wh[j]);
-                        oh[j] = __floats2half2_rn(xf2.x * (inv_rms * wf2.x), xf2.y * (inv_rms * wf2.y));
-                    }
-                }
-                quant_word(hv, wd, nwords, xq, xs_scale, xs_sum);
-            }
+            quant_word(hv, ctid + b * kCT, nwords, xq, xs_scale, xs_sum);
         }
     }
     if (tr) tr[6] = global_ns();
@@ -926,13 +1006,18 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
             const unsigned first = (cw + kCW - (sbase % kCW)) % kCW;  // first slot of this warp in the phase
             const uint32_t out_tag = tag_of(p, pi);
             const float inv_nkt = 1.0f / (float)nkt, inv_spu = 1.0f / (float)spu;
-            // old value of the residual stream for the first unit this warp will finish: requested now, used after the math
-            uint32_t resid = 0;
+            // (lane = 8 * slot + column; slots 4..7 of an 8-rank group in the second register)
+            uint32_t resid = 0, resid2 = 0;
             int resid_unit = -1;
-            if (epi == EPI_RESIDUAL && p.g == 1) {
+            const uint32_t* const oldx = epi == EPI_RESIDUAL ? p.xb[ph.xbuf_out ^ 1][p.rank] + (size_t)(lane >> 3) * kLLMaxDim + (lane & 7) : nullptr;
+            if (epi == EPI_RESIDUAL) {
                 for (int ul = 0; ul < my_units && resid_unit < 0; ul++)
                     if ((unsigned)((ul + 1) * spu - 1) % kCW == first) resid_unit = ul;
-                if (resid_unit >= 0 && lane < 8) resid = ld_tagged(p.xb[ph.xbuf_out ^ 1][0] + unit_at(resid_unit, cta, grid) * 8 + lane);
+                if (resid_unit >= 0) {
+                    const int n0 = unit_at(resid_unit, cta, grid) * 8;
+                    if ((lane >> 3) < p.g) resid = ld_tagged(oldx + n0);
+                    if ((lane >> 3) + 4 < p.g) resid2 = ld_tagged(oldx + 4 * (size_t)kLLMaxDim + n0);
+                }
             }
             for (unsigned li = first; li < (unsigned)nslots; li += kCW) {   // li = (local unit * tpu + tile) * nkt + kt
                 const int kt = li - fast_div(li, inv_nkt) * nkt;
@@ -964,6 +1049,31 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                 }
                 __syncwarp();
                 __threadfence_block();
+                float oldf = 0.f;
+                if (epi == EPI_RESIDUAL) {
+                    // Old x = the other buffer's g partials (this CTA staged that whole buffer in an earlier phase, so
+                    // they have arrived), summed in rank order in fp32 and rounded to fp16 as every reader sums them.
+                    uint32_t o1 = resid, o2 = resid2;
+                    if (ul != resid_unit) {
+                        const int n0 = unit_at(ul, cta, grid) * 8;
+                        o1 = (lane >> 3) < p.g ? ld_tagged(oldx + n0) : 0u;
+                        o2 = (lane >> 3) + 4 < p.g ? ld_tagged(oldx + 4 * (size_t)kLLMaxDim + n0) : 0u;
+                    }
+                    const float f1 = __half2float(__ushort_as_half((unsigned short)(o1 & 0xFFFFu)));
+                    const float f2 = __half2float(__ushort_as_half((unsigned short)(o2 & 0xFFFFu)));
+                    float o = 0.f;
+#pragma unroll
+                    for (int s2 = 0; s2 < 4; s2++) {
+                        const float v = __shfl_sync(0xffffffffu, f1, (lane & 7) + 8 * s2);
+                        if (s2 < p.g) o += v;
+                    }
+#pragma unroll
+                    for (int s2 = 0; s2 < 4; s2++) {
+                        const float v = __shfl_sync(0xffffffffu, f2, (lane & 7) + 8 * s2);
+                        if (s2 + 4 < p.g) o += v;
+                    }
+                    oldf = __half2float(__float2half(o));
+                }
                 if (lane < 8) {
                     const int r = lane;
                     int mi, rt;
@@ -977,27 +1087,11 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                         for (int k2 = 0; k2 < nkt; k2++) up += pu[(nkt + k2) * 8];
                         st_tagged(ph.m[0].out + n, tagged(__float2half(silu_mul(sum, up)), out_tag));
                     } else if (epi == EPI_RESIDUAL) {
-                        // Old x = the other buffer's g partials (this CTA staged that whole buffer in an earlier phase,
-                        // so they have arrived), summed as every reader sums them. This rank's partial of the new x goes
-                        // into its slot on every rank. Ordering: a rank that writes buffer b has, for every other rank,
-                        // consumed data which that rank produced after its last read of b (o projection: the peer's
-                        // down-projection partials of the previous layer, read while staging QKV; down projection: the
-                        // peer's o-projection partials, read while staging gate/up), so no reader is overtaken.
-                        const uint32_t* ob = p.xb[ph.xbuf_out ^ 1][p.rank] + n;
-                        float oldf;
-                        if (p.g == 1) {
-                            const uint32_t old = (ul == resid_unit) ? resid : ld_tagged(ob);
-                            oldf = __half2float(__ushort_as_half((unsigned short)(old & 0xFFFFu)));
-                        } else {
-                            uint32_t ow[Q4_MAX_GPUS];
-#pragma unroll
-                            for (int r2 = 0; r2 < Q4_MAX_GPUS; r2++) ow[r2] = r2 < p.g ? ld_tagged(ob + (size_t)r2 * kLLMaxDim) : 0u;
-                            float o = 0.f;
-#pragma unroll
-                            for (int r2 = 0; r2 < Q4_MAX_GPUS; r2++)
-                                if (r2 < p.g) o += __half2float(__ushort_as_half((unsigned short)(ow[r2] & 0xFFFFu)));
-                            oldf = __half2float(__float2half(o));
-                        }
+                        // This rank's partial of the new x goes into its slot on every rank. Ordering: a rank that writes
+                        // buffer b has, for every other rank, consumed data which that rank produced after its last read
+                        // of b (o projection: the peer's down-projection partials of the previous layer, read while
+                        // staging QKV; down projection: the peer's o-projection partials, read while staging gate/up),
+                        // so no reader is overtaken.
                         sum += oldf / p.gpu_count;   // each rank adds x / g (gpu_kernels.h:237-238)
                         const uint32_t word = tagged(__float2half(sum), out_tag);
                         const size_t off2 = (size_t)p.rank * kLLMaxDim + n;
