@@ -1,11 +1,12 @@
 // Fused decode path: ONE persistent cooperative kernel per token (one CTA per SM) instead of ~9 launches per layer.
-// Replaces the launch sequence of run_llama_network (llama2_q4.cu:430-538) for a single GPU.
+// Replaces the launch sequence of run_llama_network (llama2_q4.cu:430-538), on one GPU or on every rank of a
+// tensor-parallel group (hybrid split, llama2_q4.cu:45-50).
 //
 // Why: a 7B layer is 105 MB of weights = 16 us of HBM time; nine kernel boundaries per layer cost as much as the
 // streaming itself. Weight addresses never depend on activations, so each CTA has a PRODUCER warp that walks the
-// whole token's weight list and keeps a 16-slot shared-memory ring full with cp.async.bulk (TMA, 1-D, no
-// multicast), running ahead across op boundaries and grid barriers, while 8 CONSUMER warps do the math and wait at
-// the (bounded) grid barriers between dependent ops. HBM therefore stays busy through the barriers.
+// CTA's precomputed copy list and keeps a shared-memory ring (up to 12 entries of two slots) full with
+// cp.async.bulk (TMA, 1-D, no multicast), running ahead across op boundaries, while 11 CONSUMER warps do the math.
+// Dependent ops are separated by tagged activation words that the readers poll (see FParams), not by grid barriers.
 //
 // Stream layout (built once per matrix on the device from the file layout, bytes per weight unchanged):
 //   unit  = 8 output columns x 1 group of 128 inputs = 512 B of nibbles + 32 B metadata (8 fp16 scales, 8 u8 zeros)
@@ -21,8 +22,8 @@
 // (column, group): y += scale * sx * (128*Sh + Sl - zero * sum(X)). The quantisation step of x is max|x|/32512 per
 // element, below fp16's own rounding of the largest elements; nibbles, zero points and scales are used exactly.
 //
-// Every wait is bounded (mbarrier polls and barrier spins count iterations); on expiry the kernel records
-// Q4_ERR_TIMEOUT in a status word, all later waits fall through, and the kernel returns.
+// Every wait is bounded (mbarrier polls, tag polls and barrier spins are limited by the global timer); on expiry the
+// kernel records Q4_ERR_TIMEOUT in a status word, all later waits fall through, and the kernel returns.
 #include <cooperative_groups.h>
 #include <math_constants.h>
 #include <stdio.h>

@@ -74,6 +74,30 @@ def test_logits_teacher_forced(which, fwd_path, tiny_path, gqa_path, mid_path, m
         assert_close(a, b, f"{which} logits at pos {pos}")
 
 
+@pytest.mark.parametrize("cfg", ["llama2-13b-1l", "llama2-70b-1l"])
+def test_large_layer_shapes(cfg, tmp_path):
+    """One layer with the 13B / 70B matrix shapes: every forward path against the oracle (fast summation order)."""
+    path = str(tmp_path / f"{cfg}.bin")
+    synth.write_model_file(path, cfg, seed=5)
+    vocab = synth.CONFIGS[cfg][5]
+    tokens = np.random.default_rng(4).integers(3, vocab, size=6, dtype=np.int32)
+    m = O.Model(open(path, "rb").read())
+    ref = []
+    for pos, tok in enumerate(tokens):
+        m.forward(int(tok), pos, order=0)
+        ref.append(m.logits())
+    for fwd_path in (1, 2):
+        t = Transformer(path)
+        assert fwd_path != 2 or t.best_path() == 2
+        t.reset(tokens, 0)
+        for pos in range(len(tokens)):
+            t.forward(gen_token=False, path=fwd_path)
+            t.synchronize()
+            assert_close(t.logits(), ref[pos], f"{cfg} path {fwd_path} logits at pos {pos}")
+        assert t.status() == 0
+        t.close()
+
+
 def test_graph_replay_equals_per_op_launches(tiny_path):
     tokens = np.random.default_rng(1).integers(3, 512, size=10, dtype=np.int32)
     a, _ = teacher_forced(tiny_path, tokens, 0)
