@@ -134,6 +134,20 @@ int q4_embed(void* stream, uint16_t* x, const uint16_t* table, int dim, const in
 int q4_argmax(void* stream, const uint16_t* logits, int size, int* tokens_pinned, volatile int* pos_pinned,
               int* pos_dev, int write_token);
 
+/* Non-greedy branch of sample(): sampler.h:85-115 with softmax_logits_kernel / sample_top_p_kernel
+ * (gpu_kernels.h:507-592) and the sort and prefix sum between them, as ONE launch. logits[0..n) are replaced by the
+ * fp16 probabilities softmax(logits / temperature) as the reference does; the token is the first element, in
+ * descending-probability order (0 < topp < 1, threshold coin * topp) or in index order (otherwise, threshold coin),
+ * whose inclusive prefix sum reaches the threshold. The prefix sum is exact (integer multiples of 2^-24), where the
+ * reference's runs in fp16. Writes tokens_pinned[*pos_pinned + 1] and increments both position words, like q4_argmax
+ * with write_token = 1. temperature must be > 0 (the reference takes the greedy branch at 0); n <= 262144. */
+int q4_sample_topp(void* stream, uint16_t* logits, int n, float temperature, float topp, float coin, int* tokens_pinned,
+                   volatile int* pos_pinned, int* pos_dev);
+
+/* The reference's xorshift* generator (sampler.h:66-75): one coin is drawn per sample() call, greedy or not. Host only. */
+unsigned int q4_random_u32(unsigned long long* state);
+float q4_random_f32(unsigned long long* state);
+
 /* Test hook without a twin in the reference: dequantised weights w(n,k) as fp32 [N][K]
  * (the values gpu_kernels.h:204-205 computes on the fly), and raw nibbles as bytes. */
 int q4_dequant(void* stream, float* out, const q4_qweight* w, int K, int N);
@@ -202,6 +216,12 @@ int q4_model_forward(q4_model* model, void* stream, int gen_token, int path);
  * as much extra device memory as the quantized weights). Q4_ERR_UNSUPPORTED_SIZE when the path cannot serve
  * this model; q4_model_forward calls it on demand. */
 int q4_model_prepare(q4_model* model, int path);
+
+/* build_sampler (sampler.h:28-45). temperature 0 (the state after q4_model_load) decodes greedily; otherwise every
+ * generating q4_model_forward ends with q4_sample_topp instead of the argmax. One coin is drawn from the xorshift*
+ * state per forward call, greedy or not, as sample() does (sampler.h:79). All ranks of a tensor-parallel group set
+ * the same values. */
+int q4_model_set_sampler(q4_model* model, float temperature, float topp, unsigned long long seed);
 /* Synchronises the device and returns Q4_OK, or the error a bounded device-side wait recorded
  * (Q4_ERR_TIMEOUT) in the fused path or the communicator. */
 int q4_model_status(q4_model* model);

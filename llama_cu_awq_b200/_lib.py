@@ -62,6 +62,9 @@ SIGNATURES = {
     "q4_matmul_f16": (_I, [_P, _P, _P, _P, _I, _I, C.c_float]),
     "q4_embed": (_I, [_P, _P, _P, _I, _P, _P]),
     "q4_argmax": (_I, [_P, _P, _I, _P, _P, _P, _I]),
+    "q4_sample_topp": (_I, [_P, _P, _I, C.c_float, C.c_float, C.c_float, _P, _P, _P]),
+    "q4_random_u32": (C.c_uint, [_P]),
+    "q4_random_f32": (C.c_float, [_P]),
     "q4_dequant": (_I, [_P, _P, _QW, _I, _I]),
     "q4_unpack_nibbles": (_I, [_P, _P, _P, _QW, _I, _I]),
     "q4_comm_id_create": (_I, [C.POINTER(_P), _I]),
@@ -84,6 +87,7 @@ SIGNATURES = {
     "q4_model_reset": (_I, [_P, C.POINTER(C.c_int), _I, _I]),
     "q4_model_forward": (_I, [_P, _P, _I, _I]),
     "q4_model_prepare": (_I, [_P, _I]),
+    "q4_model_set_sampler": (_I, [_P, C.c_float, C.c_float, C.c_ulonglong]),
     "q4_model_status": (_I, [_P]),
     "q4_generate": (_I, [_P, C.POINTER(C.c_int), _I, _I, _I, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_double)]),
     "q4_model_token_bytes": (C.c_double, [_P, _I]),

@@ -106,7 +106,7 @@ private:
     fprintf(stderr, "  -n <int>    max number of steps to run for, default = max_seq_len\n");
     fprintf(stderr, "  -i <string> input prompt\n");
     fprintf(stderr, "  -f <string> path to file containing input prompt. Can be used with for multi-line prompts.\n");
-    fprintf(stderr, "  -t <float>  temperature in [0,inf], default 0.5 (this build decodes greedily: only 0 is honoured)\n");
+    fprintf(stderr, "  -t <float>  temperature in [0,inf], default 0.5\n");
     fprintf(stderr, "  -p <float>  p value in top-p (nucleus) sampling in [0,1] default 0.9\n");
     fprintf(stderr, "  -s <int>    random seed, default time(NULL)\n");
     fprintf(stderr, "  -z <string> optional path to custom tokenizer\n");
@@ -167,7 +167,9 @@ void load_thread(Shared* sh, const char* path, int rank, int gpu_count, int tp_m
 }
 
 // The token loop of generate_thread (llama2_q4.cu:683-757) with rank 0 streaming the text.
-void generate_thread(Shared* sh, const Vocab* vocab, const std::vector<int>* prompt, int steps, int rank, int fwd_path) {
+struct SamplerArgs { float temperature, topp; unsigned long long seed; };
+
+void generate_thread(Shared* sh, const Vocab* vocab, const std::vector<int>* prompt, int steps, int rank, int fwd_path, SamplerArgs sa) {
     cudaSetDevice(rank);
     q4_model* m = sh->models[rank];
     q4_config cfg;
@@ -177,6 +179,8 @@ void generate_thread(Shared* sh, const Vocab* vocab, const std::vector<int>* pro
     q4_shared_data* mb = q4_model_shared(m);
     int e = q4_model_reset(m, prompt->data(), (int)prompt->size(), 0);
     if (e) die(e, "reset");
+    e = q4_model_set_sampler(m, sa.temperature, sa.topp, sa.seed);   // build_sampler: every rank draws the same coins
+    if (e) die(e, "build_sampler");
     int token = (*prompt)[0], next = 0, pos = 0;
     const auto start = std::chrono::steady_clock::now();
     while (pos < steps) {
@@ -262,7 +266,7 @@ int main(int argc, char* argv[]) {
     if (temperature < 0.0f) temperature = 0.0f;
     if (topp < 0.0f || 1.0f < topp) topp = 0.9f;
     if (dataset_path) printf("Warning: dataset path is ignored in non-perplexity mode\n");
-    if (temperature != 0.0f) printf("Note: temperature / top-p sampling is not part of this build; decoding greedily (-t 0)\n");
+
     if (tp_mode == Q4_TP_COLUMN && gpu_count > 1) {
         printf("Note: -x column (4 all-gathers per layer) is not part of this build; using -x hybrid\n");
         tp_mode = Q4_TP_HYBRID;
@@ -318,7 +322,7 @@ int main(int argc, char* argv[]) {
 
     {
         std::vector<std::thread> th;
-        for (int r = 0; r < gpu_count; r++) th.emplace_back(generate_thread, &sh, &vocab, &prompt_tokens, steps, r, fwd_path);
+        for (int r = 0; r < gpu_count; r++) th.emplace_back(generate_thread, &sh, &vocab, &prompt_tokens, steps, r, fwd_path, SamplerArgs{temperature, topp, rng_seed});
         for (auto& t : th) t.join();
     }
     for (int r = 0; r < gpu_count; r++) {

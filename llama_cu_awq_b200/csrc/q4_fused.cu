@@ -144,6 +144,7 @@ struct FParams {
     unsigned long long bar_base;  // barriers completed by earlier launches
     int* status;
     int write_token;
+    int no_handoff;              // 1: leave the token mailbox and the position alone (a sampling kernel follows on the stream)
     int debug;                   // measurement only: 1 = consumers skip the GEMV math (pure streaming), 2 = no streaming (pure math)
     int n_entries;               // ring entries of kEntryBytes each
     int split_len;               // positions per attention split (a head is split in ceil(T / split_len) parts, at most nsplit)
@@ -177,10 +178,16 @@ __device__ __forceinline__ unsigned long long global_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-__device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, int* status) {
+// A parity wait cannot tell round r of a ring position from round r - 2. The producer's waits are safe (it issued round
+// r - 1 itself, after round r - 2 was released), but a consumer warp may ask for round r of a position whose round
+// r - 1 belongs to other warps and is still in flight (bulk copies complete out of order, wildly so on a cold first
+// launch): the test would pass on round r - 2's completion. Consumers therefore first wait until the producer has
+// ISSUED round r at that position (`seq`, written before the copy is issued); from then on the barrier's current phase
+// is r or r + 1 and the parity test is unambiguous. seq == nullptr: the caller is the producer.
+__device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, int* status, const unsigned* seq = nullptr, unsigned want = 0) {
     unsigned long long t0 = 0;
     for (unsigned i = 0; i < kPollLimit; i++) {
-        if (mbar_try(b, parity)) return true;
+        if ((!seq || *(const volatile unsigned*)seq == want) && mbar_try(b, parity)) return true;
         if ((i & 63u) == 63u) {
             if (*(volatile int*)status != 0) return false;
             const unsigned long long now = global_ns();
@@ -850,6 +857,7 @@ __device__ __forceinline__ void gemv_slot(const uint8_t* slot, int ng, int kt, c
 __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ uint64_t full_bar[kMaxEntries], empty_bar[kMaxEntries];
+    __shared__ unsigned s_round[kMaxEntries];   // round last issued by the producer per ring position
     const int kEntries = p.n_entries;
     __shared__ float red[kCW];
     __shared__ int s_abort;
@@ -867,7 +875,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
 
     if (tid == 0) {
         s_abort = 0;
-        for (int s = 0; s < kMaxEntries; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 2); }
+        for (int s = 0; s < kMaxEntries; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 2); s_round[s] = 0xFFFFFFFFu; }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -881,7 +889,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
         // one bulk copy when they are adjacent in memory.
         const CopyDesc* dl = p.desc + (size_t)cta * p.desc_stride;
         const int nd = p.desc_count[cta];
-        unsigned ent = 0, pround = 0;   // entries issued; ring position pe and the parity of its round
+        unsigned ent = 0, pround = 0, prnd = 0;   // entries issued; ring position pe, the parity of its round and the round
         int pe = 0;
         bool ok = true;
         for (int base = 0; base < nd && ok; base += 32) {
@@ -904,11 +912,12 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                     } else {
                         uint8_t* dst = ring + (size_t)e * kEntryBytes;
                         const uint8_t* src0 = reinterpret_cast<const uint8_t*>(((unsigned long long)s0h << 32) | s0l);
+                        *(volatile unsigned*)&s_round[e] = prnd;
                         mbar_expect_tx(&full_bar[e], b0 + b1);
                         bulk_g2s(dst, src0, b0, &full_bar[e]);
                         if (b1) bulk_g2s(dst + b0, reinterpret_cast<const uint8_t*>(((unsigned long long)s1h << 32) | s1l), b1, &full_bar[e]);
                         ent++;
-                        if (++pe == kEntries) { pe = 0; pround ^= 1u; }
+                        if (++pe == kEntries) { pe = 0; pround ^= 1u; prnd++; }
                     }
                 }
                 good = __shfl_sync(0xffffffffu, good, 0);
@@ -962,7 +971,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                 for (unsigned li = first; li < (unsigned)nslots; li += kCW) {
                     const unsigned en = ent0 + (li >> 1);
                     const int e = en % kEntries;
-                    if (failed || !mbar_wait(&full_bar[e], (en / kEntries) & 1, p.status)) { failed = true; continue; }
+                    if (failed || !mbar_wait(&full_bar[e], (en / kEntries) & 1, p.status, &s_round[e], en / kEntries)) { failed = true; continue; }
                     if (lane == 0) mbar_arrive(&empty_bar[e], (!(li & 1) && li + 1 == (unsigned)nslots) ? 2 : 1);
                 }
                 sbase += nslots;
@@ -1027,7 +1036,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                 const int eq = fast_div(en, inv_entries), e = (int)en - eq * kEntries;
                 int off = 0;
                 if (li & 1) { const int ktp = kt > 0 ? kt - 1 : nkt - 1; off = min(kSlotGroups, G - ktp * kSlotGroups) * kUnitBytes; }
-                if (!(dbg & 2) && (failed || !mbar_wait(&full_bar[e], eq & 1, p.status))) { failed = true; continue; }
+                if (!(dbg & 2) && (failed || !mbar_wait(&full_bar[e], eq & 1, p.status, &s_round[e], (unsigned)eq))) { failed = true; continue; }
                 if (!(dbg & 1)) gemv_slot(ring + (size_t)e * kEntryBytes + off, ng, kt, xq, xs_scale, xs_sum, part + (size_t)li * 8, lane);
                 __syncwarp();
                 const int ul = fast_div(li, inv_spu);
@@ -1041,10 +1050,16 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                 // ---- this warp finishes unit ul ----
                 if (lane == 0 && spu > 1) {
                     unsigned polls = 0;
+                    unsigned long long t0 = 0;
                     while (*(volatile int*)&s_unit_cnt[ul] < spu) {
-                        if ((++polls & 1023u) == 0 && (*(volatile int*)p.status != 0 || polls > (1u << 24))) {
-                            if (atomicCAS(p.status, 0, Q4_ERR_TIMEOUT) == 0) p.status[1] = 0x90000 + pi;
-                            break;
+                        if ((++polls & 1023u) == 0) {
+                            if (*(volatile int*)p.status != 0) break;
+                            const unsigned long long now = global_ns();
+                            if (t0 == 0) t0 = now;
+                            else if (now - t0 > 2 * kWaitLimitNs) {   // longer than any data wait: the root cause gets recorded first
+                                if (atomicCAS(p.status, 0, Q4_ERR_TIMEOUT) == 0) p.status[1] = 0x90000 + pi;
+                                break;
+                            }
                         }
                     }
                 }
@@ -1317,7 +1332,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                     const int eq = fast_div(en, inv_entries), e = (int)en - eq * kEntries;
                     int off = 0;
                     if (li & 1) { const int kcp = kc > 0 ? kc - 1 : nkt - 1; off = min(kClsChunk, K - kcp * kClsChunk) * 2; }
-                    if (!(p.debug & 2) && (failed || !mbar_wait(&full_bar[e], eq & 1, p.status))) { failed = true; continue; }
+                    if (!(p.debug & 2) && (failed || !mbar_wait(&full_bar[e], eq & 1, p.status, &s_round[e], (unsigned)eq))) { failed = true; continue; }
                     const uint4* wv = reinterpret_cast<const uint4*>(ring + (size_t)e * kEntryBytes + off);
                     const uint4* xv = reinterpret_cast<const uint4*>(xf + kc * kClsChunk);
                     float a4[8];
@@ -1438,7 +1453,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                         if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
                     }
                 }
-                if (lane == 0) {
+                if (lane == 0 && !p.no_handoff) {
                     int token_pos = *p.pos_pinned;
                     token_pos++;
                     if (p.write_token) p.tokens_pinned[token_pos] = (bi == 0x7fffffff) ? 0 : bi;
@@ -1884,11 +1899,12 @@ int q4_fused_prepare(q4_model* m) {
     return Q4_OK;
 }
 
-int q4_fused_forward(q4_model* m, cudaStream_t s, int gen_token) {
+int q4_fused_forward(q4_model* m, cudaStream_t s, int gen_token, int no_handoff) {
     q4_fused* f = m->fused;
     if (!f || f->unsupported) return Q4_ERR_UNSUPPORTED_SIZE;
     FParams p = f->params;
     p.write_token = gen_token;
+    p.no_handoff = no_handoff;
     p.trace = f->trace;
     {
         const char* dbg = getenv("Q4_FUSED_DEBUG");

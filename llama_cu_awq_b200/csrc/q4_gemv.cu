@@ -7,7 +7,7 @@
 // K axis (one 128-bit load per output column per chunk, lanes adjacent -> 512 B coalesced per warp per column),
 // keeps the matching 32 activations in registers and reuses them for all 8 columns. Nibbles are unpacked two at
 // a time into half2 with one LOP3 each (magic-number trick), the zero point is folded into the same subtract,
-// products are summed in short half2 chains (16 weights) that are flushed to fp32, and the group scale is
+// products are summed in short half2 chains (8 weights) that are flushed to fp32, and the group scale is
 // applied in fp32. The 8 per-column partials are reduced across the warp with a transposing butterfly
 // (9 shuffles instead of 40) and, when several warps share a tile, through shared memory.
 // Weight loads of the first chunk are issued before griddepcontrol.wait, so under programmatic dependent
@@ -146,11 +146,12 @@ __global__ void __launch_bounds__(128) q4_gemv_kernel(const GemvParams p) {
                 uint32_t zlo, zhi;
                 zero_consts(z, zlo, zhi);
                 const __half2 zero2 = u2h2(0u);
-                __half2 a = dot8(cur[r].x, xp[0], zlo, zhi, zero2);
-                a = dot8(cur[r].y, xp[1], zlo, zhi, a);
-                __half2 b = dot8(cur[r].z, xp[2], zlo, zhi, zero2);
-                b = dot8(cur[r].w, xp[3], zlo, zhi, b);
-                acc[r] = fmaf(sc, h2sum(a) + h2sum(b), acc[r]);
+                // four products per half lane, then fp32: longer fp16 chains cost accuracy on long rows (K > 8192)
+                const __half2 a0 = dot8(cur[r].x, xp[0], zlo, zhi, zero2);
+                const __half2 a1 = dot8(cur[r].y, xp[1], zlo, zhi, zero2);
+                const __half2 b0 = dot8(cur[r].z, xp[2], zlo, zhi, zero2);
+                const __half2 b1 = dot8(cur[r].w, xp[3], zlo, zhi, zero2);
+                acc[r] = fmaf(sc, (h2sum(a0) + h2sum(a1)) + (h2sum(b0) + h2sum(b1)), acc[r]);
             }
             c = cn;
         }

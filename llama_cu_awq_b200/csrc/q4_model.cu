@@ -168,7 +168,7 @@ int upload_raw(Arena& a, uint16_t** dst, const void* src, size_t bytes) {
 extern "C" int q4_model_free(q4_model* m) {
     if (!m) return Q4_OK;
     q4_fused_free(m);
-    for (int i = 0; i < 2; i++)
+    for (int i = 0; i < 3; i++)
         if (m->graph_ready[i]) cudaGraphExecDestroy(m->graph[i]);
     cudaFree(m->arena);
     cudaFree(m->x); cudaFree(m->xb); cudaFree(m->hb); cudaFree(m->q); cudaFree(m->logits);
@@ -225,7 +225,10 @@ extern "C" int q4_model_load(q4_model** out, const char* path, int rank, int gpu
     if (g > 1) q4_row_split_range(c.hidden_dim, g, rank, &m->h_kb, &m->h_kc);
     else { m->h_kb = 0; m->h_kc = c.hidden_dim; }
     m->v_n = c.vocab_size / g;
-    m->graph_ready[0] = m->graph_ready[1] = false;
+    m->graph_ready[0] = m->graph_ready[1] = m->graph_ready[2] = false;
+    m->temperature = 0.f;
+    m->topp = 0.f;
+    m->rng_state = 0;
     m->fused = nullptr;
     m->arena = nullptr;
     m->x = m->xb = m->hb = m->q = m->logits = m->kc = m->vc = nullptr;
@@ -340,7 +343,7 @@ extern "C" int q4_model_reset(q4_model* m, const int* prompt_tokens, int n, int 
 }
 
 // The per-token schedule of run_llama_network (llama2_q4.cu:430-538), hybrid tensor parallelism when g > 1.
-static int launch_token(q4_model* m, cudaStream_t s, int gen_token) {
+static int launch_token(q4_model* m, cudaStream_t s, int gen_token, bool handoff = true) {
     const q4_config& c = m->cfg;
     const int g = m->g, rank = m->rank;
     const int dim = c.dim, hs = m->head_size;
@@ -365,7 +368,7 @@ static int launch_token(q4_model* m, cudaStream_t s, int gen_token) {
     OP(q4_rmsnorm(s, m->x, m->x, m->rms_final, dim));
     OP(q4_matmul_f16(s, m->logits + (size_t)rank * m->v_n, m->x, m->wcls, dim, m->v_n, 1.0f));
     if (g > 1) OP(q4_all_gather(m->comm, s, m->logits + (size_t)rank * m->v_n, m->logits, m->v_n));
-    OP(q4_argmax(s, m->logits, c.vocab_size, (int*)m->shared->tokens, &m->shared->pos, m->pos, gen_token));
+    if (handoff) OP(q4_argmax(s, m->logits, c.vocab_size, (int*)m->shared->tokens, &m->shared->pos, m->pos, gen_token));
 #undef OP
     return Q4_OK;
 }
@@ -374,27 +377,43 @@ extern "C" int q4_model_forward(q4_model* m, void* stream, int gen_token, int pa
     if (!m) return Q4_ERR_INVALID;
     cudaStream_t s = (cudaStream_t)stream;
     gen_token = gen_token != 0;
-    if (path == 0) return launch_token(m, s, gen_token);
-    if (path == 1) {
-        if (!m->graph_ready[gen_token]) {
+    if (path < 0 || path > 2) return Q4_ERR_INVALID;
+    // sample() draws one coin per call, used or not (sampler.h:79); the greedy branch is taken at temperature 0 and for
+    // prompt positions (sampler.h:81)
+    const float coin = q4_random_f32(&m->rng_state);
+    const bool sampled = m->temperature != 0.0f && gen_token;
+    int e = Q4_OK;
+    if (path == 0) {
+        e = launch_token(m, s, gen_token, !sampled);
+    } else if (path == 1) {
+        const int gi = sampled ? 2 : gen_token;
+        if (!m->graph_ready[gi]) {
             cudaGraph_t graph = nullptr;
             Q4_CUDA_TRY(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
-            const int e = launch_token(m, s, gen_token);
+            e = launch_token(m, s, gen_token, !sampled);
             cudaError_t ce = cudaStreamEndCapture(s, &graph);
             if (e != Q4_OK) { if (graph) cudaGraphDestroy(graph); return e; }
             Q4_CUDA_TRY(ce);
-            Q4_CUDA_TRY(cudaGraphInstantiate(&m->graph[gen_token], graph, 0));
+            Q4_CUDA_TRY(cudaGraphInstantiate(&m->graph[gi], graph, 0));
             Q4_CUDA_TRY(cudaGraphDestroy(graph));
-            m->graph_ready[gen_token] = true;
+            m->graph_ready[gi] = true;
         }
-        Q4_CUDA_TRY(cudaGraphLaunch(m->graph[gen_token], s));
-        return Q4_OK;
+        Q4_CUDA_TRY(cudaGraphLaunch(m->graph[gi], s));
+    } else {
+        if ((e = q4_fused_prepare(m)) != Q4_OK) return e;
+        e = q4_fused_forward(m, s, gen_token, sampled);
     }
-    if (path == 2) {
-        if (int e = q4_fused_prepare(m)) return e;
-        return q4_fused_forward(m, s, gen_token);
-    }
-    return Q4_ERR_INVALID;
+    if (e != Q4_OK || !sampled) return e;
+    return q4_sample_topp(s, m->logits, m->cfg.vocab_size, m->temperature, m->topp, coin, (int*)m->shared->tokens, &m->shared->pos, m->pos);
+}
+
+/* build_sampler (sampler.h:28-45): temperature 0 decodes greedily. */
+extern "C" int q4_model_set_sampler(q4_model* m, float temperature, float topp, unsigned long long seed) {
+    if (!m || temperature < 0.0f) return Q4_ERR_INVALID;
+    m->temperature = temperature;
+    m->topp = topp;
+    m->rng_state = seed;
+    return Q4_OK;
 }
 
 extern "C" int q4_model_prepare(q4_model* m, int path) {

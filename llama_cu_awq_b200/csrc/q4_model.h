@@ -38,14 +38,17 @@ struct q4_model {
     float* attn_scratch;
     int* pos;
     q4_shared_data* shared;
-    cudaGraphExec_t graph[2];
-    bool graph_ready[2];
+    cudaGraphExec_t graph[3];   // prompt phase, generating (argmax), generating without the hand-off (a sampler follows)
+    bool graph_ready[3];
+    // sampler state (sampler.h:10-19): temperature 0 = greedy
+    float temperature, topp;
+    unsigned long long rng_state;
     q4_fused* fused;
 };
 
 // q4_fused.cu
 int q4_fused_prepare(q4_model* m);                              // builds the stream-layout weights and the phase table (lazy)
-int q4_fused_forward(q4_model* m, cudaStream_t s, int gen_token);
+int q4_fused_forward(q4_model* m, cudaStream_t s, int gen_token, int no_handoff);
 void q4_fused_reset(q4_model* m);                               // re-arms barrier counters (after q4_model_reset)
 void q4_fused_free(q4_model* m);
 int q4_fused_status(q4_model* m);

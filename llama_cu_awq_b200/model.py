@@ -25,6 +25,10 @@ class Transformer:
     def forward(self, gen_token=True, path=1):
         check(self._L.q4_model_forward(self.h, C.c_void_p(self.stream.cuda_stream), int(bool(gen_token)), path), "run_transformer")
 
+    def set_sampler(self, temperature, topp, seed):
+        """build_sampler (sampler.h:28): temperature 0 decodes greedily."""
+        check(self._L.q4_model_set_sampler(self.h, float(temperature), float(topp), int(seed)), "build_sampler")
+
     def best_path(self):
         """The fastest forward path that serves this model: 2 = persistent fused kernel, else 1 = CUDA-graph
         replay of the per-op kernels."""

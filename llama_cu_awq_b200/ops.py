@@ -90,6 +90,12 @@ def sample_greedy(logits, size, tokens_ptr, pos_pinned_ptr, pos_dev, gen_token, 
                                int(bool(gen_token))), "sample")
 
 
+def sample_topp(logits, size, temperature, topp, coin, tokens_ptr, pos_pinned_ptr, pos_dev, stream=None):
+    """Non-greedy branch of sample() (sampler.h:85-115): logits become probabilities, the token goes to the mailbox."""
+    check(_lib.lib().q4_sample_topp(_stream(stream), _p(logits), size, temperature, topp, coin, C.c_void_p(tokens_ptr),
+                                    C.c_void_p(pos_pinned_ptr), _p(pos_dev)), "sample")
+
+
 def dequant(w, K, N, stream=None):
     out = torch.empty((N, K), dtype=torch.float32, device=w.weight.device)
     check(_lib.lib().q4_dequant(_stream(stream), _p(out), w.ref, K, N), "dequant")

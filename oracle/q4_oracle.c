@@ -351,6 +351,89 @@ int q4o_argmax(const f16 *x, int n) {
     return best;
 }
 
+/* xorshift* generator and coin of the sampler. sampler.h:66-75. */
+unsigned int q4o_random_u32(unsigned long long *state) {
+    *state ^= *state >> 12;
+    *state ^= *state << 25;
+    *state ^= *state >> 27;
+    return (unsigned int)((*state * 0x2545F4914F6CDD1Dull) >> 32);
+}
+float q4o_random_f32(unsigned long long *state) { return (q4o_random_u32(state) >> 8) / 16777216.0f; }
+
+static unsigned long long q4o_prob_units(f16 h) { /* fp16 in [0,1] as a multiple of 2^-24 */
+    unsigned e = (h >> 10) & 31u, mnt = h & 1023u;
+    return e == 0 ? (unsigned long long)mnt : (unsigned long long)(1024u + mnt) << (e - 1);
+}
+
+/* Butterfly sum over 32 values, pairs (l, l^16), (l, l^8) ... (l, l^1): the order of a warp's xor-shuffle reduction. */
+static float q4o_butterfly32(float *v) {
+    for (int o = 16; o > 0; o >>= 1) {
+        float t[32];
+        for (int l = 0; l < 32; l++) t[l] = v[l] + v[l ^ o];
+        for (int l = 0; l < 32; l++) v[l] = t[l];
+    }
+    return v[0];
+}
+
+/* Non-greedy branch of sample(): sampler.h:85-115; softmax_logits_kernel gpu_kernels.h:507-556 (temperature, fp16
+ * rounding after the division, after exp and after the normalisation; the sum is taken over the unrounded exps);
+ * order and threshold sampler.h:92-104 (stable descending sort when 0 < topp < 1, threshold coin*topp; index order and
+ * threshold coin otherwise); selection sample_top_p_kernel gpu_kernels.h:561-592 (first position whose inclusive prefix
+ * sum >= threshold, else the last position). logits are replaced by the probabilities, as in the reference.
+ * Two choices where the reference leaves the order open: the sum of exps is taken per 1024-strided lane, then by
+ * butterfly over 32 lanes and over 32 warps (the CUDA kernel's order); the prefix sum is exact integer arithmetic on
+ * multiples of 2^-24 (the reference's device-wide scan accumulates in fp16 in an unspecified order). */
+int q4o_sample_topp(f16 *logits, int n, float temperature, float topp, float coin) {
+    float mx = -INFINITY;
+    for (int i = 0; i < n; i++) {
+        float val = q4o_h2f(logits[i]);
+        val /= temperature;
+        logits[i] = q4o_f2h(val);
+        if (q4o_h2f(logits[i]) > mx) mx = q4o_h2f(logits[i]);
+    }
+    float part[1024];
+    for (int t = 0; t < 1024; t++) part[t] = 0.f;
+    for (int i = 0; i < n; i++) {
+        float v = expf(q4o_h2f(logits[i]) - mx);
+        logits[i] = q4o_f2h(v);
+        part[i & 1023] += v; /* lane t sums i = t, t+1024, ... in order */
+    }
+    float wsum[32];
+    for (int w = 0; w < 32; w++) wsum[w] = q4o_butterfly32(part + 32 * w);
+    const float sum = q4o_butterfly32(wsum);
+    for (int i = 0; i < n; i++) logits[i] = q4o_f2h(q4o_h2f(logits[i]) / sum);
+
+    const int sorted = topp > 0.f && topp < 1.f;
+    const float threshold = sorted ? coin * topp : coin;
+    double td = ceil((double)threshold * 16777216.0);
+    unsigned long long need = td <= 1.0 ? 1ull : (td >= 9.0e18 ? ~0ull : (unsigned long long)td);
+    if (!sorted) {
+        if (!(threshold > 0.f)) return 0; /* prefix >= 0 holds at the first element whatever its probability */
+        unsigned long long c = 0;
+        for (int i = 0; i < n; i++) {
+            c += q4o_prob_units(logits[i]);
+            if (c >= need) return i;
+        }
+        return n - 1;
+    }
+    /* stable descending order by probability: counting sort on the fp16 bit pattern (non-negative values) */
+    int *order = (int *)malloc(sizeof(int) * (size_t)n);
+    int *start = (int *)calloc(65537, sizeof(int));
+    for (int i = 0; i < n; i++) start[65535 - logits[i]]++;
+    int acc = 0;
+    for (int k = 0; k < 65536; k++) { int c = start[k]; start[k] = acc; acc += c; }
+    for (int i = 0; i < n; i++) order[start[65535 - logits[i]]++] = i;
+    unsigned long long c = 0;
+    int res = order[n - 1];
+    for (int t = 0; t < n; t++) {
+        c += q4o_prob_units(logits[order[t]]);
+        if (c >= need) { res = order[t]; break; }
+    }
+    free(order);
+    free(start);
+    return res;
+}
+
 /* ------------------------------------------------------------------------------------------
  * Whole model on the packed file image (tensor order: weight_packer.cpp:256-291 written,
  * llama2_q4.cu:220-246 read). The image is the file's bytes in memory.

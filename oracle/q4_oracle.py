@@ -35,6 +35,10 @@ def lib():
         L.q4o_model_x.restype = C.c_void_p
         L.q4o_model_x.argtypes = [C.c_void_p]
         L.q4o_num_threads.restype = C.c_int
+        L.q4o_sample_topp.restype = C.c_int
+        L.q4o_sample_topp.argtypes = [C.c_void_p, C.c_int, C.c_float, C.c_float, C.c_float]
+        L.q4o_random_f32.restype = C.c_float
+        L.q4o_random_f32.argtypes = [C.c_void_p]
         _lib = L
     return _lib
 
@@ -130,6 +134,23 @@ def attention(q, kcache, vcache, n_heads, head_size, kv_mul, pos):
 def argmax(logits):
     logits = _c(logits, np.float16)
     return lib().q4o_argmax(_ptr(logits), logits.size)
+
+
+def sample_topp(logits, temperature, topp, coin):
+    """(token, probabilities): the non-greedy branch of the reference's sample(); `logits` is not modified."""
+    p = _c(logits, np.float16).copy()
+    tok = lib().q4o_sample_topp(_ptr(p), p.size, C.c_float(temperature), C.c_float(topp), C.c_float(coin))
+    return tok, p
+
+
+class Rng:
+    """The reference's xorshift* state (sampler.h:66-75)."""
+
+    def __init__(self, seed):
+        self.state = C.c_ulonglong(seed)
+
+    def f32(self):
+        return float(lib().q4o_random_f32(C.byref(self.state)))
 
 
 def allreduce_ref_order(parts, rank):
