@@ -189,8 +189,9 @@ int q4_comm_destroy(q4_comm* comm);
 typedef struct q4_model q4_model;
 
 #define Q4_TP_NONE 0   /* llama2_q4.cu:45-50 */
-#define Q4_TP_COLUMN 1
-#define Q4_TP_HYBRID 2
+#define Q4_TP_COLUMN 1 /* every matrix split by output columns, four all-gathers per layer (llama2_q4.cu:479-493, 510-524);
+                          served by forward paths 0 and 1 */
+#define Q4_TP_HYBRID 2 /* Megatron: column split for q/k/v/gate/up, row split for o/down, two all-reduces per layer; all paths */
 
 /* Reads the packed file (header + tensors in the order of weight_packer.cpp:256-291), keeps this rank's shard
  * on the current device (Megatron split of llama2_q4.cu:299-332, with row splits moved to 128-input group

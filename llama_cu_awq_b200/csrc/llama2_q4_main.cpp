@@ -190,8 +190,9 @@ void generate_thread(Shared* sh, const Vocab* vocab, const std::vector<int>* pro
         if (pos > 0) {
             next = mb->tokens[pos];
             if (next >= cfg.vocab_size || next < 0) next = 0;
-            if (rank == 0 && vocab->loaded()) {
-                fputs(vocab->decode(token, next).c_str(), stdout);
+            if (rank == 0) {
+                if (vocab->loaded()) fputs(vocab->decode(token, next).c_str(), stdout);
+                else printf(" %d", next);   // no vocabulary (token-id prompt, -k): the ids themselves
                 fflush(stdout);
             }
             if (next == kEos) break;
@@ -267,10 +268,6 @@ int main(int argc, char* argv[]) {
     if (topp < 0.0f || 1.0f < topp) topp = 0.9f;
     if (dataset_path) printf("Warning: dataset path is ignored in non-perplexity mode\n");
 
-    if (tp_mode == Q4_TP_COLUMN && gpu_count > 1) {
-        printf("Note: -x column (4 all-gathers per layer) is not part of this build; using -x hybrid\n");
-        tp_mode = Q4_TP_HYBRID;
-    }
 
     // header first, for the model summary the reference prints (llama2_q4.cu:633-634)
     q4_config cfg;

@@ -1643,7 +1643,7 @@ int q4_fused_prepare(q4_model* m) {
     m->fused = f;
     const q4_config& c = m->cfg;
     const int g = m->g;
-    if (m->head_size != 128 || (c.dim % 128) || (m->h_kc % 8) || c.dim > 4 * kCT * 8 ||   // 4 = staging batch
+    if (m->column || m->head_size != 128 || (c.dim % 128) || (m->h_kc % 8) || c.dim > 4 * kCT * 8 ||   // 4 = staging batch
         c.dim > kLLMaxDim || c.vocab_size > kLLMaxVocab || (m->v_n % 2) || (m->kv_n % 128) || (m->q_n % 128) ||
         (g > 1 && (!m->comm || q4_comm_world(m->comm) != g || q4_comm_rank(m->comm) != m->rank))) {
         f->unsupported = true;

@@ -180,7 +180,7 @@ extern "C" int q4_model_free(q4_model* m) {
 
 extern "C" int q4_model_load(q4_model** out, const char* path, int rank, int gpu_count, int tp_mode, q4_comm* comm) {
     if (!out || !path || gpu_count < 1 || gpu_count > Q4_MAX_GPUS || rank < 0 || rank >= gpu_count) return Q4_ERR_INVALID;
-    if (gpu_count > 1 && tp_mode != Q4_TP_HYBRID) return Q4_ERR_INVALID;  // column mode (4 all-gathers per layer) is not built
+    if (gpu_count > 1 && tp_mode != Q4_TP_HYBRID && tp_mode != Q4_TP_COLUMN) return Q4_ERR_INVALID;
     if (gpu_count > 1 && !comm) return Q4_ERR_INVALID;
 
     FileMap f;
@@ -222,7 +222,12 @@ extern "C" int q4_model_load(q4_model** out, const char* path, int rank, int gpu
     m->kv_n = kv_dim / g;
     m->o_kb = rank * (c.dim / g);
     m->o_kc = c.dim / g;
-    if (g > 1) q4_row_split_range(c.hidden_dim, g, rank, &m->h_kb, &m->h_kc);
+    m->column = g > 1 && tp_mode == Q4_TP_COLUMN;
+    if (m->column) {   // plain hidden/g slices (llama2_q4.cu:498): no row split, so no group alignment to keep
+        if (c.hidden_dim % (8 * g)) { delete m; return Q4_ERR_UNSUPPORTED_SIZE; }
+        m->h_kb = rank * (c.hidden_dim / g);
+        m->h_kc = c.hidden_dim / g;
+    } else if (g > 1) q4_row_split_range(c.hidden_dim, g, rank, &m->h_kb, &m->h_kc);
     else { m->h_kb = 0; m->h_kc = c.hidden_dim; }
     m->v_n = c.vocab_size / g;
     m->graph_ready[0] = m->graph_ready[1] = m->graph_ready[2] = false;
@@ -244,8 +249,10 @@ extern "C" int q4_model_load(q4_model** out, const char* path, int rank, int gpu
     add(2 * (size_t)c.dim);
     for (int l = 0; l < c.n_layers; l++) {
         auto addq = [&](int K, int N) { add((size_t)N * q4_pw(K) * 4); add((size_t)N * q4_pz(K) * 4); add((size_t)N * q4_groups(K) * 2); };
-        addq(c.dim, m->q_n); addq(c.dim, m->kv_n); addq(c.dim, m->kv_n); addq(m->o_kc, c.dim);
-        addq(c.dim, m->h_kc); addq(c.dim, m->h_kc); addq(m->h_kc, c.dim);
+        addq(c.dim, m->q_n); addq(c.dim, m->kv_n); addq(c.dim, m->kv_n);
+        if (m->column) addq(c.dim, c.dim / g); else addq(m->o_kc, c.dim);
+        addq(c.dim, m->h_kc); addq(c.dim, m->h_kc);
+        if (m->column) addq(c.hidden_dim, c.dim / g); else addq(m->h_kc, c.dim);
         add(2 * (size_t)c.dim); add(2 * (size_t)c.dim);
     }
     need += 256;
@@ -280,10 +287,12 @@ extern "C" int q4_model_load(q4_model** out, const char* path, int rank, int gpu
         LOAD_TRY(upload_q(a, &L.q, hq, col, rank * m->q_n, m->q_n, tmp));
         LOAD_TRY(upload_q(a, &L.k, hk, col, rank * m->kv_n, m->kv_n, tmp));
         LOAD_TRY(upload_q(a, &L.v, hv, col, rank * m->kv_n, m->kv_n, tmp));
-        LOAD_TRY(upload_q(a, &L.o, ho, row, m->o_kb, m->o_kc, tmp));
+        if (m->column) LOAD_TRY(upload_q(a, &L.o, ho, col, rank * (c.dim / g), c.dim / g, tmp));
+        else LOAD_TRY(upload_q(a, &L.o, ho, row, m->o_kb, m->o_kc, tmp));
         LOAD_TRY(upload_q(a, &L.up, hup, col, m->h_kb, m->h_kc, tmp));
         LOAD_TRY(upload_q(a, &L.gate, hgate, col, m->h_kb, m->h_kc, tmp));
-        LOAD_TRY(upload_q(a, &L.down, hdown, row, m->h_kb, m->h_kc, tmp));
+        if (m->column) LOAD_TRY(upload_q(a, &L.down, hdown, col, rank * (c.dim / g), c.dim / g, tmp));
+        else LOAD_TRY(upload_q(a, &L.down, hdown, row, m->h_kb, m->h_kc, tmp));
         LOAD_TRY(upload_raw(a, &L.rms_att, p, 2 * (size_t)c.dim));
         p += 2 * (size_t)c.dim;
         LOAD_TRY(upload_raw(a, &L.rms_ffn, p, 2 * (size_t)c.dim));
@@ -358,12 +367,25 @@ static int launch_token(q4_model* m, cudaStream_t s, int gen_token, bool handoff
         OP(q4_rope(s, m->q, m->kc, c.n_heads / g, c.n_kv_heads / g, hs, m->pos, loff, c.rope_theta));
         OP(q4_attention(s, m->xb + m->o_kb, m->q, m->kc + loff, m->vc + loff, m->attn_scratch, c.n_heads / g, hs, m->kv_mul,
                         c.seq_len, m->pos));
-        OP(q4_matmul_q4(s, m->x, m->xb + m->o_kb, &L.o.w, m->o_kc, dim, 1, g, -1, nullptr));
-        if (g > 1) OP(q4_all_reduce(m->comm, s, m->x, dim));
+        const int xs = rank * (dim / g), xn = dim / g;   // this rank's slice of x in column mode
+        if (m->column) {   // llama2_q4.cu:479-493: gather the attention output, o projection on a column slice, gather x
+            OP(q4_all_gather(m->comm, s, m->xb + m->o_kb, m->xb, m->o_kc));
+            OP(q4_matmul_q4(s, m->x + xs, m->xb, &L.o.w, dim, xn, 1, 1, -1, nullptr));
+            OP(q4_all_gather(m->comm, s, m->x + xs, m->x, xn));
+        } else {
+            OP(q4_matmul_q4(s, m->x, m->xb + m->o_kb, &L.o.w, m->o_kc, dim, 1, g, -1, nullptr));
+            if (g > 1) OP(q4_all_reduce(m->comm, s, m->x, dim));
+        }
         OP(q4_rmsnorm(s, m->xb, m->x, L.rms_ffn, dim));
         OP(q4_ffn_matvec_silu(s, m->hb + m->h_kb, m->xb, &L.gate.w, &L.up.w, dim, m->h_kc));
-        OP(q4_matmul_q4(s, m->x, m->hb + m->h_kb, &L.down.w, m->h_kc, dim, 1, g, -1, nullptr));
-        if (g > 1) OP(q4_all_reduce(m->comm, s, m->x, dim));
+        if (m->column) {   // llama2_q4.cu:510-524
+            OP(q4_all_gather(m->comm, s, m->hb + m->h_kb, m->hb, m->h_kc));
+            OP(q4_matmul_q4(s, m->x + xs, m->hb, &L.down.w, c.hidden_dim, xn, 1, 1, -1, nullptr));
+            OP(q4_all_gather(m->comm, s, m->x + xs, m->x, xn));
+        } else {
+            OP(q4_matmul_q4(s, m->x, m->hb + m->h_kb, &L.down.w, m->h_kc, dim, 1, g, -1, nullptr));
+            if (g > 1) OP(q4_all_reduce(m->comm, s, m->x, dim));
+        }
     }
     OP(q4_rmsnorm(s, m->x, m->x, m->rms_final, dim));
     OP(q4_matmul_f16(s, m->logits + (size_t)rank * m->v_n, m->x, m->wcls, dim, m->v_n, 1.0f));
@@ -469,7 +491,8 @@ extern "C" double q4_model_token_bytes(const q4_model* m, int pos) {
     const q4_config& c = m->cfg;
     double b = 0;
     auto qb = [](int K, int N) { return (double)qw_bytes(K, N); };
-    b += c.n_layers * (qb(c.dim, m->q_n) + 2 * qb(c.dim, m->kv_n) + qb(m->o_kc, c.dim) + 2 * qb(c.dim, m->h_kc) + qb(m->h_kc, c.dim));
+    const DevLayer& L0 = m->layers[0];
+    b += c.n_layers * (qb(c.dim, m->q_n) + 2 * qb(c.dim, m->kv_n) + qb(L0.o.K, L0.o.N) + 2 * qb(c.dim, m->h_kc) + qb(L0.down.K, L0.down.N));
     b += 2.0 * m->v_n * c.dim;                      // classifier
     b += 2.0 * c.dim * (2 * c.n_layers + 1);        // norm weights
     b += 2.0 * c.dim;                               // embedding row

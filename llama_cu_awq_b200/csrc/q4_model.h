@@ -29,6 +29,7 @@ struct q4_model {
     int o_kb, o_kc;           // local slice of the attention output vector (inputs of o_proj)
     int h_kb, h_kc;           // local slice of the hidden vector (outputs of gate/up, inputs of down)
     int v_n;                  // local classifier rows
+    bool column;              // -x column (llama2_q4.cu:479-493, 510-524): every matrix split by output columns, four all-gathers per layer
     // device memory
     char* arena;
     size_t arena_bytes;

@@ -13,12 +13,12 @@ from llama_cu_awq_b200 import synth
 pytestmark = [pytest.mark.gpu, pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")]
 
 
-def _run_tp(cfg, fwd_path, n, tmp_path):
+def _run_tp(cfg, fwd_path, n, tmp_path, mode="hybrid"):
     path = str(tmp_path / f"{cfg}.bin")
     synth.write_model_file(path, cfg, seed=7)
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
-           "--master-port", str(29500 + fwd_path + (10 if cfg == "mid" else 20) + 40 * (n - 2)), os.path.join(ROOT, "tests", "tp_worker.py"), cfg, path, str(fwd_path)]
+           "--master-port", str(29500 + fwd_path + (10 if cfg == "mid" else 20) + 40 * (n - 2) + (5 if mode == "column" else 0)), os.path.join(ROOT, "tests", "tp_worker.py"), cfg, path, str(fwd_path), mode]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert "ranks identical: True" in r.stdout
@@ -28,6 +28,13 @@ def _run_tp(cfg, fwd_path, n, tmp_path):
 @pytest.mark.parametrize("fwd_path", [0, 1, 2])
 def test_tp2_logits_match_single_gpu_oracle(cfg, fwd_path, tmp_path):
     _run_tp(cfg, fwd_path, 2, tmp_path)
+
+
+@pytest.mark.parametrize("cfg", ["mid", "mid-gqa"])
+@pytest.mark.parametrize("fwd_path", [0, 1])
+def test_tp2_column_mode(cfg, fwd_path, tmp_path):
+    """-x column (llama2_q4.cu:479-493, 510-524): all matrices split by output columns, four all-gathers per layer."""
+    _run_tp(cfg, fwd_path, 2, tmp_path, mode="column")
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")

@@ -17,12 +17,13 @@ from llama_cu_awq_b200.model import Transformer  # noqa: E402
 
 def main():
     cfg_name, path, fwd_path = sys.argv[1], sys.argv[2], int(sys.argv[3])
+    tp_mode = _lib.Q4_TP_COLUMN if len(sys.argv) > 4 and sys.argv[4] == "column" else _lib.Q4_TP_HYBRID
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     comm = ProcessComm(rank, world, dist)
-    t = Transformer(path, rank=rank, gpu_count=world, tp_mode=_lib.Q4_TP_HYBRID, comm=comm.handle)
+    t = Transformer(path, rank=rank, gpu_count=world, tp_mode=tp_mode, comm=comm.handle)
     vocab = synth.CONFIGS[cfg_name][5]
     tokens = np.random.default_rng(0).integers(3, vocab, size=24, dtype=np.int32)
     t.reset(tokens, 0)
