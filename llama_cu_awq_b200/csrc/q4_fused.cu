@@ -24,7 +24,6 @@
 //
 // Every wait is bounded (mbarrier polls, tag polls and barrier spins are limited by the global timer); on expiry the
 // kernel records Q4_ERR_TIMEOUT in a status word, all later waits fall through, and the kernel returns.
-#include <cooperative_groups.h>
 #include <math_constants.h>
 #include <stdio.h>
 #include <stdlib.h>
@@ -145,7 +144,8 @@ struct FParams {
     int* status;
     int write_token;
     int no_handoff;              // 1: leave the token mailbox and the position alone (a sampling kernel follows on the stream)
-    int debug;                   // measurement only: 1 = consumers skip the GEMV math (pure streaming), 2 = no streaming (pure math)
+    int debug;                   // measurement only: 1 = consumers skip the GEMV math (pure streaming), 2 = no streaming (pure math),
+                                 // 8 = raw ring throughput, 16 = tensor-parallel exchange kept local (no NVLink dependency)
     int n_entries;               // ring entries of kEntryBytes each
     int split_len;               // positions per attention split (a head is split in ceil(T / split_len) parts, at most nsplit)
     unsigned long long* trace;   // optional: [2 CTAs][nphases][4] device timestamps (ns), or null
@@ -426,11 +426,10 @@ __device__ __forceinline__ void load_x_batch(uint4 (&xv)[NB], const bool (&valid
 // The consumers enumerate the same order with plain arithmetic.
 struct SlotCursor {
     int pi, u, u_end, tt, kt;   // u, u_end: index of the unit inside this CTA's list
-    int wrapped, count;
     FPhase* cache;   // shared-memory copy of phases[pi] (the table itself lives in global memory)
     int cached_pi;
 };
-__device__ __forceinline__ void cursor_init(SlotCursor& c) { c.pi = -1; c.u = 0; c.u_end = 0; c.tt = 0; c.kt = 0; c.wrapped = 0; c.count = 0; c.cached_pi = -1; }
+__device__ __forceinline__ void cursor_init(SlotCursor& c) { c.pi = -1; c.u = 0; c.u_end = 0; c.tt = 0; c.kt = 0; c.cached_pi = -1; }
 __device__ __forceinline__ void copy_phase(FPhase* dst, const FPhase* src) {
     const int4* s4 = reinterpret_cast<const int4*>(src);
     int4* d4 = reinterpret_cast<int4*>(dst);
@@ -457,7 +456,6 @@ __device__ __forceinline__ bool cursor_next(SlotCursor& c, const FParams& p, int
                 bytes = len * 2;
                 if (++c.kt == ph.nkt) { c.kt = 0; if (++c.tt == 2) { c.tt = 0; c.u++; } }
             }
-            c.count++;
             return true;
         }
         if (++c.pi >= p.nphases) return false;
@@ -1111,7 +1109,14 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                         sum += oldf / p.gpu_count;   // each rank adds x / g (gpu_kernels.h:237-238)
                         const uint32_t word = tagged(__float2half(sum), out_tag);
                         const size_t off2 = (size_t)p.rank * kLLMaxDim + n;
-                        for (int peer = 0; peer < p.g; peer++) st_tagged(p.xb[ph.xbuf_out][peer] + off2, word);
+                        if (p.debug & 16) {
+                            // measurement only: the same stores, but all into this rank's own area (zeros as the peers'
+                            // partials), so that no step waits on NVLink: step time minus this = exposed exchange time
+                            for (int r2 = 0; r2 < p.g; r2++)
+                                st_tagged(p.xb[ph.xbuf_out][p.rank] + (size_t)r2 * kLLMaxDim + n, r2 == p.rank ? word : out_tag);
+                        } else {
+                            for (int peer = 0; peer < p.g; peer++) st_tagged(p.xb[ph.xbuf_out][peer] + off2, word);
+                        }
                     } else {
                         const FMat& m = ph.m[mi];
                         const __half hv = __float2half(sum);
@@ -1374,7 +1379,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                 const __half hv = __float2half(sum);
                 if (p.g == 1) p.logits[n] = hv;
                 else   // the all-gather of the logits: this rank's slice goes to every rank (plain peer stores)
-                    for (int peer = 0; peer < p.g; peer++) p.ll_logits[peer][n] = __half_as_ushort(hv);
+                    for (int peer = 0; peer < p.g; peer++) p.ll_logits[(p.debug & 16) ? p.rank : peer][n] = __half_as_ushort(hv);
                 const float v = __half2float(hv);
                 if (v > best || (v == best && n < bi)) { best = v; bi = n; }
             }
@@ -1427,8 +1432,10 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                     if (lane == 0) {
                         __threadfence_system();
                         for (int peer = 0; peer < p.g; peer++) {
-                            asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(p.cand[peer] + slot), "l"(tg | __float_as_uint(best)) : "memory");
-                            asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(p.cand[peer] + slot + 1), "l"(tg | (unsigned)bi) : "memory");
+                            // (debug 16: into this rank's own mailbox, once per rank slot)
+                            unsigned long long* dst = (p.debug & 16) ? p.cand[p.rank] + ((size_t)p.launch_parity * Q4_MAX_GPUS + peer) * 2 : p.cand[peer] + slot;
+                            asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(dst), "l"(tg | __float_as_uint(best)) : "memory");
+                            asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(dst + 1), "l"(tg | (unsigned)bi) : "memory");
                         }
                     }
                     best = -CUDART_INF_F;
