@@ -535,46 +535,69 @@ __device__ __forceinline__ uint4 attn_word_merge(const AttnWord& w) {
 // X = rint(v * 16256 / amax) and its high digit rint(v * 127 / amax) come out of two FMAs with the 1.5 * 2^23 magic
 // constant (the integer sits in the low mantissa bits), the low digit is X - 128 * hi (|lo| <= 64), and the digits
 // are gathered into the DP4A operand words with byte permutes.
-__device__ __forceinline__ void quant_word(const uint4& hv, int wd, int nwords, uint4* xq, float* xs_scale, int* xs_sum) {
-    const __half2* h = reinterpret_cast<const __half2*>(&hv);
-    const __half2 m2 = __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3])));
-    float amax = fmaxf(__low2float(m2), __high2float(m2));
-#pragma unroll
-    for (int o = 1; o < 16; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));  // 16 words = 1 group
-    const float sx = amax * (1.0f / 16256.0f);
-    const float inv = amax > 0.f ? 16256.0f / amax : 0.f;
-    const float inv128 = inv * (1.0f / 128.0f);
+// NW words are processed in lockstep so that their shuffle and conversion chains overlap.
+template <int NW>
+__device__ __forceinline__ void quant_words(const uint4 (&hv)[NW], const int (&wd)[NW], int nwords, uint4* xq, float* xs_scale, int* xs_sum) {
     constexpr float kMagic = 12582912.0f;      // 1.5 * 2^23
     constexpr int kMagicBits = 0x4B400000;
-    int xb[8], hb[8], lb[8];
+    float amax[NW];
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
-        const float2 f = __half22float2(h[j]);
-        xb[2 * j] = __float_as_int(fmaf(f.x, inv, kMagic));
-        xb[2 * j + 1] = __float_as_int(fmaf(f.y, inv, kMagic));
-        hb[2 * j] = __float_as_int(fmaf(f.x, inv128, kMagic));
-        hb[2 * j + 1] = __float_as_int(fmaf(f.y, inv128, kMagic));
+    for (int w = 0; w < NW; w++) {
+        const __half2* h = reinterpret_cast<const __half2*>(&hv[w]);
+        const __half2 m2 = __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3])));
+        amax[w] = fmaxf(__low2float(m2), __high2float(m2));
     }
-    int sum = -8 * kMagicBits;
 #pragma unroll
-    for (int j = 0; j < 8; j++) {
-        sum += xb[j];
-        lb[j] = xb[j] - (hb[j] << 7);   // low byte = X - 128 * hi (the magic constants cancel in the low byte)
+    for (int o = 1; o < 16; o <<= 1)   // 16 words = 1 group
+#pragma unroll
+        for (int w = 0; w < NW; w++) amax[w] = fmaxf(amax[w], __shfl_xor_sync(0xffffffffu, amax[w], o));
+    int sum[NW];
+    uint32_t he[NW], ho[NW], le[NW], lo[NW];
+#pragma unroll
+    for (int w = 0; w < NW; w++) {
+        const __half2* h = reinterpret_cast<const __half2*>(&hv[w]);
+        const float inv = amax[w] > 0.f ? 16256.0f / amax[w] : 0.f;
+        const float inv128 = inv * (1.0f / 128.0f);
+        int xb[8], hb[8], lb[8];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float2 f = __half22float2(h[j]);
+            xb[2 * j] = __float_as_int(fmaf(f.x, inv, kMagic));
+            xb[2 * j + 1] = __float_as_int(fmaf(f.y, inv, kMagic));
+            hb[2 * j] = __float_as_int(fmaf(f.x, inv128, kMagic));
+            hb[2 * j + 1] = __float_as_int(fmaf(f.y, inv128, kMagic));
+        }
+        int sm = (int)(0u - 8u * (unsigned)kMagicBits);
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            sm += xb[j];
+            lb[j] = xb[j] - (hb[j] << 7);   // low byte = X - 128 * hi (the magic constants cancel in the low byte)
+        }
+        sum[w] = sm;
+        // byte 0 of four registers -> one word: (a, b) -> [a.b0, b.b0], then the two halves together
+        he[w] = prmt(prmt(hb[0], hb[2], 0x0040), prmt(hb[4], hb[6], 0x0040), 0x5410);
+        ho[w] = prmt(prmt(hb[1], hb[3], 0x0040), prmt(hb[5], hb[7], 0x0040), 0x5410);
+        le[w] = prmt(prmt(lb[0], lb[2], 0x0040), prmt(lb[4], lb[6], 0x0040), 0x5410);
+        lo[w] = prmt(prmt(lb[1], lb[3], 0x0040), prmt(lb[5], lb[7], 0x0040), 0x5410);
     }
-    // byte 0 of four registers -> one word: (a, b) -> [a.b0, b.b0], then the two halves together
-    const uint32_t he = prmt(prmt(hb[0], hb[2], 0x0040), prmt(hb[4], hb[6], 0x0040), 0x5410);
-    const uint32_t ho = prmt(prmt(hb[1], hb[3], 0x0040), prmt(hb[5], hb[7], 0x0040), 0x5410);
-    const uint32_t le = prmt(prmt(lb[0], lb[2], 0x0040), prmt(lb[4], lb[6], 0x0040), 0x5410);
-    const uint32_t lo = prmt(prmt(lb[1], lb[3], 0x0040), prmt(lb[5], lb[7], 0x0040), 0x5410);
-    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-    sum += __shfl_xor_sync(0xffffffffu, sum, 4);  // 8 words = the 64 inputs of one (group, half)
-    if (wd < nwords) {
-        const int g = wd >> 4, c = (wd >> 2) & 3, wi = wd & 3;
-        const int kt = g >> 4, lane = 2 * (g & 15) + (c >> 1), j2 = c & 1;
-        xq[((kt * 2 + j2) * 4 + wi) * 32 + lane] = make_uint4(he, ho, le, lo);
-        if ((wd & 7) == 0) { xs_scale[kt * 32 + lane] = sx; xs_sum[kt * 32 + lane] = sum; }
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1)   // 8 words = the 64 inputs of one (group, half)
+#pragma unroll
+        for (int w = 0; w < NW; w++) sum[w] += __shfl_xor_sync(0xffffffffu, sum[w], o);
+#pragma unroll
+    for (int w = 0; w < NW; w++) {
+        if (wd[w] < nwords) {
+            const int g = wd[w] >> 4, c = (wd[w] >> 2) & 3, wi = wd[w] & 3;
+            const int kt = g >> 4, lane = 2 * (g & 15) + (c >> 1), j2 = c & 1;
+            xq[((kt * 2 + j2) * 4 + wi) * 32 + lane] = make_uint4(he[w], ho[w], le[w], lo[w]);
+            if ((wd[w] & 7) == 0) { xs_scale[kt * 32 + lane] = amax[w] * (1.0f / 16256.0f); xs_sum[kt * 32 + lane] = sum[w]; }
+        }
     }
+}
+__device__ __forceinline__ void quant_word(const uint4& hv, int wd, int nwords, uint4* xq, float* xs_scale, int* xs_sum) {
+    const uint4 h1[1] = {hv};
+    const int w1[1] = {wd};
+    quant_words<1>(h1, w1, nwords, xq, xs_scale, xs_sum);
 }
 
 // Splits per head at sequence length T: short contexts are not split at all (one CTA per head, no partial traffic).
@@ -688,8 +711,10 @@ __device__ void stage_x_quant(const FPhase& ph, const FParams& p, int pos, uint4
                 if (bad == 0 || !keep_polling(polls, t0, p.status, 0x80000 + ph.in_phase)) break;
             }
             if (tr && it0 == 0) tr[4] = global_ns();
-            quant_word(attn_word_merge(w0), wd0, nwords, xq, xs_scale, xs_sum);
-            if (it0 + 1 < iters) quant_word(attn_word_merge(w1), wd1, nwords, xq, xs_scale, xs_sum);
+            // (a word index past the vector quantises zeros and stores nothing)
+            const uint4 hv2[2] = {attn_word_merge(w0), attn_word_merge(w1)};
+            const int wd2[2] = {wd0, wd1};
+            quant_words<2>(hv2, wd2, nwords, xq, xs_scale, xs_sum);
         }
         consumer_sync();
         return;
@@ -730,19 +755,25 @@ __device__ void stage_x_quant(const FPhase& ph, const FParams& p, int pos, uint4
     const float inv_rms = 1.0f / sqrtf(ss);
     if (tr) tr[5] = global_ns();
 #pragma unroll
-    for (int b = 0; b < 4; b++) {
-        if (b < iters) {  // uniform over the block: the shuffles in quant_word see all lanes
-            // val = x * (inv_rms * w), rounded to fp16 once (gpu_kernels.h:100-102)
-            uint4 hv;
-            const __half2* xh = reinterpret_cast<const __half2*>(&xv[b]);
-            const __half2* wh = reinterpret_cast<const __half2*>(&wv[b]);
-            __half2* oh = reinterpret_cast<__half2*>(&hv);
+    for (int b0 = 0; b0 < 4; b0 += 2) {
+        if (b0 < iters) {  // uniform over the block: the shuffles in quant_words see all lanes
+            // val = x * (inv_rms * w), rounded to fp16 once (gpu_kernels.h:100-102); two words in lockstep (a word
+            // index past the vector holds zeros and stores nothing)
+            uint4 hv[2];
+            int wd2[2];
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const float2 xf2 = __half22float2(xh[j]), wf2 = __half22float2(wh[j]);
-                oh[j] = __floats2half2_rn(xf2.x * (inv_rms * wf2.x), xf2.y * (inv_rms * wf2.y));
+            for (int b = 0; b < 2; b++) {
+                const __half2* xh = reinterpret_cast<const __half2*>(&xv[b0 + b]);
+                const __half2* wh = reinterpret_cast<const __half2*>(&wv[b0 + b]);
+                __half2* oh = reinterpret_cast<__half2*>(&hv[b]);
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const float2 xf2 = __half22float2(xh[j]), wf2 = __half22float2(wh[j]);
+                    oh[j] = __floats2half2_rn(xf2.x * (inv_rms * wf2.x), xf2.y * (inv_rms * wf2.y));
+                }
+                wd2[b] = ctid + (b0 + b) * kCT;
             }
-            quant_word(hv, ctid + b * kCT, nwords, xq, xs_scale, xs_sum);
+            quant_words<2>(hv, wd2, nwords, xq, xs_scale, xs_sum);
         }
     }
     if (tr) tr[6] = global_ns();
