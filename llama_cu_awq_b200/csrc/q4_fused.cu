@@ -203,6 +203,7 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kCT) : "memory"); }
+__device__ __forceinline__ void phase_fetch_wait() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 __device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {
     int d;
     asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
@@ -287,7 +288,9 @@ __device__ __forceinline__ float transpose_reduce8(const float acc[8], int lane)
     return a1;
 }
 
-// Sum over the consumer threads; every consumer thread gets the total. red: 8 floats of shared memory.
+// Sum over the consumer threads; every consumer thread gets the total. red: kCW floats of shared memory.
+// REUSE_BARRIER = false: the caller guarantees a consumer-wide barrier before `red` is written again.
+template <bool REUSE_BARRIER = true>
 __device__ __forceinline__ float consumer_sum(float v, float* red, int ctid) {
     v = warp_sum(v);
     if ((ctid & 31) == 0) red[ctid >> 5] = v;
@@ -295,7 +298,7 @@ __device__ __forceinline__ float consumer_sum(float v, float* red, int ctid) {
     float t = 0.f;
 #pragma unroll
     for (int i = 0; i < kCW; i++) t += red[i];
-    consumer_sync();
+    if (REUSE_BARRIER) consumer_sync();
     return t;
 }
 
@@ -749,7 +752,7 @@ __device__ void stage_x_quant(const FPhase& ph, const FParams& p, int pos, uint4
         if (iters > 2) stage_words<2, 4, true, true>(ph, p, base, g, want, 2, iters, nwords, xq, xs_scale, xs_sum, ctid, ss, gave_up, xv + 2);
     }
     if (tr) tr[4] = global_ns();
-    ss = consumer_sum(ss, red, ctid);
+    ss = consumer_sum<false>(ss, red, ctid);   // the staging's closing barrier comes before any other use of `red`
     ss /= K;
     ss += 1e-5f;
     const float inv_rms = 1.0f / sqrtf(ss);
@@ -891,6 +894,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
     __shared__ float red[kCW];
     __shared__ int s_abort;
     __shared__ __align__(16) FPhase s_cph;     // consumers' phase descriptor
+    __shared__ __align__(16) FPhase s_next;    // the next one, on its way in
     __shared__ int s_unit_cnt[kMaxUnitsPerCta];  // slots done per unit of the current phase
 
     uint8_t* ring = smem;
@@ -977,10 +981,22 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
     const int HS = p.head_size;
     const float inv_entries = 1.0f / (float)kEntries;
 
+    // Phase descriptors are fetched one phase ahead with asynchronous copies (no register is held, nothing waits on the
+    // L2 round trip): the copy of phase pi + 1 into s_next is issued at the top of phase pi and completed before the
+    // barrier that closes phase pi; the next phase starts by moving it to the fixed place the code reads it from.
+    constexpr int kPhaseVecs = (int)(sizeof(FPhase) / 16);
+    auto fetch_phase = [&](int which) {
+        if (which < p.nphases && ctid < kPhaseVecs)
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(smem_u32(reinterpret_cast<int4*>(&s_next) + ctid)),
+                         "l"(reinterpret_cast<const int4*>(p.phases + which) + ctid) : "memory");
+    };
+    fetch_phase(0);
+    phase_fetch_wait();
+    consumer_sync();
     for (int pi = 0; pi < p.nphases; pi++) {
-        if (ctid < (int)(sizeof(FPhase) / 16))
-            reinterpret_cast<int4*>(&s_cph)[ctid] = __ldg(reinterpret_cast<const int4*>(p.phases + pi) + ctid);
+        if (ctid < kPhaseVecs) reinterpret_cast<int4*>(&s_cph)[ctid] = reinterpret_cast<const int4*>(&s_next)[ctid];
         consumer_sync();
+        fetch_phase(pi + 1);   // by the threads that have just read s_next
         const FPhase& ph = s_cph;
         // all consumer threads leave together (named barriers count live threads), never one by one:
         // s_abort is written by thread 0 inside grid_barrier and read after the barrier's closing consumer_sync
@@ -1006,6 +1022,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                 sbase += nslots;
                 ent0 += (nslots + 1) >> 1;
             }
+            phase_fetch_wait();
             consumer_sync();
             continue;
         }
@@ -1027,7 +1044,8 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                     }
                 }
             }
-            consumer_sync();  // nobody may still be reading this phase's descriptor when the next one replaces it
+            phase_fetch_wait();
+            consumer_sync();  // closes the phase: the next descriptor is in place, this one may be replaced from now on
 
         } else if (ph.type == PH_GEMV) {
             if (ctid < kMaxUnitsPerCta) s_unit_cnt[ctid] = 0;   // ordered before the first count by the staging's closing barrier
@@ -1159,8 +1177,9 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
             sbase += nslots;
             ent0 += (nslots + 1) >> 1;
             TRACE(2);
+            phase_fetch_wait();
             if (ph.barrier_after) grid_barrier(p, nbar, ctid, &s_abort);
-            else consumer_sync();  // the phase descriptor in shared memory is replaced next
+            else consumer_sync();  // closes the phase
             TRACE(3);
 
         } else if (ph.type == PH_ATTN) {
@@ -1347,6 +1366,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                 consumer_sync();
             }
             TRACE(2);
+            phase_fetch_wait();
             consumer_sync();   // no grid barrier: the partials are tagged and the o projection polls them
             TRACE(3);
 
@@ -1434,6 +1454,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                 p.cand_idx[cta] = bi;
             }
             TRACE(2);
+            phase_fetch_wait();
             grid_barrier(p, nbar, ctid, &s_abort);
             TRACE(3);
 
