@@ -1176,10 +1176,15 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
             }
             sbase += nslots;
             ent0 += (nslots + 1) >> 1;
+            if (p.trace && cta == 0 && lane == 0) p.trace[(size_t)2 * p.nphases * kTraceCols + (size_t)pi * 16 + cw] = global_ns();   // per-warp finish time
             TRACE(2);
             phase_fetch_wait();
+            if (p.trace && cta == 0 && lane == 0 && (cw == 0 || cw == kCW - 1))
+                p.trace[(size_t)2 * p.nphases * kTraceCols + (size_t)pi * 16 + (cw == 0 ? 11 : 13)] = global_ns();
             if (ph.barrier_after) grid_barrier(p, nbar, ctid, &s_abort);
             else consumer_sync();  // closes the phase
+            if (p.trace && cta == 0 && lane == 0 && (cw == 0 || cw == kCW - 1))
+                p.trace[(size_t)2 * p.nphases * kTraceCols + (size_t)pi * 16 + (cw == 0 ? 12 : 14)] = global_ns();
             TRACE(3);
 
         } else if (ph.type == PH_ATTN) {
@@ -1987,7 +1992,7 @@ extern "C" int q4_model_trace(q4_model* m, unsigned long long* out, int* phase_t
     if (!m) return Q4_ERR_INVALID;
     if (int e = q4_fused_prepare(m)) return e;
     q4_fused* f = m->fused;
-    const size_t n = (size_t)2 * f->nphases * kTraceCols;
+    const size_t n = (size_t)2 * f->nphases * kTraceCols + (size_t)f->nphases * 16;   // + per-warp finish times of CTA 0
     if (!f->trace) {
         if (int e = fused_alloc(f, (void**)&f->trace, n * sizeof(unsigned long long))) return e;
         Q4_CUDA_TRY(cudaMemset(f->trace, 0, n * sizeof(unsigned long long)));

@@ -15,6 +15,7 @@ CONFIGS = {
     "tiny-gqa": (512, 768, 2, 4, 2, 512, 64, 10000.0),
     "mid": (1024, 2816, 2, 8, 8, 2048, 128, 10000.0),      # 22 groups in the down projection: a full and a partial k-tile
     "mid-gqa": (1024, 2816, 2, 8, 2, 2048, 128, 10000.0),
+    "mid-long": (1024, 2816, 2, 8, 2, 2048, 2048, 10000.0),         # long context on a small model (attention over > 1000 positions)
     "llama2-13b-1l": (5120, 13824, 1, 40, 40, 4096, 128, 10000.0),   # 13B / 70B layer shapes, one layer, small vocabulary:
     "llama2-70b-1l": (8192, 28672, 1, 64, 8, 4096, 128, 10000.0),    # shape coverage (3, 4, 7 and 14 k-tiles, 8 query heads per KV head)
     "llama2-7b-4l": (4096, 11008, 4, 32, 32, 32000, 2048, 10000.0),  # 7B layer shapes, 4 layers: profiling-sized

@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 import torch
 
-from conftest import GOLDEN, assert_close
+from conftest import GOLDEN, MAX_REL, assert_close
 from llama_cu_awq_b200 import _lib, synth
 from llama_cu_awq_b200.model import Transformer
 from oracle import q4_oracle as O
@@ -131,6 +131,40 @@ def test_fused_attention_splits(mid_gqa_path, monkeypatch):
     got, ref = teacher_forced(mid_gqa_path, tokens, 2)
     for pos in (0, 7, 8, 9, 23, 24, 25, 40, 59):
         assert_close(got[pos], ref[pos], f"split attention, pos {pos}")
+
+
+def test_long_context_fused_vs_per_op(tmp_path):
+    """1100 positions: the fused kernel's attention (four splits per head, several steps per split, RoPE table far out)
+    against the per-op path, whose attention kernel is held to the oracle up to position 4095 at op level. The first
+    24 positions are also checked against the oracle, so both runs start from verified state."""
+    path = str(tmp_path / "mid_long.bin")
+    synth.write_model_file(path, "mid-long", seed=21)
+    vocab = synth.CONFIGS["mid-long"][5]
+    n = 1100
+    tokens = np.random.default_rng(9).integers(3, vocab, size=n, dtype=np.int32)
+    keep = set(range(24)) | set(range(170, 180)) | set(range(n - 12, n))
+    logits = {}
+    for fwd_path in (1, 2):
+        t = Transformer(path)
+        assert fwd_path != 2 or t.best_path() == 2
+        t.reset(tokens, 0)
+        out = {}
+        for pos in range(n):
+            t.forward(gen_token=False, path=fwd_path)
+            if pos in keep:
+                t.synchronize()
+                out[pos] = t.logits()
+        t.synchronize()
+        assert t.status() == 0
+        t.close()
+        logits[fwd_path] = out
+    m = O.Model(open(path, "rb").read())
+    for pos in range(24):
+        m.forward(int(tokens[pos]), pos, order=0)
+        assert_close(logits[2][pos], m.logits(), f"fused path vs oracle at pos {pos}")
+    # two paths that are each within the tolerance of the oracle are within twice the tolerance of each other
+    for pos in sorted(keep):
+        assert_close(logits[2][pos], logits[1][pos], f"fused vs per-op path at pos {pos}", max_rel=2 * MAX_REL)
 
 
 def test_fused_and_graph_paths_share_the_kv_cache(mid_path):
