@@ -241,10 +241,10 @@ double q4_model_token_bytes(const q4_model* model, int pos);
 int q4_model_time_ffn(q4_model* model, void* stream, int reps, double* total_ms, double* bytes_per_launch);
 
 /* Profiling hook of the fused path: the first call arms per-phase device timestamps (globaltimer, ns) for the
- * following launches; later calls copy the last launch's stamps to `out` (32 words per phase:
- * [2 CTAs][nphases][8] = phase start, inputs staged, weights consumed, phase closed, then staging detail: loads
- * back, norm reduced, quantised; followed by [nphases][16] = finish time of each consumer warp of CTA 0)
- * and a type code per phase. Returns the phase count (always larger than any status code) or a status code. */
+ * following launches; later calls copy the last launch's stamps to `out` ([2 CTAs][nphases][8]: phase start,
+ * inputs staged, weights consumed, phase closed, then staging detail: loads back, norm reduced, quantised)
+ * and a type code per phase. The stamps are global stores and perturb what they measure by a few tenths of a
+ * microsecond. Returns the phase count (always larger than any status code) or a status code. */
 int q4_model_trace(q4_model* model, unsigned long long* out, int* phase_types, int max_phases);
 
 /* Host-side shard helpers (no GPU needed): copy rank `rank`'s shard of a quantized matrix held in host

@@ -895,7 +895,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
     __shared__ int s_abort;
     __shared__ __align__(16) FPhase s_cph;     // consumers' phase descriptor
     __shared__ __align__(16) FPhase s_next;    // the next one, on its way in
-    __shared__ int s_unit_cnt[kMaxUnitsPerCta];  // slots done per unit of the current phase
+    __shared__ uint64_t unit_bar[kMaxUnitsPerCta];  // per unit of the current phase: completes when all its slots are done
 
     uint8_t* ring = smem;
     uint4* xq = reinterpret_cast<uint4*>(smem + (size_t)p.n_entries * kEntryBytes);
@@ -909,6 +909,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
     if (tid == 0) {
         s_abort = 0;
         for (int s = 0; s < kMaxEntries; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 2); s_round[s] = 0xFFFFFFFFu; }
+        for (int s = 0; s < kMaxUnitsPerCta; s++) mbar_init(&unit_bar[s], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -1048,7 +1049,10 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
             consumer_sync();  // closes the phase: the next descriptor is in place, this one may be replaced from now on
 
         } else if (ph.type == PH_GEMV) {
-            if (ctid < kMaxUnitsPerCta) s_unit_cnt[ctid] = 0;   // ordered before the first count by the staging's closing barrier
+            if (ctid < kMaxUnitsPerCta) {   // re-armed for this phase's slots per unit; the staging's closing barrier orders it before the first arrival
+                asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_u32(&unit_bar[ctid])) : "memory");
+                mbar_init(&unit_bar[ctid], ph.tpu * ph.nkt);
+            }
             stage_x_quant(ph, p, pos, xq, xs_scale, xs_sum, red, ctid,
                           (p.trace && ctid == 0 && cta == 0) ? p.trace + (size_t)pi * kTraceCols : nullptr);
             TRACE(1);
@@ -1090,15 +1094,17 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                 if (lane == 0) {
                     // an entry is released by its two slots; a phase's odd last slot releases it alone
                     if (!(dbg & 2)) mbar_arrive(&empty_bar[e], (!(li & 1) && li + 1 == (unsigned)nslots) ? 2 : 1);
-                    __threadfence_block();   // the slot's partials before the count
-                    atomicAdd(&s_unit_cnt[ul], 1);
+                    mbar_arrive(&unit_bar[ul], 1);   // release: the slot's partials are written
                 }
                 if ((int)li - ul * spu != spu - 1) continue;
                 // ---- this warp finishes unit ul ----
-                if (lane == 0 && spu > 1) {
+                // output index of this lane's column, looked up before the wait (shared-memory reads off the critical path)
+                int mi, rt;
+                tile_info(ph, unit_at(ul, cta, grid) * tpu, mi, rt);
+                if (spu > 1) {   // every lane waits (acquire): no warp-level hand-over needed afterwards
                     unsigned polls = 0;
                     unsigned long long t0 = 0;
-                    while (*(volatile int*)&s_unit_cnt[ul] < spu) {
+                    while (!mbar_try(&unit_bar[ul], 0)) {
                         if ((++polls & 1023u) == 0) {
                             if (*(volatile int*)p.status != 0) break;
                             const unsigned long long now = global_ns();
@@ -1110,8 +1116,6 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                         }
                     }
                 }
-                __syncwarp();
-                __threadfence_block();
                 float oldf = 0.f;
                 if (epi == EPI_RESIDUAL) {
                     // Old x = the other buffer's g partials (this CTA staged that whole buffer in an earlier phase, so
@@ -1139,15 +1143,21 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                 }
                 if (lane < 8) {
                     const int r = lane;
-                    int mi, rt;
-                    tile_info(ph, unit_at(ul, cta, grid) * tpu, mi, rt);
                     const float* pu = part + (size_t)ul * spu * 8 + r;
-                    float sum = 0.f;
-                    for (int k2 = 0; k2 < nkt; k2++) sum += pu[k2 * 8];
+                    // per-slot partials in slot order; four loads in flight at a time
+                    auto sum_slots = [&](const float* q) {
+                        float acc = 0.f;
+                        for (int k2 = 0; k2 < nkt; k2 += 4) {
+                            const float v0 = q[k2 * 8], v1 = k2 + 1 < nkt ? q[(k2 + 1) * 8] : 0.f;
+                            const float v2 = k2 + 2 < nkt ? q[(k2 + 2) * 8] : 0.f, v3 = k2 + 3 < nkt ? q[(k2 + 3) * 8] : 0.f;
+                            acc += v0; acc += v1; acc += v2; acc += v3;
+                        }
+                        return acc;
+                    };
+                    float sum = sum_slots(pu);
                     const int n = rt * 8 + r;
                     if (epi == EPI_SILU) {
-                        float up = 0.f;
-                        for (int k2 = 0; k2 < nkt; k2++) up += pu[(nkt + k2) * 8];
+                        const float up = sum_slots(pu + nkt * 8);
                         st_tagged(ph.m[0].out + n, tagged(__float2half(silu_mul(sum, up)), out_tag));
                     } else if (epi == EPI_RESIDUAL) {
                         // This rank's partial of the new x goes into its slot on every rank. Ordering: a rank that writes
@@ -1176,7 +1186,6 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
             }
             sbase += nslots;
             ent0 += (nslots + 1) >> 1;
-            if (p.trace && cta == 0 && lane == 0) p.trace[(size_t)2 * p.nphases * kTraceCols + (size_t)pi * 16 + cw] = global_ns();   // per-warp finish time
             TRACE(2);
             phase_fetch_wait();
             if (p.trace && cta == 0 && lane == 0 && (cw == 0 || cw == kCW - 1))
@@ -1940,7 +1949,7 @@ int q4_fused_prepare(q4_model* m) {
     p.part_floats = std::max(max_part, 64);
     // the ring gets whatever shared memory the activation buffers leave (227 KB per CTA, 1 KB kept for static data)
     const size_t other = (size_t)p.xq_bytes + meta_bytes + sizeof(float) * p.part_floats;
-    const size_t budget = 226 * 1024;
+    const size_t budget = 225 * 1024;   // + about 1.3 KB of static shared memory = 227 KB per CTA
     int n_entries = other < budget ? (int)((budget - other) / kEntryBytes) : 0;
     n_entries = std::min(n_entries, kMaxEntries);
     if (n_entries < kMinEntries) { f->unsupported = true; return Q4_ERR_UNSUPPORTED_SIZE; }
@@ -1992,7 +2001,7 @@ extern "C" int q4_model_trace(q4_model* m, unsigned long long* out, int* phase_t
     if (!m) return Q4_ERR_INVALID;
     if (int e = q4_fused_prepare(m)) return e;
     q4_fused* f = m->fused;
-    const size_t n = (size_t)2 * f->nphases * kTraceCols + (size_t)f->nphases * 16;   // + per-warp finish times of CTA 0
+    const size_t n = (size_t)2 * f->nphases * kTraceCols;
     if (!f->trace) {
         if (int e = fused_alloc(f, (void**)&f->trace, n * sizeof(unsigned long long))) return e;
         Q4_CUDA_TRY(cudaMemset(f->trace, 0, n * sizeof(unsigned long long)));
