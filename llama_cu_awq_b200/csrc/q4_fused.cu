@@ -1091,11 +1091,11 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                 if (!(dbg & 1)) gemv_slot(ring + (size_t)e * kEntryBytes + off, ng, kt, xq, xs_scale, xs_sum, part + (size_t)li * 8, lane);
                 __syncwarp();
                 const int ul = fast_div(li, inv_spu);
-                if (lane == 0) {
-                    // an entry is released by its two slots; a phase's odd last slot releases it alone
-                    if (!(dbg & 2)) mbar_arrive(&empty_bar[e], (!(li & 1) && li + 1 == (unsigned)nslots) ? 2 : 1);
-                    mbar_arrive(&unit_bar[ul], 1);   // release: the slot's partials are written
-                }
+                // One arrive instruction, two lanes: lane 0 releases the ring entry (an entry is released by its two slots;
+                // a phase's odd last slot releases it alone), lane 1 counts the slot in for its unit (release: the slot's
+                // partials are written).
+                if (lane < 2 && !(lane == 0 && (dbg & 2)))
+                    mbar_arrive(lane == 0 ? &empty_bar[e] : &unit_bar[ul], (lane == 0 && !(li & 1) && li + 1 == (unsigned)nslots) ? 2 : 1);
                 if ((int)li - ul * spu != spu - 1) continue;
                 // ---- this warp finishes unit ul ----
                 // output index of this lane's column, looked up before the wait (shared-memory reads off the critical path)
