@@ -31,7 +31,7 @@ sys.path.insert(0, ROOT)
 
 N_PROMPT, N_DECODE = 16, 256
 STEPS_PER_GEN = N_PROMPT + N_DECODE  # positions per generation (-n 272)
-FUSED_TRAFFIC_RATIO = 1.024  # dram__bytes_read + dram__bytes_write over algorithmic bytes of a fused_token_kernel launch (ncu)
+FUSED_TRAFFIC_RATIO = 1.023  # dram__bytes_read + dram__bytes_write over algorithmic bytes of a fused_token_kernel launch (ncu)
 
 
 def peaks():
@@ -298,7 +298,7 @@ def main():
         roof = {"bound": "hbm", "kernel": "fused_token_kernel (whole token: W4 GEMVs, attention, classifier)",
                 "achieved": token_gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": token_gbs / pk["hbm_gbs"], "peak_kind": pk_kind,
                 # DRAM bytes per launch from the ncu capture of this kernel on the 4-layer model of the same shapes
-                # (profiles/fused_token_kernel_llama2-7b-4l.md: read + write = 1.024 x algorithmic), scaled by bytes
+                # (profiles/fused_token_kernel_llama2-7b-4l.md: read + write = 1.023 x algorithmic), scaled by bytes
                 "traffic": FUSED_TRAFFIC_RATIO * mean_bytes, "traffic_source": "ncu capture on llama2-7b-4l, scaled by algorithmic bytes",
                 "bytes_per_launch": mean_bytes, "us_per_launch": 1e6 / value,
                 "per_op_gemv_kernel": {"kernel": "q4_gemv_kernel (fused gate/up + SiLU, per-op path)", "achieved": achieved,
