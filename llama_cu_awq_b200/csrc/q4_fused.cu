@@ -515,7 +515,8 @@ __device__ __forceinline__ uint4 attn_word_merge(const AttnWord& w) {
 #pragma unroll
     for (int s = 0; s < kMaxSplit; s++) {
         if (w.ml[s].x != -CUDART_INF_F) {
-            const float e = w.ml[s].y * expf(w.ml[s].x - M);  // weight of the split = its sum, rescaled to the common max
+            const float e = w.ml[s].y * __expf(w.ml[s].x - M);  // weight of the split = its sum, rescaled to the common max
+            // (merge weights: the fast exponential's error is far below the fp16 outputs; the scores themselves use expf)
             L += e;
             const __half2* hh = reinterpret_cast<const __half2*>(&w.a[s]);
 #pragma unroll
@@ -1344,7 +1345,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                 for (int o = 8; o <= 16; o <<= 1) {
                     const float mo = __shfl_xor_sync(0xffffffffu, m, o), lo2 = __shfl_xor_sync(0xffffffffu, l, o);
                     const float mn = fmaxf(m, mo);
-                    const float ca = m == -CUDART_INF_F ? 0.f : expf(m - mn), cb = mo == -CUDART_INF_F ? 0.f : expf(mo - mn);
+                    const float ca = m == -CUDART_INF_F ? 0.f : __expf(m - mn), cb = mo == -CUDART_INF_F ? 0.f : __expf(mo - mn);
                     l = l * ca + lo2 * cb;
 #pragma unroll
                     for (int j = 0; j < 16; j++) acc[j] = acc[j] * ca + __shfl_xor_sync(0xffffffffu, acc[j], o) * cb;
@@ -1365,7 +1366,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
 #pragma unroll
                     for (int g2 = 0; g2 < kCW; g2++) {
                         if (sm_m[g2] != -CUDART_INF_F) {
-                            const float w = expf(sm_m[g2] - M);
+                            const float w = __expf(sm_m[g2] - M);
                             a += sm_acc[g2 * 128 + ctid] * w;
                             L += sm_l[g2] * w;
                         }
