@@ -1378,7 +1378,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                         st_tagged4(outp + 128, make_uint4(out_tag | (mb & 0xFFFFu), out_tag | (mb >> 16), out_tag | (lb & 0xFFFFu), out_tag | (lb >> 16)));
                     }
                 }
-                consumer_sync();
+                if (id + grid < nitems) consumer_sync();   // the merge buffers are reused by this CTA's next item
             }
             TRACE(2);
             phase_fetch_wait();
