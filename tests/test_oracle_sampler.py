@@ -21,6 +21,18 @@ def test_coin_sequence_matches_xorshift_star():
         assert r.f32() == np.float32((u >> 8) / 16777216.0)
 
 
+def test_library_coin_matches_oracle():
+    """q4_random_f32 of the shared library (host code, no GPU needed) draws the reference's sequence."""
+    import ctypes as C
+
+    from llama_cu_awq_b200 import _lib
+    L = _lib.lib()
+    st = C.c_ulonglong(987654321)
+    r = O.Rng(987654321)
+    for _ in range(32):
+        assert float(L.q4_random_f32(C.byref(st))) == r.f32()
+
+
 def select_float64(p16, topp, coin):
     """The selection rule in float64 on the fp16 probabilities (sums of multiples of 2^-24 are exact in float64)."""
     p = p16.astype(np.float64)
