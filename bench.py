@@ -10,10 +10,16 @@ scaling: the job is one sequence). Rank 0 prints one JSON line.
             without host synchronisation, weights resident in HBM), max over ranks
   e2e       tokens/s of the user-facing call q4_generate(): the reference's generation loop and timing window
             (host synchronisation per token, token ids exchanged through the pinned host mailbox)
-  roofline  the dominant kernel (fused gate/up W4 GEMV) timed with CUDA events over all layers' weights
+  roofline  the dominant kernel against the measured HBM bandwidth
+  parity    logits of the first positions of this very model against the CPU oracle, and the token ids of the two
+            timed loops against each other; the run FAILS (exit code 1) when either check does not hold
   cpu_baseline  the CPU oracle (OpenMP port of the reference arithmetic) on a bounded sample, rank 0, N = 1
---impl reference runs the reference's own CUDA program (built from the reference sources into oracle/_ref/)
-on the same file and prompt; without that build it times the CPU port instead.
+  extra     kernels: every W4 projection shape of the model (and the single 4096x4096 layer) per op, rotated over
+            distinct matrices; allreduce (N > 1): peer push vs NCCL per message size; models (N > 1): the larger models
+            the metric names for tensor parallelism (13B at TP N; 70B at TP 4 and 8), generated on the device, with the
+            share of the step that waits for the exchange
+--impl reference runs the reference's own CUDA program (built from the reference sources into oracle/_ref/) on the
+same file and prompt, on N GPUs with its own hybrid tensor parallelism; without that build it times the CPU port.
 """
 import argparse
 import ctypes as C
@@ -31,7 +37,11 @@ sys.path.insert(0, ROOT)
 
 N_PROMPT, N_DECODE = 16, 256
 STEPS_PER_GEN = N_PROMPT + N_DECODE  # positions per generation (-n 272)
-FUSED_TRAFFIC_RATIO = 1.023  # dram__bytes_read + dram__bytes_write over algorithmic bytes of a fused_token_kernel launch (ncu)
+# dram__bytes_read + dram__bytes_write over algorithmic bytes of one fused_token_kernel launch, from the ncu capture
+# of this kernel on the 4-layer model of the same layer shapes (traffic grows with the layer count like the bytes do)
+FUSED_TRAFFIC_RATIO = 1.023
+PARITY_POSITIONS = 4
+MAX_REL, MIN_COS = 1e-2, 0.999   # tolerance of the floating-point parity checks
 
 
 def peaks():
@@ -94,21 +104,62 @@ def model_file(name, rank, dist):
     return path
 
 
-def cpu_port_toks(path, prompt, n_tokens):
-    """Tokens/s of the CPU oracle on the first n_tokens positions of the same workload."""
+def cpu_port(path, prompt, n_tokens):
+    """The CPU oracle on positions 0 .. n_tokens of the same workload (teacher-forced with the prompt): tokens/s over
+    positions 1 .. n_tokens (position 0 pages the file in), the thread count, and the logits of every position."""
     from oracle import q4_oracle as O
     with open(path, "rb") as f:
         m = O.Model(f.read())
-    tok = int(prompt[0])
-    m.forward(tok, 0)  # page the image in
+    logits = []
+    m.forward(int(prompt[0]), 0)
+    logits.append(m.logits().copy())
     t0 = time.perf_counter()
     for pos in range(1, 1 + n_tokens):
-        nxt = m.forward(int(prompt[pos]) if pos < len(prompt) else tok, pos)
-        tok = nxt
+        m.forward(int(prompt[pos]), pos)
+        logits.append(m.logits().copy())
     dt = time.perf_counter() - t0
     cores = O.num_threads()
     m.close()
-    return n_tokens / dt, cores
+    return n_tokens / dt, cores, logits
+
+
+def compare(got, ref):
+    got = np.asarray(got, np.float64)
+    ref = np.asarray(ref, np.float64)
+    rel = float(np.abs(got - ref).max() / max(np.abs(ref).max(), 1e-30))
+    cos = float(got @ ref / max(np.linalg.norm(got) * np.linalg.norm(ref), 1e-30))
+    return rel, cos
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# reference arm
+# ---------------------------------------------------------------------------------------------------------------
+REF_CHILD = r"""
+import json, sys
+sys.path.insert(0, {root!r})
+import numpy as np
+from oracle import ref_gpu as R
+prompt = np.array({prompt!r}, np.int32)
+vals = []
+for i in range({runs}):
+    toks, _, tps, timed, secs = R.generate({path!r}, prompt, {steps}, {vocab}, gpu_count={gpus})
+    vals.append((timed, secs))
+extra = {{}}
+if {kernels}:
+    shapes = {shapes!r}
+    extra["kernels"] = {{name: {{"us": R.time_q4(kind, K, N, nmat=nmat), "K": K, "N": N}} for name, kind, K, N, nmat in shapes}}
+if {gpus} > 1:
+    extra["allreduce"] = {{str(2 * c): R.time_allreduce({gpus}, c) for c in (4096, 5120, 8192)}}
+print("REFRESULT " + json.dumps({{"vals": vals, "extra": extra}}))
+"""
+
+
+def kernel_shapes(cfg):
+    """(name, kind, K, N, distinct matrices) of the W4 ops of one layer, plus the single-layer config of the metric."""
+    dim, hid = cfg[0], cfg[1]
+    hid8 = hid // 8 * 8
+    return [("cfg0_gemv_4096x4096", 0, 4096, 4096, 32), ("o_proj", 0, dim, dim, 32), ("down_proj", 0, hid8, dim, 16),
+            ("qkv_matvec", 1, dim, dim, 33), ("ffn_gate_up_silu", 2, dim, hid8, 16)]
 
 
 def run_reference(args, rank, world):
@@ -121,40 +172,51 @@ def run_reference(args, rank, world):
     base = {"metric": "decode tok/s @bs1", "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16 (int4 weights, fp32 accumulate)",
             "data": "synthetic", "impl": "reference",
-            "config": {"workload": f"{args.model} W4 g128, 16 synthetic prompt ids + 256 greedy tokens, batch 1 (-n 272)", "l2": "weights per token >> L2"}}
+            "config": {"workload": f"{args.model} W4 g128, 16 synthetic prompt ids + 256 greedy tokens, batch 1 (-n 272)",
+                       "parallelism": f"tp{args.gpus}" if args.gpus > 1 else "none", "l2": "weights per token >> L2"}}
     have_gpu = False
     try:
         import torch
         from oracle import ref_gpu as R
-        have_gpu = R.available()
+        have_gpu = R.available() and torch.cuda.device_count() >= args.gpus
     except Exception:
         have_gpu = False
     if have_gpu:
-        # The reference program itself (llama2_q4.cu, -x none) on one GPU: its own loader, kernels and token loop.
-        vals = []
+        # The reference program itself (llama2_q4.cu): its own loader, kernels, collectives and token loop, -x none on one
+        # GPU, -x hybrid with one host thread per GPU on N. It runs in a child process with a time limit: its host-side
+        # rendezvous (std::barrier inside every collective, cuda_comm.h:184,223) has no time-out of its own.
+        code = REF_CHILD.format(root=ROOT, prompt=[int(v) for v in prompt], runs=args.warmup + args.steps, path=path, steps=STEPS_PER_GEN,
+                                vocab=cfg[5], gpus=args.gpus, kernels=args.gpus == 1 and not args.no_extras, shapes=kernel_shapes(cfg))
         sampler = ClockSampler(0)
-        for i in range(args.warmup + args.steps):
-            if i == args.warmup:
-                sampler.start()
-            toks, _, tps, timed, secs = R.generate(path, prompt, STEPS_PER_GEN, cfg[5])
-            if i >= args.warmup:
-                vals.append((timed, secs))
+        sampler.start()
+        try:
+            r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600)
+            line = [l for l in r.stdout.splitlines() if l.startswith("REFRESULT ")]
+            res = json.loads(line[-1][len("REFRESULT "):]) if r.returncode == 0 and line else None
+            why = None if res else f"reference program exited with code {r.returncode}: {(r.stderr or r.stdout)[-300:]}"
+        except subprocess.TimeoutExpired:
+            res, why = None, "reference program did not finish within 600 s on this GPU count (killed)"
         clocks = sampler.stop()
+        if res is None:
+            return {"impl": "reference", "unavailable": why.replace("\n", " ")}
+        vals = res["vals"][args.warmup:]
         tot_t = sum(v[0] for v in vals)
         tot_s = sum(v[1] for v in vals)
         v = tot_t / tot_s
         base.update({"value": v, "ms_per_step": 1e3 * tot_s / len(vals), "clocks": clocks, "gpu_launches": 0,
                      "cpu_baseline": {"value": v, "unit": "tok/s", "cores": 0, "kind": "reference",
-                                      "sample": "the reference's own CUDA program compiled for sm_100a (oracle/_ref), 1 GPU, whole 272-position run; "
-                                                "the reference has no CPU implementation of this path"},
-                     "e2e": {"value": v, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
+                                      "sample": f"the reference's own CUDA program compiled for sm_100a (oracle/_ref), {args.gpus} GPU(s), whole "
+                                                "272-position run; the reference has no CPU implementation of this path"},
+                     "e2e": {"value": v, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                     "extra": res["extra"]})
         if args.gpus > 1:
-            base["config"]["note"] = "reference arm runs on 1 GPU: its row-split loader misplaces zeros/scales at this model's shard sizes"
+            base["config"]["note"] = ("the reference's row-split loader misplaces zero points and scales when groups-per-rank is odd or "
+                                      "fractional (7B down projection at every N > 1): its outputs differ there, its timing is valid")
     else:
         n = 3
         vals = []
         for i in range(min(args.warmup, 1) + args.steps):
-            v, cores = cpu_port_toks(path, prompt, n)
+            v, cores, _ = cpu_port(path, prompt, n)
             vals.append(v)
         vals = vals[-args.steps:]
         v = sum(vals) / len(vals)
@@ -164,15 +226,144 @@ def run_reference(args, rank, world):
     return base
 
 
-def kernel_roofline(t, torch, reps=5):
-    """Times the fused gate/up GEMV on every layer's weights back to back (inputs 1.5 GB >> L2)."""
-    L = t._L
-    n_layers = t.config.n_layers
-    ms = C.c_double()
-    bytes_per_launch = C.c_double()
-    from llama_cu_awq_b200._lib import check
-    check(L.q4_model_time_ffn(t.h, C.c_void_p(t.stream.cuda_stream), reps, C.byref(ms), C.byref(bytes_per_launch)), "time_ffn")
-    return ms.value / (reps * n_layers), bytes_per_launch.value
+# ---------------------------------------------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------------------------------------------
+def time_generations(t, prompt, fwd_path, steps, warmup, barrier, torch, dist, on_timed_start=None):
+    """Device-timed tokens/s over `steps` generations (max over ranks), and the token ids of the last one."""
+    def one():
+        t.reset(prompt, 0)
+        for pos in range(STEPS_PER_GEN - 1):  # the reference counts pos-1 = 271 timed positions per run
+            t.forward(gen_token=pos >= N_PROMPT - 1, path=fwd_path)
+
+    for _ in range(warmup):
+        one()
+    t.synchronize()
+    barrier()
+    if on_timed_start:
+        on_timed_start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    total_ms = 0.0
+    for _ in range(steps):
+        t.reset(prompt, 0)  # synchronous; outside the timed region
+        barrier()
+        with torch.cuda.stream(t.stream):
+            e0.record(t.stream)
+            for pos in range(STEPS_PER_GEN - 1):
+                t.forward(gen_token=pos >= N_PROMPT - 1, path=fwd_path)
+            e1.record(t.stream)
+        t.synchronize()
+        total_ms += e0.elapsed_time(e1)
+    barrier()
+    tokens = np.array(t.shared().tokens[:STEPS_PER_GEN])
+    ms_t = torch.tensor([total_ms], dtype=torch.float64, device="cuda")
+    if dist is not None:
+        dist.all_reduce(ms_t, op=dist.ReduceOp.MAX)
+    total_ms = float(ms_t.item())
+    return (STEPS_PER_GEN - 1) * steps / (total_ms / 1e3), total_ms, tokens
+
+
+def op_kernels(cfg, torch):
+    """Every W4 op of one layer (and the single 4096 x 4096 layer) timed alone over distinct matrices."""
+    from llama_cu_awq_b200 import _lib
+    L = _lib.lib()
+    out = {}
+    pk, _ = peaks()
+    g = torch.Generator(device="cuda").manual_seed(0)
+    s = torch.cuda.current_stream()
+    for name, kind, K, N, nmat in kernel_shapes(cfg):
+        pw, pz, gg = ((K + 31) // 32) * 4, ((K + 127) // 128 + 7) // 8, (K + 127) // 128
+        keep, mats = [], (_lib.q4_qweight * nmat)()
+        for i in range(nmat):
+            w = torch.randint(-2**31, 2**31 - 1, (N, pw), dtype=torch.int32, device="cuda", generator=g)
+            z = torch.randint(-2**31, 2**31 - 1, (N, pz), dtype=torch.int32, device="cuda", generator=g)
+            sc = (torch.rand((N, gg), device="cuda", generator=g) * 0.018 + 0.002).half()
+            keep += [w, z, sc]
+            mats[i] = _lib.q4_qweight(w.data_ptr(), z.data_ptr(), sc.data_ptr())
+        x = torch.randn(K, device="cuda", generator=g).half()
+        ys = [torch.zeros(4 * N, dtype=torch.float16, device="cuda") for _ in range(3)]
+        pos = torch.zeros(1, dtype=torch.int32, device="cuda")
+        us, nbytes = C.c_double(), C.c_double()
+        torch.cuda.synchronize()
+        st = L.q4_time_q4_op(C.c_void_p(s.cuda_stream), kind, C.c_void_p(ys[0].data_ptr()), C.c_void_p(ys[1].data_ptr()), C.c_void_p(ys[2].data_ptr()),
+                             C.c_void_p(x.data_ptr()), mats, nmat, K, N, 20, C.c_void_p(pos.data_ptr()), C.byref(us), C.byref(nbytes))
+        if st != 0:
+            out[name] = {"error": st}
+            continue
+        gbs = nbytes.value / (us.value * 1e-6) / 1e9
+        out[name] = {"K": K, "N": N, "us": us.value, "bytes": nbytes.value, "gbs": gbs, "frac_of_hbm_peak": gbs / pk["hbm_gbs"], "distinct_matrices": nmat}
+        del keep
+    return out
+
+
+def allreduce_table(comm, dist, torch):
+    """Microseconds per in-place fp16 all-reduce of one model vector (8, 10, 16 KB) and of 64 KB: peer push vs NCCL."""
+    from llama_cu_awq_b200 import _lib
+    L = _lib.lib()
+    out = {}
+    have_nccl = False
+    try:
+        comm.attach_nccl(dist)
+        have_nccl = True
+    except Exception as e:  # NCCL cannot be opened: the table then has the peer push only
+        out["nccl_error"] = str(e)[:120]
+    s = torch.cuda.current_stream()
+    for count in (4096, 5120, 8192, 32768):
+        buf = torch.zeros(count, dtype=torch.float16, device="cuda")
+        row = {}
+        for name, backend in (("p2p_push", _lib.Q4_COMM_BACKEND_P2P), ("nccl", _lib.Q4_COMM_BACKEND_NCCL)):
+            if backend == _lib.Q4_COMM_BACKEND_NCCL and not have_nccl:
+                continue
+            comm.set_backend(backend)
+            torch.cuda.synchronize()
+            dist.barrier()
+            us = C.c_double()
+            st = L.q4_time_all_reduce(comm.handle, C.c_void_p(s.cuda_stream), C.c_void_p(buf.data_ptr()), count, 200, C.byref(us))
+            v = torch.tensor([us.value if st == 0 else -1.0], dtype=torch.float64, device="cuda")
+            dist.all_reduce(v, op=dist.ReduceOp.MAX)
+            row[name] = float(v.item())
+        out[str(2 * count)] = row
+    comm.set_backend(_lib.Q4_COMM_BACKEND_P2P)
+    out["unit"] = "us per call, max over ranks, 200 calls back to back"
+    return out
+
+
+def extra_model(name, rank, world, dist, torch, barrier, pk):
+    """A larger model of the metric at this tensor-parallel degree, generated on the device: tok/s, fraction of the
+    weight-streaming roofline, and the share of the step that waits for the exchange between the ranks (step time minus
+    the same step with every rank's exchange kept inside its own memory, measured with the test build of the library)."""
+    from llama_cu_awq_b200 import _lib, synth
+    from llama_cu_awq_b200.comm import ProcessComm
+    from llama_cu_awq_b200.model import Transformer
+    cfg = synth.CONFIGS[name]
+    prompt = synth.synth_prompt(N_PROMPT, cfg[5], seed=0)
+    res = {}
+    for which in ("product", "exchange_local"):
+        lib = _lib.lib() if which == "product" else _lib.test_lib()
+        if which == "exchange_local":
+            lib.q4_test_set_fused_debug(16)
+        comm = ProcessComm(rank, world, dist, lib=lib)
+        t = Transformer(None, rank=rank, gpu_count=world, tp_mode=_lib.Q4_TP_HYBRID, comm=comm.handle, lib=lib, synthetic=(cfg, 0))
+        ok = torch.tensor([1 if t.best_path() == 2 else 0], device="cuda")
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if int(ok.item()) != 1:
+            t.close(); comm.close()
+            return {"error": "the fused path does not serve this model at this degree"}
+        barrier()
+        toks, total_ms, tokens = time_generations(t, prompt, 2, 2, 1, barrier, torch, dist)
+        st = t.status()
+        if which == "product":
+            mean_bytes = sum(t.token_bytes(p) for p in range(STEPS_PER_GEN - 1)) / (STEPS_PER_GEN - 1)
+            res.update({"tok_s": toks, "us_per_token": 1e6 / toks, "bytes_per_token_per_gpu": mean_bytes,
+                        "token_roofline_frac": mean_bytes * toks / 1e9 / pk["hbm_gbs"], "status": st})
+        else:
+            lib.q4_test_set_fused_debug(0)
+            res["us_per_token_exchange_local"] = 1e6 / toks
+            res["exposed_exchange_pct"] = 100.0 * (res["us_per_token"] - 1e6 / toks) / res["us_per_token"]
+        t.close()
+        comm.close()
+        barrier()
+    return res
 
 
 def main():
@@ -184,6 +375,7 @@ def main():
     ap.add_argument("--model", default="llama2-7b")
     ap.add_argument("--path", type=int, default=-1, help="forward path: 1 = CUDA-graph replay of per-op kernels (default: best available)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the per-op kernel table, the all-reduce table and the larger models")
     ap.add_argument("--positions", type=int, default=0, help="positions per generation (default 272 = 16 prompt + 256 decode); smaller for profiling runs")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
@@ -237,39 +429,11 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    def one_generation_device():
-        t.reset(prompt, 0)
-        for pos in range(STEPS_PER_GEN - 1):  # the reference counts pos-1 = 271 timed positions per run
-            t.forward(gen_token=pos >= N_PROMPT - 1, path=fwd_path)
-
     # ---- device-timed value ----
-    for _ in range(args.warmup):
-        one_generation_device()
-    t.synchronize()
-    barrier()
     sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    total_ms = 0.0
-    for _ in range(args.steps):
-        t.reset(prompt, 0)  # synchronous; outside the timed region
-        barrier()
-        with torch.cuda.stream(t.stream):
-            e0.record(t.stream)
-            for pos in range(STEPS_PER_GEN - 1):
-                t.forward(gen_token=pos >= N_PROMPT - 1, path=fwd_path)
-            e1.record(t.stream)
-        t.synchronize()
-        total_ms += e0.elapsed_time(e1)
-    barrier()
-    tokens_dev = np.array(t.shared().tokens[:STEPS_PER_GEN])
-    ms_t = torch.tensor([total_ms], dtype=torch.float64, device="cuda")
-    if dist is not None:
-        dist.all_reduce(ms_t, op=dist.ReduceOp.MAX)
-    total_ms = float(ms_t.item())
+    value, total_ms, tokens_dev = time_generations(t, prompt, fwd_path, args.steps, args.warmup, barrier, torch, dist,
+                                                   on_timed_start=sampler.start if rank == 0 else None)
     timed_tokens = (STEPS_PER_GEN - 1) * args.steps
-    value = timed_tokens / (total_ms / 1e3)
 
     # ---- end to end through the public generation call ----
     t.generate(prompt, STEPS_PER_GEN, path=fwd_path)
@@ -285,28 +449,70 @@ def main():
         e2e_sec += float(st.item())
     e2e = e2e_tok / e2e_sec
     clocks = sampler.stop() if rank == 0 else None
+    tokens_match = bool((tokens_dev == toks[:STEPS_PER_GEN]).all())
+    if dist is not None:   # and every rank holds the same ids
+        mine = torch.from_numpy(np.concatenate([tokens_dev, toks[:STEPS_PER_GEN]]).astype(np.int64)).cuda()
+        lo, hi = mine.clone(), mine.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        tokens_match = tokens_match and bool(torch.equal(lo, hi))
+
+    # ---- parity of this very model: first positions against the CPU oracle (which is also the timed CPU baseline) ----
+    parity = {"tokens_match_e2e": tokens_match, "limits": {"max_rel": MAX_REL, "cosine": MIN_COS}}
+    cpu = None
+    if rank == 0 and not args.no_cpu_baseline:
+        cpu = cpu_port(path, prompt, PARITY_POSITIONS)
+    t.reset(prompt, 0)
+    barrier()
+    got = []
+    for pos in range(PARITY_POSITIONS + 1):
+        t.forward(gen_token=False, path=fwd_path)
+        t.synchronize()
+        got.append(t.logits())
+    if cpu is not None:
+        rels, coss = zip(*[compare(a, b) for a, b in zip(got, cpu[2])])
+        parity.update({"positions": len(rels), "max_rel": max(rels), "cosine": min(coss), "against": "CPU oracle, same file, teacher-forced prompt"})
+    parity["device_status"] = t.status()
+    parity["ok"] = bool(tokens_match and parity["device_status"] == 0 and (cpu is None or (parity["max_rel"] <= MAX_REL and parity["cosine"] >= MIN_COS)))
 
     # ---- dominant kernel against the HBM roofline ----
     pk, pk_kind = peaks()
-    k_ms, k_bytes = kernel_roofline(t, torch)
-    achieved = k_bytes / (k_ms * 1e-3) / 1e9
     mean_bytes = sum(t.token_bytes(p) for p in range(STEPS_PER_GEN - 1)) / (STEPS_PER_GEN - 1)
     token_gbs = mean_bytes * value / 1e9
-
+    extra = {}
+    if world == 1 and not args.no_extras:
+        extra["kernels"] = op_kernels(cfg, torch)
     if fwd_path == 2:
         launches_per_token = 1  # one persistent cooperative kernel per token
         roof = {"bound": "hbm", "kernel": "fused_token_kernel (whole token: W4 GEMVs, attention, classifier)",
                 "achieved": token_gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": token_gbs / pk["hbm_gbs"], "peak_kind": pk_kind,
-                # DRAM bytes per launch from the ncu capture of this kernel on the 4-layer model of the same shapes
-                # (profiles/fused_token_kernel_llama2-7b-4l.md: read + write = 1.023 x algorithmic), scaled by bytes
-                "traffic": FUSED_TRAFFIC_RATIO * mean_bytes, "traffic_source": "ncu capture on llama2-7b-4l, scaled by algorithmic bytes",
-                "bytes_per_launch": mean_bytes, "us_per_launch": 1e6 / value,
-                "per_op_gemv_kernel": {"kernel": "q4_gemv_kernel (fused gate/up + SiLU, per-op path)", "achieved": achieved,
-                                       "frac": achieved / pk["hbm_gbs"], "bytes_per_launch": k_bytes, "us_per_launch": k_ms * 1e3}}
+                "traffic": FUSED_TRAFFIC_RATIO * mean_bytes, "traffic_source": "ncu capture of this kernel on the 4-layer model of the same layer shapes, scaled by algorithmic bytes",
+                "bytes_per_launch": mean_bytes, "us_per_launch": 1e6 / value}
     else:
         launches_per_token = 4 + 9 * cfg[2] + (2 * cfg[2] + 1 if world > 1 else 0)
-        roof = {"bound": "hbm", "kernel": "q4_gemv_kernel (fused gate/up + SiLU)", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                "frac": achieved / pk["hbm_gbs"], "peak_kind": pk_kind, "traffic": None, "bytes_per_launch": k_bytes, "us_per_launch": k_ms * 1e3}
+        k = (extra.get("kernels") or {}).get("ffn_gate_up_silu") or {}
+        roof = {"bound": "hbm", "kernel": "q4_gemv_kernel (fused gate/up + SiLU)", "achieved": k.get("gbs"), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                "frac": k.get("frac_of_hbm_peak"), "peak_kind": pk_kind, "traffic": None, "bytes_per_launch": k.get("bytes"), "us_per_launch": k.get("us")}
+    t.close()
+    if comm:
+        comm.close()
+
+    # ---- N > 1: the collectives alone, and the models the metric names for tensor parallelism ----
+    if world > 1 and not args.no_extras:
+        c2 = ProcessComm(rank, world, dist)
+        extra["allreduce"] = allreduce_table(c2, dist, torch)
+        c2.close()
+        barrier()
+        models = {}
+        names = ["llama2-13b"] + (["llama2-70b"] if world >= 4 else [])
+        for name in names:
+            try:
+                models[f"{name}_tp{world}"] = extra_model(name, rank, world, dist, torch, barrier, pk)
+            except Exception as e:  # reported, not fatal: the headline line stays valid
+                models[f"{name}_tp{world}"] = {"error": str(e)[:200]}
+                break
+        extra["models"] = models
+
     line = {
         "metric": "decode tok/s @bs1", "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
@@ -314,27 +520,28 @@ def main():
         "config": {"workload": f"{args.model} W4 g128, 16 synthetic prompt ids + {STEPS_PER_GEN - N_PROMPT} greedy tokens, batch 1 (-n {STEPS_PER_GEN})",
                    "parallelism": f"tp{world}" if world > 1 else "none", "forward_path": fwd_path,
                    "l2": "inputs larger than L2 (weights per token >> 126 MB); no flush needed",
-                   "tokens_match_e2e": bool((tokens_dev == toks[:STEPS_PER_GEN]).all())},
+                   "tokens_match_e2e": tokens_match},
         "clocks": clocks,
         "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": 4 * N_PROMPT + 4 * STEPS_PER_GEN, "d2h_bytes_per_step": 8 * STEPS_PER_GEN},
         "gpu_launches": launches_per_token * timed_tokens,
         "roofline": roof,
         "token_roofline": {"bytes_per_token_per_gpu": mean_bytes, "achieved_gbs_per_gpu": token_gbs, "frac": token_gbs / pk["hbm_gbs"],
                            "frac_of_nominal_8tbs": token_gbs / 8000.0},
+        "parity": parity,
+        "extra": extra,
     }
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        n = 4
-        v, cores = cpu_port_toks(path, prompt, n)
-        line["cpu_baseline"] = {"value": v, "unit": "tok/s", "cores": cores, "kind": "port",
-                                "sample": f"first {n} positions of the same model and prompt, CPU oracle (OpenMP over output columns)"}
-    t.close()
-    if comm:
-        comm.close()
+    if cpu is not None and world == 1:
+        line["cpu_baseline"] = {"value": cpu[0], "unit": "tok/s", "cores": cpu[1], "kind": "port",
+                                "sample": f"positions 1-{PARITY_POSITIONS} of the same model and prompt, CPU oracle (OpenMP over output columns)"}
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
     if rank == 0:
         print(json.dumps(line))
+    if not parity["ok"]:
+        if rank == 0:
+            print("bench.py: parity check failed (see the `parity` block): the numbers above are not valid", file=sys.stderr)
+        sys.exit(1)
 
 
 if __name__ == "__main__":

@@ -114,7 +114,9 @@ int q4_attention(void* stream, uint16_t* output, const uint16_t* q, const uint16
  * The first call on each device looks the array's device address up (cudaGetSymbolAddress); make that first call
  * outside of any stream capture. All calls share the one array: two calls that overlap on the GPU (different
  * streams) race; calls on one stream are safe. Nothing has to be cleared between calls: each call overwrites
- * every word it later reads. */
+ * every word it later reads. The array's address is remembered per CUDA device ordinal of the calling thread's
+ * current device, which must be the device `stream` belongs to; the remembered address does not survive
+ * cudaDeviceReset() (do not call this entry point again in a process that has reset the device). */
 #define Q4_ATTENTION_STATIC_MAX_BYTES (256 * 1024)
 int q4_attention_static(void* stream, uint16_t* output, const uint16_t* q, const uint16_t* key_cache,
                         const uint16_t* value_cache, int num_heads, int head_size, int kv_mul, int max_seq_len,
@@ -179,6 +181,26 @@ int q4_all_reduce(q4_comm* comm, void* stream, uint16_t* buf, int count);
 int q4_all_gather(q4_comm* comm, void* stream, const uint16_t* send, uint16_t* recv, int sendcount);
 /* Device-side wait status: 0, or Q4_ERR_TIMEOUT after a peer flag did not arrive within the bound. */
 int q4_comm_status(q4_comm* comm);
+/* Bound of the collectives' wait for the peers' flags, in nanoseconds of the device's global timer (default two
+ * seconds; 0 restores it), and re-arming after a recorded timeout (every rank of the group must call it before
+ * the next collective). */
+int q4_comm_set_wait_limit_ns(q4_comm* comm, unsigned long long ns);
+int q4_comm_reset(q4_comm* comm);
+/* NCCL as the alternative transport of q4_all_reduce / q4_all_gather: the reference's -DENABLE_NCCL build
+ * (CMakeLists.txt:14-43; ncclGetUniqueId / ncclCommInitRank at llama2_q4.cu:638-640,688-689, ncclAllReduce /
+ * ncclAllGather at :474,505,534). libnccl.so.2 is opened at run time; without it q4_comm_nccl_available() is 0 and
+ * the other calls return Q4_ERR_UNSUPPORTED_SIZE. One rank creates the id, the caller distributes its 128 bytes,
+ * then every rank calls q4_comm_nccl_init (collective) on its communicator. The backend chooses the transport per
+ * call: P2P (default) = one-shot peer push; NCCL; AUTO = by message size from the measured latency table (peer push
+ * up to Q4_COMM_MAX_HALFS, NCCL above). */
+typedef struct { char internal[128]; } q4_nccl_id; /* same size and meaning as ncclUniqueId */
+#define Q4_COMM_BACKEND_P2P 0
+#define Q4_COMM_BACKEND_NCCL 1
+#define Q4_COMM_BACKEND_AUTO 2
+int q4_comm_nccl_available(void);
+int q4_comm_nccl_unique_id(q4_nccl_id* id);
+int q4_comm_nccl_init(q4_comm* comm, const q4_nccl_id* id);
+int q4_comm_set_backend(q4_comm* comm, int backend);
 /* cudaCommDestroy: cuda_comm.h:278-286. */
 int q4_comm_destroy(q4_comm* comm);
 
@@ -197,6 +219,13 @@ typedef struct q4_model q4_model;
  * on the current device (Megatron split of llama2_q4.cu:299-332, with row splits moved to 128-input group
  * boundaries) and allocates the run state (llama2_q4.cu:62-91). comm may be NULL when gpu_count == 1. */
 int q4_model_load(q4_model** model, const char* path, int rank, int gpu_count, int tp_mode, q4_comm* comm);
+/* The same model object without a file: a synthetic model of the given configuration, generated on the device
+ * shard by shard from (seed, tensor, element index) - what stands in for real checkpoints in benchmarks of models
+ * whose file would be tens of gigabytes (the reference reads the whole file through host memory,
+ * llama2_q4.cu:645-646; it has no counterpart of this call). All ranks and all tensor-parallel degrees obtain shards
+ * of one and the same logical model; llama_cu_awq_b200/synth.py writes the identical model as a packed file. */
+int q4_model_create_synthetic(q4_model** model, const q4_config* cfg, unsigned long long seed, int rank, int gpu_count,
+                              int tp_mode, q4_comm* comm);
 int q4_model_free(q4_model* model);
 int q4_model_config(const q4_model* model, q4_config* out);
 /* Pinned mailbox of this rank (tokens[], pos) and device buffers, for tests and for the host loop. */
@@ -205,13 +234,17 @@ const uint16_t* q4_model_logits(const q4_model* model); /* device, vocab_size ha
 const uint16_t* q4_model_x(const q4_model* model);      /* device, dim halfs */
 /* Synchronous device-to-host copy of a run-state vector: what = 0 logits (vocab_size halfs), 1 x (dim halfs). */
 int q4_model_read(const q4_model* model, int what, uint16_t* host_out);
-/* Resets position counters (device and pinned) to `pos` and copies `n` prompt ids into the mailbox. */
+/* Resets position counters (device and pinned) to `pos` and copies `n` prompt ids into the mailbox.
+ * Q4_ERR_INVALID when an id lies outside [0, vocab_size): the embedding gather would read outside the table. */
 int q4_model_reset(q4_model* model, const int* prompt_tokens, int n, int pos);
 /* run_transformer(): one token at the current position on `stream`: embedding .. logits, then the greedy
  * hand-off (gen_token != 0 writes the sampled id to tokens[pos+1]); asynchronous. `path`: 0 = per-op kernels
  * launched one by one, 1 = the same launches replayed from a captured CUDA graph, 2 = one persistent
- * cooperative kernel per token that streams re-tiled weights through a shared-memory ring (head size 128,
- * one GPU; returns Q4_ERR_UNSUPPORTED_SIZE otherwise). */
+ * cooperative kernel per token that streams re-tiled weights through a shared-memory ring and exchanges the
+ * residual stream between the ranks inside the kernel (head size 128, dim a multiple of 128, Q4_TP_NONE or
+ * Q4_TP_HYBRID on 1 to 8 GPUs; returns Q4_ERR_UNSUPPORTED_SIZE otherwise).
+ * Q4_ERR_LIMIT when the model's sequence length has been reached since the last q4_model_reset: the call would
+ * write a K/V row outside the cache. */
 int q4_model_forward(q4_model* model, void* stream, int gen_token, int path);
 /* Builds whatever `path` needs ahead of the first token (path 2: re-tiled weight copy and phase table; needs
  * as much extra device memory as the quantized weights). Q4_ERR_UNSUPPORTED_SIZE when the path cannot serve
@@ -223,6 +256,12 @@ int q4_model_prepare(q4_model* model, int path);
  * state per forward call, greedy or not, as sample() does (sampler.h:79). All ranks of a tensor-parallel group set
  * the same values. */
 int q4_model_set_sampler(q4_model* model, float temperature, float topp, unsigned long long seed);
+/* Limit, in nanoseconds of the device's global timer, of every wait inside the fused kernel (path 2) for data of
+ * another CTA or rank; 0 restores the default of two seconds. When a wait runs out the kernel records
+ * Q4_ERR_TIMEOUT, lets all later waits fall through and returns; q4_model_status reports it and q4_model_reset
+ * re-arms the path. The reference has no counterpart: a missing peer blocks its host barrier for ever
+ * (cuda_comm.h:184,223). */
+int q4_model_set_wait_limit_ns(q4_model* model, unsigned long long ns);
 /* Synchronises the device and returns Q4_OK, or the error a bounded device-side wait recorded
  * (Q4_ERR_TIMEOUT) in the fused path or the communicator. */
 int q4_model_status(q4_model* model);
@@ -240,12 +279,38 @@ double q4_model_token_bytes(const q4_model* model, int pos);
  * Returns the total milliseconds and the algorithmic bytes one launch moves. */
 int q4_model_time_ffn(q4_model* model, void* stream, int reps, double* total_ms, double* bytes_per_launch);
 
+/* Measurement hook: one W4 op wrapper (kind 0 q4_matmul_q4, 1 q4_qkv_matvec with kvSize = opSize, 2 q4_ffn_matvec_silu)
+ * over `nmat` distinct matrices of one shape, captured as one CUDA graph (kinds 1 / 2 take three / two matrices per
+ * launch) and replayed `reps` times between two events on `stream`: weights come from HBM, not from L2, and no
+ * launch gap is timed. Returns microseconds and algorithmic bytes per launch. */
+int q4_time_q4_op(void* stream, int kind, uint16_t* y, uint16_t* y2, uint16_t* y3, const uint16_t* x, const q4_qweight* mats,
+                  int nmat, int K, int N, int reps, const int* pPos, double* us_per_launch, double* bytes_per_launch);
+/* Measurement hook: `reps` in-place q4_all_reduce calls of `count` halfs back to back between two events on `stream`. */
+int q4_time_all_reduce(q4_comm* comm, void* stream, uint16_t* buf, int count, int reps, double* us_per_call);
+
 /* Profiling hook of the fused path: the first call arms per-phase device timestamps (globaltimer, ns) for the
  * following launches; later calls copy the last launch's stamps to `out` ([2 CTAs][nphases][8]: phase start,
  * inputs staged, weights consumed, phase closed, then staging detail: loads back, norm reduced, quantised)
  * and a type code per phase. The stamps are global stores and perturb what they measure by a few tenths of a
  * microsecond. Returns the phase count (always larger than any status code) or a status code. */
 int q4_model_trace(q4_model* model, unsigned long long* out, int* phase_types, int max_phases);
+
+/* ---------------------------------------------------------------------------------------------
+ * Tokenizer of the command line (host code, no GPU): tokenizer.h:36-223. The vocabulary file is the reference's
+ * tokenizer.bin format (uint32 max_token_length, then per token float32 score, int32 length, bytes).
+ * ------------------------------------------------------------------------------------------- */
+typedef struct q4_tokenizer q4_tokenizer;
+/* build_tokenizer: tokenizer.h:36-61. Q4_ERR_IO when the file is missing or short (the reference exits). */
+int q4_tokenizer_load(q4_tokenizer** tokenizer, const char* path, int vocab_size);
+void q4_tokenizer_free(q4_tokenizer* tokenizer);
+/* encode: tokenizer.h:108-223. bos/eos != 0 add ids 1 / 2. *n_tokens receives the count; Q4_ERR_LIMIT when it
+ * exceeds max_tokens (strlen(text) + 3 always suffices), Q4_ERR_BAD_MODEL when the vocabulary has no " " piece or
+ * no byte pieces where the text needs them. */
+int q4_tokenizer_encode(const q4_tokenizer* tokenizer, const char* text, int bos, int eos, int* tokens, int max_tokens,
+                        int* n_tokens);
+/* decode + safe_printf: tokenizer.h:72-100. The text to print for `token` following `prev_token` ("" for an
+ * unprintable single byte). The pointer stays valid until the next call on the same tokenizer. */
+const char* q4_tokenizer_decode(q4_tokenizer* tokenizer, int prev_token, int token);
 
 /* Host-side shard helpers (no GPU needed): copy rank `rank`'s shard of a quantized matrix held in host
  * memory. Column split = contiguous slice of outputs (llama2_q4.cu:254-263). Row split = slice of inputs on

@@ -7,8 +7,9 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-# Q4B200_LIB selects another build of the same library (A/B timing of two builds in one session).
-LIB_PATH = os.environ.get("Q4B200_LIB") or os.path.join(HERE, "libq4b200.so")
+LIB_PATH = os.path.join(HERE, "libq4b200.so")
+# The same sources built with -DQ4_TEST_BUILD: adds measurement switches and host-side fault injectors (tests only).
+TEST_LIB_PATH = os.path.join(HERE, "libq4b200_test.so")
 
 Q4_OK = 0
 Q4_ERR_UNSUPPORTED_SIZE = 1
@@ -20,6 +21,7 @@ Q4_ERR_TIMEOUT = 6
 Q4_ERR_LIMIT = 7
 Q4_MAX_SEQ_LEN = 128 * 1024
 Q4_TP_NONE, Q4_TP_COLUMN, Q4_TP_HYBRID = 0, 1, 2
+Q4_COMM_BACKEND_P2P, Q4_COMM_BACKEND_NCCL, Q4_COMM_BACKEND_AUTO = 0, 1, 2
 
 
 class Q4Error(RuntimeError):
@@ -76,8 +78,15 @@ SIGNATURES = {
     "q4_all_reduce": (_I, [_P, _P, _P, _I]),
     "q4_all_gather": (_I, [_P, _P, _P, _P, _I]),
     "q4_comm_status": (_I, [_P]),
+    "q4_comm_set_wait_limit_ns": (_I, [_P, C.c_ulonglong]),
+    "q4_comm_reset": (_I, [_P]),
+    "q4_comm_nccl_available": (_I, []),
+    "q4_comm_nccl_unique_id": (_I, [_P]),
+    "q4_comm_nccl_init": (_I, [_P, _P]),
+    "q4_comm_set_backend": (_I, [_P, _I]),
     "q4_comm_destroy": (_I, [_P]),
     "q4_model_load": (_I, [C.POINTER(_P), C.c_char_p, _I, _I, _I, _P]),
+    "q4_model_create_synthetic": (_I, [C.POINTER(_P), C.POINTER(q4_config), C.c_ulonglong, _I, _I, _I, _P]),
     "q4_model_free": (_I, [_P]),
     "q4_model_config": (_I, [_P, C.POINTER(q4_config)]),
     "q4_model_shared": (C.POINTER(q4_shared_data), [_P]),
@@ -89,31 +98,61 @@ SIGNATURES = {
     "q4_model_prepare": (_I, [_P, _I]),
     "q4_model_set_sampler": (_I, [_P, C.c_float, C.c_float, C.c_ulonglong]),
     "q4_model_status": (_I, [_P]),
+    "q4_model_set_wait_limit_ns": (_I, [_P, C.c_ulonglong]),
     "q4_generate": (_I, [_P, C.POINTER(C.c_int), _I, _I, _I, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_double)]),
     "q4_model_token_bytes": (C.c_double, [_P, _I]),
     "q4_model_time_ffn": (_I, [_P, _P, _I, C.POINTER(C.c_double), C.POINTER(C.c_double)]),
+    "q4_time_q4_op": (_I, [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, C.POINTER(C.c_double), C.POINTER(C.c_double)]),
+    "q4_time_all_reduce": (_I, [_P, _P, _P, _I, _I, C.POINTER(C.c_double)]),
     "q4_model_trace": (_I, [_P, _P, _P, _I]),
+    "q4_tokenizer_load": (_I, [C.POINTER(_P), C.c_char_p, _I]),
+    "q4_tokenizer_free": (None, [_P]),
+    "q4_tokenizer_encode": (_I, [_P, C.c_char_p, _I, _I, C.POINTER(_I), _I, C.POINTER(_I)]),
+    "q4_tokenizer_decode": (C.c_char_p, [_P, _I, _I]),
     "q4_row_split_range": (None, [_I, _I, _I, C.POINTER(_I), C.POINTER(_I)]),
     "q4_shard_columns_host": (_I, [_QW, _I, _I, _I, _I, _P, _P, _P]),
     "q4_shard_rows_host": (_I, [_QW, _I, _I, _I, _I, _P, _P, _P]),
 }
 
+# exported by the test build only
+TEST_SIGNATURES = {
+    "q4_test_set_fused_debug": (None, [_I]),
+    "q4_test_set_split_len": (None, [_I]),
+    "q4_test_set_ring_entries": (None, [_I]),
+    "q4_test_fail_fused_alloc": (None, [_I]),
+    "q4_test_comm_set_peer": (_I, [_P, _I, _P]),
+    "q4_test_fused_gemv": (_I, [_P, _P, _P, _QW, _I, _I]),
+}
+
 _lib = None
+_test_lib = None
+
+
+def _load(path, signatures):
+    if not os.path.exists(path):
+        raise RuntimeError(f"{path} is missing: build it with `python -m llama_cu_awq_b200.build`; there is no fallback path")
+    L = C.CDLL(path)
+    for name, (res, args) in signatures.items():
+        fn = getattr(L, name)
+        fn.restype = res
+        fn.argtypes = args
+    return L
 
 
 def lib():
     """The loaded shared library; raises if it is missing (no fallback of any kind)."""
     global _lib
     if _lib is None:
-        if not os.path.exists(LIB_PATH):
-            raise RuntimeError(f"{LIB_PATH} is missing: build it with `python -m llama_cu_awq_b200.build`; there is no fallback path")
-        L = C.CDLL(LIB_PATH)
-        for name, (res, args) in SIGNATURES.items():
-            fn = getattr(L, name)
-            fn.restype = res
-            fn.argtypes = args
-        _lib = L
+        _lib = _load(LIB_PATH, SIGNATURES)
     return _lib
+
+
+def test_lib():
+    """The test build of the library (its own copy of all state; objects of one build must not be passed to the other)."""
+    global _test_lib
+    if _test_lib is None:
+        _test_lib = _load(TEST_LIB_PATH, {**SIGNATURES, **TEST_SIGNATURES})
+    return _test_lib
 
 
 def status_string(status):

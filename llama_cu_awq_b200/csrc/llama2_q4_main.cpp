@@ -15,88 +15,32 @@
 #include <ctime>
 #include <string>
 #include <thread>
-#include <unordered_map>
 #include <vector>
 
 #include "../../include/q4b200.h"
 
 namespace {
 
-constexpr int kBos = 1, kEos = 2;  // tokenizer.h:8-9
+constexpr int kEos = 2;  // tokenizer.h:9
 
-// llama2.c-format vocabulary file (tokenizer.bin): uint32 max_token_length, then per token
-// float32 score, int32 length, bytes. Encoding is greedy best-score pair merging over UTF-8 pieces with byte
-// fallback (+3 offset), decoding strips the leading space after BOS and maps <0xXX> pieces to raw bytes
-// (behaviour of tokenizer.h:36-223).
+// The vocabulary (tokenizer.bin) through the library's tokenizer entry points (q4_tokenizer_*).
 class Vocab {
 public:
-    bool load(const char* path, int vocab_size) {
-        FILE* f = fopen(path, "rb");
-        if (!f) return false;
-        uint32_t max_len = 0;
-        if (fread(&max_len, 4, 1, f) != 1) { fclose(f); return false; }
-        pieces_.resize(vocab_size);
-        scores_.resize(vocab_size);
-        for (int i = 0; i < vocab_size; i++) {
-            int len = 0;
-            if (fread(&scores_[i], 4, 1, f) != 1 || fread(&len, 4, 1, f) != 1 || len < 0) { fclose(f); return false; }
-            pieces_[i].resize(len);
-            if (len && fread(&pieces_[i][0], len, 1, f) != 1) { fclose(f); return false; }
-            index_.emplace(pieces_[i], i);
-        }
-        fclose(f);
-        return true;
-    }
-    bool loaded() const { return !pieces_.empty(); }
-
+    ~Vocab() { q4_tokenizer_free(t_); }
+    bool load(const char* path, int vocab_size) { return q4_tokenizer_load(&t_, path, vocab_size) == Q4_OK; }
+    bool loaded() const { return t_ != nullptr; }
     std::vector<int> encode(const std::string& text, bool bos) const {
-        std::vector<int> out;
-        if (bos) out.push_back(kBos);
-        if (text.empty()) return out;
-        auto sp = index_.find(" ");
-        if (sp != index_.end()) out.push_back(sp->second);  // dummy prefix
-        for (size_t i = 0; i < text.size();) {
-            size_t n = 1;
-            while (i + n < text.size() && (static_cast<unsigned char>(text[i + n]) & 0xC0) == 0x80 && n < 4) n++;
-            auto it = index_.find(text.substr(i, n));
-            if (it != index_.end()) out.push_back(it->second);
-            else
-                for (size_t b = 0; b < n; b++) out.push_back(static_cast<unsigned char>(text[i + b]) + 3);
-            i += n;
-        }
-        for (;;) {
-            float best = -1e10f;
-            int best_id = -1;
-            size_t best_at = 0;
-            for (size_t i = 0; i + 1 < out.size(); i++) {
-                auto it = index_.find(pieces_[out[i]] + pieces_[out[i + 1]]);
-                if (it != index_.end() && scores_[it->second] > best) { best = scores_[it->second]; best_id = it->second; best_at = i; }
-            }
-            if (best_id < 0) break;
-            out[best_at] = best_id;
-            out.erase(out.begin() + best_at + 1);
-        }
+        std::vector<int> out(text.size() + 3);
+        int n = 0;
+        if (q4_tokenizer_encode(t_, text.c_str(), bos ? 1 : 0, 0, out.data(), (int)out.size(), &n) != Q4_OK) n = 0;
+        out.resize(n);
         return out;
     }
-
     // Printable text of `token` following `prev`; empty for unprintable single bytes.
-    std::string decode(int prev, int token) const {
-        if (token < 0 || token >= (int)pieces_.size()) return "";
-        std::string p = pieces_[token];
-        if (prev == kBos && !p.empty() && p[0] == ' ') p.erase(0, 1);
-        unsigned byte = 0;
-        if (p.size() == 6 && sscanf(p.c_str(), "<0x%02X>", &byte) == 1) p = std::string(1, (char)byte);
-        if (p.size() == 1) {
-            unsigned char c = (unsigned char)p[0];
-            if (!(isprint(c) || isspace(c))) return "";
-        }
-        return p;
-    }
+    std::string decode(int prev, int token) const { return t_ ? q4_tokenizer_decode(t_, prev, token) : ""; }
 
 private:
-    std::vector<std::string> pieces_;
-    std::vector<float> scores_;
-    std::unordered_map<std::string, int> index_;
+    q4_tokenizer* t_ = nullptr;
 };
 
 [[noreturn]] void error_usage(const char* argv0) {

@@ -13,13 +13,16 @@
 // only after it finished reading its epoch-e slots, so no slot is overwritten while it is still being read.
 // No host synchronisation is involved, so the call can be captured in a CUDA graph.
 // Waits are bounded: after kWaitLimitNs the kernel records Q4_ERR_TIMEOUT in the status word and returns.
+#include <chrono>
+#include <dlfcn.h>
 #include <mutex>
 #include <string.h>
+#include <thread>
 
 #include "q4_comm_internal.h"
 
 namespace {
-constexpr unsigned long long kWaitLimitNs = 2000ULL * 1000 * 1000;  // 2 s on the device's global timer
+constexpr unsigned long long kDefaultWaitNs = 2000ULL * 1000 * 1000;  // default bound of the flag wait: 2 s on the device's global timer
 constexpr int kCommThreads = 1024;
 
 struct Inbox {
@@ -47,6 +50,9 @@ struct q4_comm {
     PeerPtrs peers;
     bool imported[Q4_MAX_GPUS];  // opened through IPC (must be closed)
     q4_comm_id* id;
+    unsigned long long wait_ns = kDefaultWaitNs;
+    int backend = Q4_COMM_BACKEND_P2P;
+    void* nccl = nullptr;        // ncclComm_t once q4_comm_nccl_init has run
 };
 
 namespace {
@@ -66,7 +72,7 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
 
 // mode 0: all-reduce (sum) of buf[count] in place. mode 1: all-gather, send[count] -> recv[g*count].
 __global__ void __launch_bounds__(kCommThreads) comm_kernel(PeerPtrs peers, Inbox* local, int rank, int g, __half* buf, const __half* send,
-                                                            int count, int mode) {
+                                                            int count, int mode, unsigned long long wait_ns) {
     __shared__ uint32_t s_epoch;
     griddep_wait();
     griddep_launch_dependents();
@@ -90,7 +96,7 @@ __global__ void __launch_bounds__(kCommThreads) comm_kernel(PeerPtrs peers, Inbo
             if ((++spins & 255u) == 0) {
                 const unsigned long long now = global_timer_ns();
                 if (t_start == 0) t_start = now;
-                else if (now - t_start > kWaitLimitNs) { local->status = Q4_ERR_TIMEOUT; break; }
+                else if (now - t_start > wait_ns) { local->status = Q4_ERR_TIMEOUT; break; }
             }
         }
     }
@@ -176,13 +182,21 @@ extern "C" int q4_comm_init_rank(q4_comm** comm, int gpu_count, q4_comm_id* id, 
         id->inbox[rank] = c->local;
         id->registered++;
     }
-    // bounded rendezvous: wait until every rank has published its inbox
-    for (long long spins = 0;; spins++) {
+    // bounded rendezvous: wait (at most 60 s of wall time) until every rank has published its inbox
+    const auto t0 = std::chrono::steady_clock::now();
+    for (;;) {
         {
             std::lock_guard<std::mutex> lk(id->mu);
             if (id->registered >= gpu_count) break;
+            if (std::chrono::steady_clock::now() - t0 > std::chrono::seconds(60)) {
+                id->inbox[rank] = nullptr;   // withdraw: nobody has read the table yet (readers wait for the full count)
+                id->registered--;
+                cudaFree(c->local);
+                delete c;
+                return Q4_ERR_TIMEOUT;
+            }
         }
-        if (spins > 2000000000LL) { return Q4_ERR_TIMEOUT; }
+        std::this_thread::sleep_for(std::chrono::microseconds(50));
     }
     for (int i = 0; i < gpu_count; i++) c->peers.p[i] = id->inbox[i];
     *comm = c;
@@ -229,12 +243,103 @@ static int comm_launch(q4_comm* c, cudaStream_t s, __half* buf, const __half* se
     for (int i = 0; i < c->gpu_count; i++)
         if (!c->peers.p[i]) return Q4_ERR_INVALID;
     Q4Launch L(dim3(1), dim3(kCommThreads), 0, s);
-    Q4_CUDA_TRY(cudaLaunchKernelEx(&L.cfg, comm_kernel, c->peers, c->local, c->rank, c->gpu_count, buf, send, count, mode));
+    Q4_CUDA_TRY(cudaLaunchKernelEx(&L.cfg, comm_kernel, c->peers, c->local, c->rank, c->gpu_count, buf, send, count, mode, c->wait_ns));
+    return Q4_OK;
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// NCCL backend (the reference's -DENABLE_NCCL build: ncclAllReduce / ncclAllGather at the same call sites,
+// llama2_q4.cu:474,505,534). The library is opened at run time, so that nothing here depends on it being installed;
+// whichever libnccl.so.2 the process already holds (e.g. the one an ML framework loaded) is the one that is used.
+// ------------------------------------------------------------------------------------------------------------
+namespace {
+struct NcclApi {
+    void* lib = nullptr;
+    int (*GetUniqueId)(void*) = nullptr;
+    int (*CommInitRank)(void**, int, q4_nccl_id, int) = nullptr;
+    int (*AllReduce)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+    int (*AllGather)(const void*, void*, size_t, int, void*, cudaStream_t) = nullptr;
+    int (*CommDestroy)(void*) = nullptr;
+    bool ok = false;
+};
+constexpr int kNcclHalf = 6, kNcclSum = 0;   // ncclFloat16, ncclSum (nccl.h)
+std::mutex g_nccl_mu;
+NcclApi g_nccl;
+
+const NcclApi* nccl_api() {
+    std::lock_guard<std::mutex> lk(g_nccl_mu);
+    if (!g_nccl.lib) {
+        g_nccl.lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+        if (!g_nccl.lib) g_nccl.lib = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+        if (g_nccl.lib) {
+            g_nccl.GetUniqueId = (int (*)(void*))dlsym(g_nccl.lib, "ncclGetUniqueId");
+            g_nccl.CommInitRank = (int (*)(void**, int, q4_nccl_id, int))dlsym(g_nccl.lib, "ncclCommInitRank");
+            g_nccl.AllReduce = (int (*)(const void*, void*, size_t, int, int, void*, cudaStream_t))dlsym(g_nccl.lib, "ncclAllReduce");
+            g_nccl.AllGather = (int (*)(const void*, void*, size_t, int, void*, cudaStream_t))dlsym(g_nccl.lib, "ncclAllGather");
+            g_nccl.CommDestroy = (int (*)(void*))dlsym(g_nccl.lib, "ncclCommDestroy");
+            g_nccl.ok = g_nccl.GetUniqueId && g_nccl.CommInitRank && g_nccl.AllReduce && g_nccl.AllGather && g_nccl.CommDestroy;
+        }
+    }
+    return g_nccl.ok ? &g_nccl : nullptr;
+}
+}  // namespace
+
+extern "C" int q4_comm_nccl_available(void) { return nccl_api() ? 1 : 0; }
+
+extern "C" int q4_comm_nccl_unique_id(q4_nccl_id* id) {
+    if (!id) return Q4_ERR_INVALID;
+    const NcclApi* a = nccl_api();
+    if (!a) return Q4_ERR_UNSUPPORTED_SIZE;
+    return a->GetUniqueId(id) == 0 ? Q4_OK : Q4_ERR_CUDA;
+}
+
+extern "C" int q4_comm_nccl_init(q4_comm* comm, const q4_nccl_id* id) {
+    if (!comm || !id) return Q4_ERR_INVALID;
+    const NcclApi* a = nccl_api();
+    if (!a) return Q4_ERR_UNSUPPORTED_SIZE;
+    if (comm->nccl) return Q4_OK;
+    void* nc = nullptr;
+    if (a->CommInitRank(&nc, comm->gpu_count, *id, comm->rank) != 0) return Q4_ERR_CUDA;
+    comm->nccl = nc;
+    return Q4_OK;
+}
+
+extern "C" int q4_comm_set_backend(q4_comm* comm, int backend) {
+    if (!comm || backend < Q4_COMM_BACKEND_P2P || backend > Q4_COMM_BACKEND_AUTO) return Q4_ERR_INVALID;
+    if (backend == Q4_COMM_BACKEND_NCCL && !comm->nccl) return Q4_ERR_INVALID;
+    comm->backend = backend;
+    return Q4_OK;
+}
+
+// Which implementation serves a message of `count` halfs. AUTO follows the measured latency table (one 8-16 KB
+// vector: the one-shot push is several times faster than an NCCL call at every group size): peer push for
+// everything its inbox holds, NCCL beyond that when it is attached.
+static bool use_nccl(const q4_comm* c, int count) {
+    if (!c->nccl) return false;
+    if (c->backend == Q4_COMM_BACKEND_NCCL) return true;
+    return c->backend == Q4_COMM_BACKEND_AUTO && count > Q4_COMM_MAX_HALFS;
+}
+
+extern "C" int q4_comm_set_wait_limit_ns(q4_comm* comm, unsigned long long ns) {
+    if (!comm) return Q4_ERR_INVALID;
+    comm->wait_ns = ns ? ns : kDefaultWaitNs;
+    return Q4_OK;
+}
+
+// After a recorded timeout the flags and the call counter of this rank are out of step with its peers': clear them.
+// Every rank of the group calls this (with a host-side barrier around the calls) before the next collective.
+extern "C" int q4_comm_reset(q4_comm* comm) {
+    if (!comm) return Q4_ERR_INVALID;
+    Q4_CUDA_TRY(cudaDeviceSynchronize());
+    Q4_CUDA_TRY(cudaMemset(comm->local, 0, offsetof(Inbox, slots)));
+    Q4_CUDA_TRY(cudaDeviceSynchronize());
     return Q4_OK;
 }
 
 extern "C" int q4_all_reduce(q4_comm* comm, void* stream, uint16_t* buf, int count) {
     if (comm && comm->gpu_count == 1) return Q4_OK;  // cuda_comm.h:163-171: in place, nothing to do
+    if (comm && buf && count > 0 && use_nccl(comm, count))
+        return nccl_api()->AllReduce(buf, buf, (size_t)count, kNcclHalf, kNcclSum, comm->nccl, (cudaStream_t)stream) == 0 ? Q4_OK : Q4_ERR_CUDA;
     return comm_launch(comm, (cudaStream_t)stream, (__half*)buf, nullptr, count, 0);
 }
 
@@ -244,6 +349,8 @@ extern "C" int q4_all_gather(q4_comm* comm, void* stream, const uint16_t* send, 
         if (send != recv) Q4_CUDA_TRY(cudaMemcpyAsync(recv, send, (size_t)sendcount * 2, cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
         return Q4_OK;
     }
+    if (comm && recv && sendcount > 0 && use_nccl(comm, sendcount))
+        return nccl_api()->AllGather(send, recv, (size_t)sendcount, kNcclHalf, comm->nccl, (cudaStream_t)stream) == 0 ? Q4_OK : Q4_ERR_CUDA;
     return comm_launch(comm, (cudaStream_t)stream, (__half*)recv, (const __half*)send, sendcount, 1);
 }
 
@@ -256,9 +363,21 @@ extern "C" int q4_comm_status(q4_comm* comm) {
 
 extern "C" int q4_comm_destroy(q4_comm* comm) {
     if (!comm) return Q4_OK;
+    if (comm->nccl && nccl_api()) nccl_api()->CommDestroy(comm->nccl);
     for (int i = 0; i < comm->gpu_count; i++)
         if (comm->imported[i]) cudaIpcCloseMemHandle(comm->peers.p[i]);
     cudaFree(comm->local);
     delete comm;
     return Q4_OK;
 }
+
+#ifdef Q4_TEST_BUILD
+// Test build only: makes `other`'s inbox (a second communicator of the same process and device) stand in for rank
+// `peer` of `comm`. Nobody ever writes that rank's flags, so a collective on `comm` stores into valid memory, waits
+// for the missing rank until the wait limit and records Q4_ERR_TIMEOUT: the time-out path exercised on one GPU.
+extern "C" int q4_test_comm_set_peer(q4_comm* comm, int peer, q4_comm* other) {
+    if (!comm || !other || peer < 0 || peer >= comm->gpu_count || peer == comm->rank) return Q4_ERR_INVALID;
+    comm->peers.p[peer] = other->local;
+    return Q4_OK;
+}
+#endif

@@ -55,7 +55,15 @@ constexpr int kTraceCols = 8;           // timestamps per phase: 0 start, 1 inpu
 constexpr int kMaxUnitsPerCta = 64;    // units of one phase per CTA (host-checked)
 constexpr int kClsChunk = 4096;        // halfs of one classifier row per slot (8192 B)
 constexpr unsigned kPollLimit = 1u << 26;                        // polls, and
-constexpr unsigned long long kWaitLimitNs = 2000ULL * 1000 * 1000;  // two seconds on the global timer, whichever comes first
+constexpr unsigned long long kDefaultWaitNs = 2000ULL * 1000 * 1000;  // default limit of a device-side wait: two seconds on the global timer (FParams::wait_ns)
+
+// Measurement and test switches of the kernel (skip the math, skip the streaming, keep the exchange local) exist only in the
+// test build of the library; in the product build the expression is the constant 0 and the branches are compiled out.
+#ifdef Q4_TEST_BUILD
+#define Q4_DBG(p) ((p).debug)
+#else
+#define Q4_DBG(p) 0
+#endif
 
 enum PhaseType { PH_EMBED = 0, PH_GEMV = 1, PH_ATTN = 2, PH_CLS = 3, PH_ARGMAX = 4 };
 enum EpiKind { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SILU = 2 };
@@ -113,7 +121,8 @@ struct FParams {
     // (tag_base + producing phase + 1) in the high half. A reader that needs the whole vector polls the words
     // themselves until all carry the expected tag, so most op boundaries need no grid barrier: one L2 round trip
     // instead of fence + arrive + poll. A buffer is rewritten only after every CTA has provably read it (the next
-    // writer's own input wait, or the barrier kept after attention, implies it).
+    // writer's own input wait implies it; phases with fewer units than CTAs end with a grid barrier, because a CTA
+    // without units writes nothing that anyone waits for and could otherwise fall behind unnoticed).
     //
     // The residual stream is the one vector that all ranks of a tensor-parallel group share. It lives in the exchange
     // area of the communicator as g partial vectors ("slots", one per source rank) in two alternating buffers:
@@ -144,8 +153,10 @@ struct FParams {
     int* status;
     int write_token;
     int no_handoff;              // 1: leave the token mailbox and the position alone (a sampling kernel follows on the stream)
-    int debug;                   // measurement only: 1 = consumers skip the GEMV math (pure streaming), 2 = no streaming (pure math),
+    int debug;                   // test build only (Q4_TEST_BUILD; always 0 and compiled out of the product library):
+                                 // 1 = consumers skip the GEMV math (pure streaming), 2 = no streaming (pure math),
                                  // 8 = raw ring throughput, 16 = tensor-parallel exchange kept local (no NVLink dependency)
+    unsigned long long wait_ns;  // limit of every device-side wait on the global timer; on expiry the kernel records Q4_ERR_TIMEOUT
     int n_entries;               // ring entries of kEntryBytes each
     int split_len;               // positions per attention split (a head is split in ceil(T / split_len) parts, at most nsplit)
     unsigned long long* trace;   // optional: [2 CTAs][nphases][4] device timestamps (ns), or null
@@ -184,7 +195,7 @@ __device__ __forceinline__ unsigned long long global_ns() {
 // launch): the test would pass on round r - 2's completion. Consumers therefore first wait until the producer has
 // ISSUED round r at that position (`seq`, written before the copy is issued); from then on the barrier's current phase
 // is r or r + 1 and the parity test is unambiguous. seq == nullptr: the caller is the producer.
-__device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, int* status, const unsigned* seq = nullptr, unsigned want = 0) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, int* status, unsigned long long limit_ns, const unsigned* seq = nullptr, unsigned want = 0) {
     unsigned long long t0 = 0;
     for (unsigned i = 0; i < kPollLimit; i++) {
         if ((!seq || *(const volatile unsigned*)seq == want) && mbar_try(b, parity)) return true;
@@ -192,7 +203,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* b, uint32_t parity, int* sta
             if (*(volatile int*)status != 0) return false;
             const unsigned long long now = global_ns();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > kWaitLimitNs) break;
+            else if (now - t0 > limit_ns) break;
         }
     }
     if (atomicCAS(status, 0, Q4_ERR_TIMEOUT) == 0) status[1] = 0x40000 + (int)(smem_u32(b) & 0xFFFF);
@@ -238,7 +249,7 @@ __device__ __forceinline__ void grid_barrier(const FParams& p, unsigned& nbar, i
                 if (*(volatile int*)p.status != 0) { *s_abort = 1; break; }
                 const unsigned long long now = global_ns();
                 if (t0 == 0) t0 = now;
-                else if (now - t0 > 2 * kWaitLimitNs) {   // longer than any single data wait, so that the root cause is what gets recorded
+                else if (now - t0 > 2 * p.wait_ns) {   // longer than any single data wait, so that the root cause is what gets recorded
                     if (atomicCAS(p.status, 0, Q4_ERR_TIMEOUT) == 0) { p.status[1] = 0x50000 + (int)nbar; p.status[2] = (int)v; p.status[3] = (int)target; }
                     *s_abort = 1;
                     break;
@@ -344,12 +355,12 @@ __device__ __forceinline__ uint4 load_tagged8(const uint32_t* src, uint32_t tag_
     return make_uint4(prmt(a.x, a.y, 0x5410), prmt(a.z, a.w, 0x5410), prmt(b.x, b.y, 0x5410), prmt(b.z, b.w, 0x5410));
 }
 // Bounded retry bookkeeping for the tag polls: returns false when the wait must be given up.
-__device__ __forceinline__ bool keep_polling(unsigned& polls, unsigned long long& t0, int* status, int where = 0) {
+__device__ __forceinline__ bool keep_polling(unsigned& polls, unsigned long long& t0, int* status, unsigned long long limit_ns, int where = 0) {
     if ((++polls & 15u) == 0) {
         if (*(volatile int*)status != 0) return false;
         const unsigned long long now = global_ns();
         if (t0 == 0) t0 = now;
-        else if (now - t0 > kWaitLimitNs) {
+        else if (now - t0 > limit_ns) {
             if (atomicCAS(status, 0, Q4_ERR_TIMEOUT) == 0) status[1] = where;  // where the first wait ran out (diagnostics)
             return false;
         }
@@ -362,7 +373,7 @@ __device__ __forceinline__ bool keep_polling(unsigned& polls, unsigned long long
 // words are in flight per round trip (64 registers), so an 8-rank group costs two round trips per pair of words.
 template <int NB>
 __device__ __forceinline__ void load_x_batch(uint4 (&xv)[NB], const bool (&valid)[NB], const int (&wd)[NB], const uint32_t* base, int g,
-                                             uint32_t want, int* status, int where) {
+                                             uint32_t want, int* status, unsigned long long limit_ns, int where) {
     unsigned polls = 0;
     unsigned long long t0 = 0;
     if (g == 1) {
@@ -373,7 +384,7 @@ __device__ __forceinline__ void load_x_batch(uint4 (&xv)[NB], const bool (&valid
                 xv[b] = make_uint4(0, 0, 0, 0);
                 if (valid[b]) xv[b] = load_tagged8(base + wd[b] * 8, want, bad);
             }
-            if (bad == 0 || !keep_polling(polls, t0, status, where)) break;
+            if (bad == 0 || !keep_polling(polls, t0, status, limit_ns, where)) break;
         }
         return;
     }
@@ -399,7 +410,7 @@ __device__ __forceinline__ void load_x_batch(uint4 (&xv)[NB], const bool (&valid
                         a[b][c] = make_uint4(0, 0, 0, 0);
                         if (valid[b0 + b] && r0 + c < g) a[b][c] = load_tagged8(base + (size_t)(r0 + c) * kLLMaxDim + wd[b0 + b] * 8, want, bad);
                     }
-                if (bad == 0 || !keep_polling(polls, t0, status, where)) break;
+                if (bad == 0 || !keep_polling(polls, t0, status, limit_ns, where)) break;
             }
 #pragma unroll
             for (int b = 0; b < SB; b++)
@@ -497,7 +508,7 @@ __device__ __forceinline__ void attn_word_load(AttnWord& w, const FParams& p, in
         w.ml[s] = make_float2(-CUDART_INF_F, 0.f);
         w.a[s] = make_uint4(0, 0, 0, 0);
         if (valid && s < ns) {
-            const uint32_t* base = p.attn_part + ((size_t)h * ns + s) * kAttnPartStride;
+            const uint32_t* base = p.attn_part + ((size_t)h * p.nsplit + s) * kAttnPartStride;
             w.a[s] = load_tagged8(base + d, want, bad);
             const uint4 t = ld_poll(reinterpret_cast<const uint4*>(base + 128));
             bad |= ((t.x ^ want) | (t.y ^ want) | (t.z ^ want) | (t.w ^ want)) >> 16;
@@ -610,8 +621,10 @@ __device__ __forceinline__ int attn_splits_for(const FParams& p, int T) { return
 // Words b0.. of one batch: SB words per thread in flight, CH rank slots per round trip. A word is processed as soon as
 // the whole warp has it (the 16 threads of a group share a scale), so the words that are there early are done while the
 // late ones - the outputs of the slowest CTA or rank - are still being polled. Plain inputs are quantised at once.
-// RMSNorm inputs (DEFER) need the whole vector first: their words are summed over the ranks, squared into ss and
-// handed back in xout (the reference rounds x * (w / rms) to fp16, gpu_kernels.h:100-102, and so does the caller).
+// RMSNorm inputs (DEFER) need the whole vector first: their words are summed over the ranks and handed back in xout
+// (the reference rounds x * (w / rms) to fp16, gpu_kernels.h:100-102, and so does the caller). The sum of squares is
+// NOT accumulated here: words complete in whatever order their tags arrive, and a float sum taken in arrival order
+// would differ in the last bit from run to run, from CTA to CTA and from rank to rank.
 template <int SB, int CH, bool MULTI, bool DEFER>
 __device__ __forceinline__ void stage_words(const FPhase& ph, const FParams& p, const uint32_t* base, int g, uint32_t want, int it0, int iters,
                                             int nwords, uint4* xq, float* xs_scale, int* xs_sum, int ctid, float& ss, bool& gave_up,
@@ -674,20 +687,13 @@ __device__ __forceinline__ void stage_words(const FPhase& ph, const FParams& p, 
                     for (int j = 0; j < 4; j++) oh[j] = __floats2half2_rn(acc[b * bb][2 * j], acc[b * bb][2 * j + 1]);
                 }
                 if (DEFER) {
-                    const __half2* oh = reinterpret_cast<const __half2*>(&hv);
-#pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        const float2 xf2 = __half22float2(oh[j]);
-                        ss = fmaf(xf2.x, xf2.x, ss);
-                        ss = fmaf(xf2.y, xf2.y, ss);
-                    }
-                    xout[b] = hv;
+                    xout[b] = hv;   // the caller squares and sums the words in index order once all have arrived
                 } else {
                     quant_word(hv, wds[b], nwords, xq, xs_scale, xs_sum);
                 }
             }
             if (pend) {
-                int go = keep_polling(polls, t0, p.status, 0x100 + ph.in_phase) ? 1 : 0;
+                int go = keep_polling(polls, t0, p.status, p.wait_ns, 0x100 + ph.in_phase) ? 1 : 0;
                 go = __all_sync(0xffffffffu, go);
                 if (!go) { gave_up = true; break; }
             }
@@ -712,7 +718,7 @@ __device__ void stage_x_quant(const FPhase& ph, const FParams& p, int pos, uint4
                 uint32_t bad = 0;
                 attn_word_load(w0, p, ns, wd0, wd0 < nwords && wd0 * 8 < K, want, bad);
                 attn_word_load(w1, p, ns, wd1, it0 + 1 < iters && wd1 < nwords && wd1 * 8 < K, want, bad);
-                if (bad == 0 || !keep_polling(polls, t0, p.status, 0x80000 + ph.in_phase)) break;
+                if (bad == 0 || !keep_polling(polls, t0, p.status, p.wait_ns, 0x80000 + ph.in_phase)) break;
             }
             if (tr && it0 == 0) tr[4] = global_ns();
             // (a word index past the vector quantises zeros and stores nothing)
@@ -753,6 +759,17 @@ __device__ void stage_x_quant(const FPhase& ph, const FParams& p, int pos, uint4
         if (iters > 2) stage_words<2, 4, true, true>(ph, p, base, g, want, 2, iters, nwords, xq, xs_scale, xs_sum, ctid, ss, gave_up, xv + 2);
     }
     if (tr) tr[4] = global_ns();
+    // sum of squares in a fixed order: word index inside the thread, shuffle tree inside the warp, warp index last
+#pragma unroll
+    for (int b = 0; b < 4; b++) {
+        const __half2* xh = reinterpret_cast<const __half2*>(&xv[b]);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float2 xf2 = __half22float2(xh[j]);
+            ss = fmaf(xf2.x, xf2.x, ss);
+            ss = fmaf(xf2.y, xf2.y, ss);
+        }
+    }
     ss = consumer_sum<false>(ss, red, ctid);   // the staging's closing barrier comes before any other use of `red`
     ss /= K;
     ss += 1e-5f;
@@ -794,7 +811,7 @@ __device__ void stage_x_f16(const FPhase& ph, const FParams& p, __half* xf, floa
         uint4 xv1[1];
         const bool valid1[1] = {true};
         const int wd1[1] = {wd};
-        load_x_batch<1>(xv1, valid1, wd1, p.xb[ph.xbuf_in][p.rank], p.g, want, p.status, 0x60000 + ph.in_phase);
+        load_x_batch<1>(xv1, valid1, wd1, p.xb[ph.xbuf_in][p.rank], p.g, want, p.status, p.wait_ns, 0x60000 + ph.in_phase);
         const uint4 v = xv1[0];
         reinterpret_cast<uint4*>(xf)[wd] = v;
         const __half2* h = reinterpret_cast<const __half2*>(&v);
@@ -918,7 +935,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
     if (warp == 0) {
         // ================= producer: stream every phase's weights of this CTA into the ring =================
         // (Requesting weights into L2 ahead of the ring was measured and dropped: it slows the stream down.)
-        if (p.debug & 2) return;
+        if (Q4_DBG(p) & 2) return;
         // The whole warp walks this CTA's precomputed copy list: 32 descriptors are fetched at a time (one per lane),
         // then lane 0 issues them one by one as ring entries free up. One entry = two consecutive slots of a phase,
         // one bulk copy when they are adjacent in memory.
@@ -942,7 +959,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                 int good = 1;
                 if (lane == 0) {
                     const int e = pe;
-                    if (!mbar_wait(&empty_bar[e], pround ^ 1u, p.status)) {
+                    if (!mbar_wait(&empty_bar[e], pround ^ 1u, p.status, p.wait_ns)) {
                         good = 0;
                     } else {
                         uint8_t* dst = ring + (size_t)e * kEntryBytes;
@@ -1009,7 +1026,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
         if (ph.next_norm_w && cta == pi % grid && ctid * 64 < ph.next_norm_n)
             asm volatile("prefetch.global.L2 [%0];" ::"l"(ph.next_norm_w + ctid * 64));
 
-        if (p.debug & 8) {
+        if (Q4_DBG(p) & 8) {
             // measurement only: raw ring throughput over the real weight layout (no staging, no math, no barriers)
             if (ph.type == PH_GEMV || ph.type == PH_CLS) {
                 const int tpu = ph.type == PH_GEMV ? ph.tpu : 2;
@@ -1018,7 +1035,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                 for (unsigned li = first; li < (unsigned)nslots; li += kCW) {
                     const unsigned en = ent0 + (li >> 1);
                     const int e = en % kEntries;
-                    if (failed || !mbar_wait(&full_bar[e], (en / kEntries) & 1, p.status, &s_round[e], en / kEntries)) { failed = true; continue; }
+                    if (failed || !mbar_wait(&full_bar[e], (en / kEntries) & 1, p.status, p.wait_ns, &s_round[e], en / kEntries)) { failed = true; continue; }
                     if (lane == 0) mbar_arrive(&empty_bar[e], (!(li & 1) && li + 1 == (unsigned)nslots) ? 2 : 1);
                 }
                 sbase += nslots;
@@ -1062,7 +1079,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
             // been counted in (they were started earlier by other warps), sums the per-slot partials in slot order and
             // writes the outputs at once - no CTA-wide step between the math and the stores.
             // Phase constants live in registers: the descriptor is not re-read inside the loops.
-            const int nunits = ph.nunits, tpu = ph.tpu, nkt = ph.nkt, G = ph.G, dbg = p.debug, epi = ph.epi;
+            const int nunits = ph.nunits, tpu = ph.tpu, nkt = ph.nkt, G = ph.G, dbg = Q4_DBG(p), epi = ph.epi;
             const int my_units = unit_count(nunits, cta, grid);
             const int spu = tpu * nkt, nslots = my_units * spu;
             const unsigned first = (cw + kCW - (sbase % kCW)) % kCW;  // first slot of this warp in the phase
@@ -1088,7 +1105,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                 const int eq = fast_div(en, inv_entries), e = (int)en - eq * kEntries;
                 int off = 0;
                 if (li & 1) { const int ktp = kt > 0 ? kt - 1 : nkt - 1; off = min(kSlotGroups, G - ktp * kSlotGroups) * kUnitBytes; }
-                if (!(dbg & 2) && (failed || !mbar_wait(&full_bar[e], eq & 1, p.status, &s_round[e], (unsigned)eq))) { failed = true; continue; }
+                if (!(dbg & 2) && (failed || !mbar_wait(&full_bar[e], eq & 1, p.status, p.wait_ns, &s_round[e], (unsigned)eq))) { failed = true; continue; }
                 if (!(dbg & 1)) gemv_slot(ring + (size_t)e * kEntryBytes + off, ng, kt, xq, xs_scale, xs_sum, part + (size_t)li * 8, lane);
                 __syncwarp();
                 const int ul = fast_div(li, inv_spu);
@@ -1110,7 +1127,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                             if (*(volatile int*)p.status != 0) break;
                             const unsigned long long now = global_ns();
                             if (t0 == 0) t0 = now;
-                            else if (now - t0 > 2 * kWaitLimitNs) {   // longer than any data wait: the root cause gets recorded first
+                            else if (now - t0 > 2 * p.wait_ns) {   // longer than any data wait: the root cause gets recorded first
                                 if (atomicCAS(p.status, 0, Q4_ERR_TIMEOUT) == 0) p.status[1] = 0x90000 + pi;
                                 break;
                             }
@@ -1169,7 +1186,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                         sum += oldf / p.gpu_count;   // each rank adds x / g (gpu_kernels.h:237-238)
                         const uint32_t word = tagged(__float2half(sum), out_tag);
                         const size_t off2 = (size_t)p.rank * kLLMaxDim + n;
-                        if (p.debug & 16) {
+                        if (Q4_DBG(p) & 16) {
                             // measurement only: the same stores, but all into this rank's own area (zeros as the peers'
                             // partials), so that no step waits on NVLink: step time minus this = exposed exchange time
                             for (int r2 = 0; r2 < p.g; r2++)
@@ -1255,7 +1272,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                         uint32_t bad = 0;
                         lo4[0] = load_tagged8(qp, want, bad); lo4[1] = load_tagged8(qp + 8, want, bad);
                         hi4[0] = load_tagged8(qp + 64, want, bad); hi4[1] = load_tagged8(qp + 72, want, bad);
-                        if (bad == 0 || !keep_polling(polls, tw, p.status)) break;
+                        if (bad == 0 || !keep_polling(polls, tw, p.status, p.wait_ns, 0x20000 + pi)) break;
                     }
                     const __half* lo = reinterpret_cast<const __half*>(lo4);
                     const __half* hi = reinterpret_cast<const __half*>(hi4);
@@ -1288,7 +1305,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                             lo4[0] = load_tagged8(kp, want, bad); lo4[1] = load_tagged8(kp + 8, want, bad);
                             hi4[0] = load_tagged8(kp + 64, want, bad); hi4[1] = load_tagged8(kp + 72, want, bad);
                             vnew4[0] = load_tagged8(vp, want, bad); vnew4[1] = load_tagged8(vp + 8, want, bad);
-                            if (bad == 0 || !keep_polling(polls, tw, p.status, 0x30000 + pi)) break;
+                            if (bad == 0 || !keep_polling(polls, tw, p.status, p.wait_ns, 0x30000 + pi)) break;
                         }
                         {
                             const __half2* hh = reinterpret_cast<const __half2*>(vnew4);
@@ -1357,7 +1374,13 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                     for (int j = 0; j < 16; j++) sm_acc[cw * 128 + d0 + j] = acc[j];
                 }
                 consumer_sync();
-                uint32_t* outp = p.attn_part + (size_t)id * kAttnPartStride;
+                // Slot (h, split) of a fixed [heads][nsplit] layout. The CTA that writes a head's last split in use also stamps
+                // the head's unused slots with this launch's tag: every slot is rewritten by every launch, so a slot that
+                // comes into use when the context grows never holds a tag from thousands of launches ago that could equal
+                // (modulo 2^16) the tag its first reader waits for.
+                uint32_t* outp = p.attn_part + ((size_t)h * p.nsplit + split) * kAttnPartStride;
+                if (split == ns - 1 && ctid < kAttnPartStride)
+                    for (int s2 = ns; s2 < p.nsplit; s2++) st_tagged(p.attn_part + ((size_t)h * p.nsplit + s2) * kAttnPartStride + ctid, out_tag);
                 if (ctid < HS) {
                     float M = -CUDART_INF_F;
 #pragma unroll
@@ -1403,7 +1426,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                     const int eq = fast_div(en, inv_entries), e = (int)en - eq * kEntries;
                     int off = 0;
                     if (li & 1) { const int kcp = kc > 0 ? kc - 1 : nkt - 1; off = min(kClsChunk, K - kcp * kClsChunk) * 2; }
-                    if (!(p.debug & 2) && (failed || !mbar_wait(&full_bar[e], eq & 1, p.status, &s_round[e], (unsigned)eq))) { failed = true; continue; }
+                    if (!(Q4_DBG(p) & 2) && (failed || !mbar_wait(&full_bar[e], eq & 1, p.status, p.wait_ns, &s_round[e], (unsigned)eq))) { failed = true; continue; }
                     const uint4* wv = reinterpret_cast<const uint4*>(ring + (size_t)e * kEntryBytes + off);
                     const uint4* xv = reinterpret_cast<const uint4*>(xf + kc * kClsChunk);
                     float a4[8];
@@ -1430,7 +1453,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                     a = warp_sum(a);
                     if (lane == 0) part[li] = a;
                     __syncwarp();
-                    if (lane == 0 && !(p.debug & 2)) mbar_arrive(&empty_bar[e], (!(li & 1) && li + 1 == (unsigned)nslots) ? 2 : 1);
+                    if (lane == 0 && !(Q4_DBG(p) & 2)) mbar_arrive(&empty_bar[e], (!(li & 1) && li + 1 == (unsigned)nslots) ? 2 : 1);
                 }
             }
             sbase += nslots;
@@ -1445,7 +1468,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                 const __half hv = __float2half(sum);
                 if (p.g == 1) p.logits[n] = hv;
                 else   // the all-gather of the logits: this rank's slice goes to every rank (plain peer stores)
-                    for (int peer = 0; peer < p.g; peer++) p.ll_logits[(p.debug & 16) ? p.rank : peer][n] = __half_as_ushort(hv);
+                    for (int peer = 0; peer < p.g; peer++) p.ll_logits[(Q4_DBG(p) & 16) ? p.rank : peer][n] = __half_as_ushort(hv);
                 const float v = __half2float(hv);
                 if (v > best || (v == best && n < bi)) { best = v; bi = n; }
             }
@@ -1500,7 +1523,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                         __threadfence_system();
                         for (int peer = 0; peer < p.g; peer++) {
                             // (debug 16: into this rank's own mailbox, once per rank slot)
-                            unsigned long long* dst = (p.debug & 16) ? p.cand[p.rank] + ((size_t)p.launch_parity * Q4_MAX_GPUS + peer) * 2 : p.cand[peer] + slot;
+                            unsigned long long* dst = (Q4_DBG(p) & 16) ? p.cand[p.rank] + ((size_t)p.launch_parity * Q4_MAX_GPUS + peer) * 2 : p.cand[peer] + slot;
                             asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(dst), "l"(tg | __float_as_uint(best)) : "memory");
                             asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(dst + 1), "l"(tg | (unsigned)bi) : "memory");
                         }
@@ -1516,7 +1539,7 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                             asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(w0) : "l"(src) : "memory");
                             asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(w1) : "l"(src + 1) : "memory");
                             if (((w0 ^ tg) >> 32) == 0 && ((w1 ^ tg) >> 32) == 0) { best = __uint_as_float((unsigned)w0); bi = (int)(unsigned)w1; break; }
-                            if (!keep_polling(polls, t0, p.status, 0x70000 + lane)) break;
+                            if (!keep_polling(polls, t0, p.status, p.wait_ns, 0x70000 + lane)) break;
                         }
                     }
                     __threadfence_system();
@@ -1640,9 +1663,24 @@ struct q4_fused {
     Q4LLArea* ll_local = nullptr;   // this rank's exchange area (inside the communicator's inbox, or own allocation at g = 1)
     size_t attn_part_bytes = 0;
     bool armed = false;             // buffers and counters are in their initial state or in step with the launches so far
+    unsigned long long wait_ns = kDefaultWaitNs;
 };
 
+#ifdef Q4_TEST_BUILD
+// Switches of the test build (see Q4_DBG): set through exported functions, never through the environment.
+static int g_test_debug = 0, g_test_split_len = 0, g_test_entries = 0;
+static int g_test_fail_alloc = -1;   // >= 0: the allocation with this running index fails once (host-side fault injection)
+static int g_test_alloc_index = 0;
+extern "C" void q4_test_set_fused_debug(int bits) { g_test_debug = bits; }
+extern "C" void q4_test_set_split_len(int positions) { g_test_split_len = positions; }
+extern "C" void q4_test_set_ring_entries(int n) { g_test_entries = n; }
+extern "C" void q4_test_fail_fused_alloc(int index) { g_test_fail_alloc = index; g_test_alloc_index = 0; }
+#endif
+
 static int fused_alloc(q4_fused* f, void** p, size_t bytes) {
+#ifdef Q4_TEST_BUILD
+    if (g_test_fail_alloc >= 0 && g_test_alloc_index++ == g_test_fail_alloc) { g_test_fail_alloc = -1; return Q4_ERR_CUDA; }
+#endif
     Q4_CUDA_TRY(cudaMalloc(p, bytes));
     f->allocs.push_back(*p);
     return Q4_OK;
@@ -1676,19 +1714,26 @@ void q4_fused_reset(q4_model* m) {
     int st = 0;
     cudaDeviceSynchronize();
     if (f->armed && cudaMemcpy(&st, f->params.status, sizeof(int), cudaMemcpyDeviceToHost) == cudaSuccess && st == 0) return;
-    f->armed = true;
+    f->armed = false;
     const q4_config& c = m->cfg;
-    cudaMemset(f->params.bar_counter, 0, sizeof(unsigned long long));
-    cudaMemset(f->params.status, 0, (4 + 4 * 256) * sizeof(int));
-    cudaMemset(f->ll_local->x, 0, sizeof(f->ll_local->x));
-    cudaMemset(f->ll_local->cand, 0, sizeof(f->ll_local->cand));
-    cudaMemset(f->params.hb, 0, 4 * (size_t)c.hidden_dim);
-    cudaMemset(f->params.q, 0, 4 * (size_t)c.dim);
-    cudaMemset(f->params.attn_part, 0, f->attn_part_bytes);
-    cudaMemset(f->params.knew, 0, 4 * (size_t)m->kv_n);
-    cudaMemset(f->params.vnew, 0, 4 * (size_t)m->kv_n);
-    cudaDeviceSynchronize();  // the memsets run on the default stream; forward calls use the caller's stream
+    bool ok = true;
+    ok &= cudaMemset(f->params.bar_counter, 0, sizeof(unsigned long long)) == cudaSuccess;
+    ok &= cudaMemset(f->params.status, 0, (4 + 4 * 256) * sizeof(int)) == cudaSuccess;
+    ok &= cudaMemset(f->ll_local->x, 0, sizeof(f->ll_local->x)) == cudaSuccess;
+    ok &= cudaMemset(f->ll_local->cand, 0, sizeof(f->ll_local->cand)) == cudaSuccess;
+    ok &= cudaMemset(f->params.hb, 0, 4 * (size_t)c.hidden_dim) == cudaSuccess;
+    ok &= cudaMemset(f->params.q, 0, 4 * (size_t)c.dim) == cudaSuccess;
+    ok &= cudaMemset(f->params.attn_part, 0, f->attn_part_bytes) == cudaSuccess;
+    ok &= cudaMemset(f->params.knew, 0, 4 * (size_t)m->kv_n) == cudaSuccess;
+    ok &= cudaMemset(f->params.vnew, 0, 4 * (size_t)m->kv_n) == cudaSuccess;
+    ok &= cudaDeviceSynchronize() == cudaSuccess;  // the memsets run on the default stream; forward calls use the caller's stream
     f->launches = 0;
+    f->armed = ok;
+}
+
+// Limit of every device-side wait of the fused kernel (default two seconds); takes effect with the next launch.
+void q4_fused_set_wait_limit(q4_model* m, unsigned long long ns) {
+    if (m->fused && !m->fused->unsupported) m->fused->wait_ns = ns ? ns : kDefaultWaitNs;
 }
 
 int q4_fused_status(q4_model* m) {
@@ -1697,7 +1742,8 @@ int q4_fused_status(q4_model* m) {
     Q4_CUDA_TRY(cudaMemcpy(st, m->fused->params.status, sizeof(st), cudaMemcpyDeviceToHost));
     if (st[0] != 0) {
         fprintf(stderr, "q4 fused path: a bounded device-side wait ran out (status %d, location 0x%x)\n", st[0], st[1]);
-        if (getenv("Q4_FUSED_DEBUG")) {
+#ifdef Q4_TEST_BUILD
+        if (g_test_debug & 32) {
             int prog[256];
             cudaMemcpy(prog, m->fused->params.status + 4, sizeof(prog), cudaMemcpyDeviceToHost);
             fprintf(stderr, "  phase reached per CTA:");
@@ -1707,14 +1753,39 @@ int q4_fused_status(q4_model* m) {
             for (int i = 0; i < m->fused->grid && i < 256; i++) fprintf(stderr, " %d", prog[i]);
             fprintf(stderr, "\n");
         }
+#endif
     }
     return st[0];
 }
 
+static int fused_build(q4_model* m, q4_fused* f);
+
+// Builds the fused path's state into a private object and publishes it in the model only when every step has
+// succeeded. A model that the path cannot serve is remembered as such (an empty object with `unsupported` set); any
+// other failure (out of memory, a CUDA error) frees what was allocated and leaves the model as it was, so that a later
+// call starts from scratch instead of launching a half-built state.
 int q4_fused_prepare(q4_model* m) {
     if (m->fused) return m->fused->unsupported ? Q4_ERR_UNSUPPORTED_SIZE : Q4_OK;
     q4_fused* f = new q4_fused();
-    m->fused = f;
+    int e = fused_build(m, f);
+    if (e == Q4_OK) {
+        m->fused = f;
+        q4_fused_reset(m);
+        if (cudaDeviceSynchronize() != cudaSuccess || !f->armed) e = Q4_ERR_CUDA;
+        if (e == Q4_OK) return Q4_OK;
+        m->fused = nullptr;
+    }
+    for (void* p : f->allocs) cudaFree(p);
+    f->allocs.clear();
+    if (e == Q4_ERR_UNSUPPORTED_SIZE && f->unsupported) {
+        m->fused = f;
+        return e;
+    }
+    delete f;
+    return e;
+}
+
+static int fused_build(q4_model* m, q4_fused* f) {
     const q4_config& c = m->cfg;
     const int g = m->g;
     if (m->column || m->head_size != 128 || (c.dim % 128) || (m->h_kc % 8) || c.dim > 4 * kCT * 8 ||   // 4 = staging batch
@@ -1816,6 +1887,7 @@ int q4_fused_prepare(q4_model* m) {
     auto finish = [&](FPhase& a) {
         const int max_units = q4_div_up(a.nunits, sms);
         if (max_units > kMaxUnitsPerCta) too_many_units = true;
+        if (a.nunits < sms) a.barrier_after = 1;   // some CTAs have no unit: keep them in step (see "tagged activations")
         max_part = std::max(max_part, max_units * a.tpu * a.nkt * 8);
         max_K = std::max(max_K, a.K);
         ph.push_back(a);
@@ -1954,7 +2026,9 @@ int q4_fused_prepare(q4_model* m) {
     int n_entries = other < budget ? (int)((budget - other) / kEntryBytes) : 0;
     n_entries = std::min(n_entries, kMaxEntries);
     if (n_entries < kMinEntries) { f->unsupported = true; return Q4_ERR_UNSUPPORTED_SIZE; }
-    if (const char* ne = getenv("Q4_FUSED_ENTRIES")) n_entries = std::max(kMinEntries, std::min(n_entries, atoi(ne)));
+#ifdef Q4_TEST_BUILD
+    if (g_test_entries > 0) n_entries = std::max(kMinEntries, std::min(n_entries, g_test_entries));
+#endif
     p.n_entries = n_entries;
     p.meta_off = n_entries * kEntryBytes + p.xq_bytes;
     p.part_off = p.meta_off + meta_bytes;
@@ -1967,8 +2041,6 @@ int q4_fused_prepare(q4_model* m) {
         f->unsupported = true;
         return Q4_ERR_UNSUPPORTED_SIZE;
     }
-    q4_fused_reset(m);
-    Q4_CUDA_TRY(cudaDeviceSynchronize());
 #undef FTRY
     return Q4_OK;
 }
@@ -1976,16 +2048,18 @@ int q4_fused_prepare(q4_model* m) {
 int q4_fused_forward(q4_model* m, cudaStream_t s, int gen_token, int no_handoff) {
     q4_fused* f = m->fused;
     if (!f || f->unsupported) return Q4_ERR_UNSUPPORTED_SIZE;
+    if (!f->armed) return Q4_ERR_CUDA;   // the last re-arm did not complete
     FParams p = f->params;
     p.write_token = gen_token;
     p.no_handoff = no_handoff;
     p.trace = f->trace;
-    {
-        const char* dbg = getenv("Q4_FUSED_DEBUG");
-        p.debug = dbg ? atoi(dbg) : 0;
-        const char* sl = getenv("Q4_FUSED_SPLIT_LEN");  // tuning / test knob
-        p.split_len = (sl && atoi(sl) > 0) ? atoi(sl) : kSplitLen;
-    }
+    p.debug = 0;
+    p.split_len = kSplitLen;
+    p.wait_ns = f->wait_ns;
+#ifdef Q4_TEST_BUILD
+    p.debug = g_test_debug & 31;
+    if (g_test_split_len > 0) p.split_len = g_test_split_len;
+#endif
     p.bar_base = f->launches * (unsigned long long)f->barriers_per_launch;
     p.tag_base = (unsigned)((f->launches * (unsigned long long)f->nphases) & 0xFFFFu);
     p.launch_parity = (unsigned)(f->launches & 1);
@@ -1994,6 +2068,69 @@ int q4_fused_forward(q4_model* m, cudaStream_t s, int gen_token, int no_handoff)
     Q4_CUDA_TRY(cudaLaunchCooperativeKernel((void*)fused_token_kernel, dim3(f->grid), dim3(kThreads), args, f->smem_bytes, s));
     return Q4_OK;
 }
+
+#ifdef Q4_TEST_BUILD
+// Test build only: the fused path's W4 dot product (activation staging to block fixed point + gemv_slot) on a caller's
+// activation vector, outside the token kernel, so that tests can feed it vectors the model never produces on its own
+// (outliers, empty groups, subnormals, the largest fp16 values). One CTA per 8-column tile; plain loads, not tuned.
+namespace {
+__global__ void __launch_bounds__(kCT) test_gemv_kernel(const uint8_t* blocks, const __half* x, __half* y, int K, int G, int nkt) {
+    extern __shared__ __align__(128) uint8_t tsm[];
+    const int ctid = threadIdx.x, cw = ctid >> 5, lane = ctid & 31, rt = blockIdx.x;
+    uint4* xq = reinterpret_cast<uint4*>(tsm);
+    float* xs_scale = reinterpret_cast<float*>(tsm + (size_t)nkt * 2 * 4 * 32 * 16);
+    int* xs_sum = reinterpret_cast<int*>(xs_scale) + 32 * 16;
+    float* part = reinterpret_cast<float*>(xs_sum + 32 * 16);
+    uint8_t* slots = reinterpret_cast<uint8_t*>(part + 16 * 8);
+    const int nwords = G * 16;
+    for (int w0 = 0; w0 < nwords; w0 += kCT) {   // every thread takes part in every round: the shuffles need whole warps
+        const int wd = w0 + ctid;
+        uint4 hv = make_uint4(0, 0, 0, 0);
+        if (wd < nwords) {
+            __half* h = reinterpret_cast<__half*>(&hv);
+            for (int j = 0; j < 8; j++) h[j] = wd * 8 + j < K ? x[wd * 8 + j] : __float2half(0.f);
+        }
+        quant_word(hv, wd, nwords, xq, xs_scale, xs_sum);
+    }
+    __syncthreads();
+    for (int kt = cw; kt < nkt; kt += kCW) {
+        const int ng = min(kSlotGroups, G - kt * kSlotGroups);
+        const uint4* src = reinterpret_cast<const uint4*>(blocks + ((size_t)rt * G + (size_t)kt * kSlotGroups) * kUnitBytes);
+        uint4* dst = reinterpret_cast<uint4*>(slots + (size_t)cw * kSlotBytes);
+        for (int i = lane; i < ng * kUnitBytes / 16; i += 32) dst[i] = src[i];
+        __syncwarp();
+        gemv_slot(reinterpret_cast<const uint8_t*>(dst), ng, kt, xq, xs_scale, xs_sum, part + kt * 8, lane);
+        __syncwarp();
+    }
+    __syncthreads();
+    if (ctid < 8) {
+        float sum = 0.f;
+        for (int kt = 0; kt < nkt; kt++) sum += part[kt * 8 + ctid];
+        y[rt * 8 + ctid] = __float2half(sum);
+    }
+}
+}  // namespace
+
+extern "C" int q4_test_fused_gemv(void* stream, uint16_t* y, const uint16_t* x, const q4_qweight* w, int K, int N) {
+    if (!y || !x || !w || K <= 0 || N <= 0 || (N & 7) || (K & 7)) return Q4_ERR_INVALID;
+    const int G = q4_groups(K), nkt = q4_div_up(G, kSlotGroups);
+    if (nkt > 16) return Q4_ERR_UNSUPPORTED_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    uint8_t* blocks = nullptr;
+    Q4_CUDA_TRY(cudaMalloc((void**)&blocks, stream_bytes(K, N)));
+    repack_kernel<<<dim3(G, N / 8), 64, 0, s>>>(blocks, w->weight, w->zeros, (const __half*)w->scales, K, N, q4_pw(K), q4_pz(K), G);
+    const size_t smem = (size_t)nkt * 2 * 4 * 32 * 16 + 32 * 16 * 4 * 2 + 16 * 8 * 4 + (size_t)kCW * kSlotBytes;
+    cudaError_t e = cudaFuncSetAttribute(test_gemv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) {
+        test_gemv_kernel<<<N / 8, kCT, smem, s>>>(blocks, (const __half*)x, (__half*)y, K, G, nkt);
+        e = cudaGetLastError();
+    }
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    cudaFree(blocks);
+    Q4_CUDA_TRY(e);
+    return Q4_OK;
+}
+#endif  // Q4_TEST_BUILD
 
 // Profiling hook: arms per-phase timestamps (CTA 0 and the last CTA) for the following fused launches and, when
 // `out` is given, copies the last launch's stamps out. Layout [2][nphases][4] of nanoseconds; also returns the

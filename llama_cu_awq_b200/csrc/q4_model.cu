@@ -178,24 +178,29 @@ extern "C" int q4_model_free(q4_model* m) {
     return Q4_OK;
 }
 
-extern "C" int q4_model_load(q4_model** out, const char* path, int rank, int gpu_count, int tp_mode, q4_comm* comm) {
-    if (!out || !path || gpu_count < 1 || gpu_count > Q4_MAX_GPUS || rank < 0 || rank >= gpu_count) return Q4_ERR_INVALID;
-    if (gpu_count > 1 && tp_mode != Q4_TP_HYBRID && tp_mode != Q4_TP_COLUMN) return Q4_ERR_INVALID;
-    if (gpu_count > 1 && !comm) return Q4_ERR_INVALID;
+// Where a model's tensors come from: the packed file (mapped), or the counter-based synthetic generator (seed).
+struct ModelSource {
+    const uint8_t* file = nullptr;   // start of the mapping, or null
+    unsigned long long seed = 0;
+};
 
-    FileMap f;
-    f.fd = open(path, O_RDONLY);
-    if (f.fd < 0) { fprintf(stderr, "Couldn't open file %s\n", path); return Q4_ERR_IO; }
-    struct stat st;
-    if (fstat(f.fd, &st) != 0) return Q4_ERR_IO;
-    f.n = (size_t)st.st_size;
-    if (f.n < sizeof(q4_config)) { fprintf(stderr, "Invalid header size\n"); return Q4_ERR_BAD_MODEL; }
-    void* mp = mmap(nullptr, f.n, PROT_READ, MAP_PRIVATE, f.fd, 0);
-    if (mp == MAP_FAILED) return Q4_ERR_IO;
-    f.p = (const uint8_t*)mp;
+// One quantized matrix of the synthetic model, generated on the device straight into this rank's shard. Every value is
+// a function of (seed, tensor id, logical element index), so all ranks and all tensor-parallel degrees see the same model.
+static int synth_q(Arena& a, DevQW* dst, int K_full, int N_full, SplitKind kind, int begin, int count, unsigned long long seed, int tid) {
+    int K = K_full, N = N_full, n0 = 0, kb = 0;
+    if (kind == SPLIT_COLS) { N = count; n0 = begin; }
+    if (kind == SPLIT_ROWS) { K = count; kb = begin; }
+    const size_t wb = (size_t)N * q4_pw(K) * 4, zb = (size_t)N * q4_pz(K) * 4, sb = (size_t)N * q4_groups(K) * 2;
+    uint32_t* dw = (uint32_t*)a.take(wb);
+    uint32_t* dz = (uint32_t*)a.take(zb);
+    uint16_t* ds = (uint16_t*)a.take(sb);
+    if (!dw || !dz || !ds) return Q4_ERR_BAD_MODEL;
+    dst->w.weight = dw; dst->w.zeros = dz; dst->w.scales = ds;
+    dst->K = K; dst->N = N;
+    return q4_synth_qweight(dw, dz, ds, K_full, K, kb, N, n0, seed, tid);
+}
 
-    q4_config c;
-    memcpy(&c, f.p, sizeof(c));
+static int model_build(q4_model** out, const q4_config& c, int rank, int gpu_count, int tp_mode, q4_comm* comm, const ModelSource& src) {
     if (c.dim <= 0 || c.hidden_dim <= 0 || c.n_layers <= 0 || c.n_heads <= 0 || c.n_kv_heads <= 0 || c.vocab_size <= 0 ||
         c.seq_len <= 0 || c.seq_len > Q4_MAX_SEQ_LEN || c.dim % c.n_heads || c.n_heads % c.n_kv_heads || (c.dim & 7) || (c.hidden_dim & 7))
         return Q4_ERR_BAD_MODEL;
@@ -204,10 +209,6 @@ extern "C" int q4_model_load(q4_model** out, const char* path, int rank, int gpu
     const int kv_dim = c.dim * c.n_kv_heads / c.n_heads;
     if (c.n_heads % g || c.n_kv_heads % g || c.vocab_size % (8 * g)) return Q4_ERR_UNSUPPORTED_SIZE;
     if (g > 1 && ((c.dim / g) % 128 || c.hidden_dim % 128)) return Q4_ERR_UNSUPPORTED_SIZE;
-    const size_t per_layer = 2 * qw_bytes(c.dim, c.dim) + 2 * qw_bytes(c.dim, kv_dim) + 2 * qw_bytes(c.dim, c.hidden_dim) +
-                             qw_bytes(c.hidden_dim, c.dim) + 4 * (size_t)c.dim;
-    const size_t expect = 32 + 4 * (size_t)c.vocab_size * c.dim + 2 * (size_t)c.dim + per_layer * c.n_layers;
-    if (expect != f.n) { fprintf(stderr, "error reading weights"); return Q4_ERR_BAD_MODEL; }
 
     q4_model* m = new q4_model();
     m->cfg = c;
@@ -235,6 +236,7 @@ extern "C" int q4_model_load(q4_model** out, const char* path, int rank, int gpu
     m->topp = 0.f;
     m->rng_state = 0;
     m->fused = nullptr;
+    m->host_pos = 0;
     m->arena = nullptr;
     m->x = m->xb = m->hb = m->q = m->logits = m->kc = m->vc = nullptr;
     m->attn_scratch = nullptr;
@@ -264,39 +266,69 @@ extern "C" int q4_model_load(q4_model** out, const char* path, int rank, int gpu
     Arena a{m->arena, 0, need};
 
     printf("\nLoading Weights... ");
-    const uint8_t* p = f.p + 32;
-    LOAD_TRY(upload_raw(a, &m->emb, p, 2 * (size_t)c.vocab_size * c.dim));
-    p += 2 * (size_t)c.vocab_size * c.dim;
-    LOAD_TRY(upload_raw(a, &m->wcls, p + 2 * (size_t)rank * m->v_n * c.dim, 2 * (size_t)m->v_n * c.dim));
-    p += 2 * (size_t)c.vocab_size * c.dim;
-    LOAD_TRY(upload_raw(a, &m->rms_final, p, 2 * (size_t)c.dim));
-    p += 2 * (size_t)c.dim;
     m->layers.resize(c.n_layers);
-    std::vector<uint8_t> tmp;
-    for (int l = 0; l < c.n_layers; l++) {
-        DevLayer& L = m->layers[l];
-        HostQ hq, hk, hv, ho, hup, hgate, hdown;
-        p = take_q(p, &hq, c.dim, c.dim);
-        p = take_q(p, &hk, c.dim, kv_dim);
-        p = take_q(p, &hv, c.dim, kv_dim);
-        p = take_q(p, &ho, c.dim, c.dim);
-        p = take_q(p, &hup, c.dim, c.hidden_dim);    // up precedes gate in the file (weight_packer.cpp:283-284)
-        p = take_q(p, &hgate, c.dim, c.hidden_dim);
-        p = take_q(p, &hdown, c.hidden_dim, c.dim);
-        const SplitKind col = g > 1 ? SPLIT_COLS : SPLIT_NONE, row = g > 1 ? SPLIT_ROWS : SPLIT_NONE;
-        LOAD_TRY(upload_q(a, &L.q, hq, col, rank * m->q_n, m->q_n, tmp));
-        LOAD_TRY(upload_q(a, &L.k, hk, col, rank * m->kv_n, m->kv_n, tmp));
-        LOAD_TRY(upload_q(a, &L.v, hv, col, rank * m->kv_n, m->kv_n, tmp));
-        if (m->column) LOAD_TRY(upload_q(a, &L.o, ho, col, rank * (c.dim / g), c.dim / g, tmp));
-        else LOAD_TRY(upload_q(a, &L.o, ho, row, m->o_kb, m->o_kc, tmp));
-        LOAD_TRY(upload_q(a, &L.up, hup, col, m->h_kb, m->h_kc, tmp));
-        LOAD_TRY(upload_q(a, &L.gate, hgate, col, m->h_kb, m->h_kc, tmp));
-        if (m->column) LOAD_TRY(upload_q(a, &L.down, hdown, col, rank * (c.dim / g), c.dim / g, tmp));
-        else LOAD_TRY(upload_q(a, &L.down, hdown, row, m->h_kb, m->h_kc, tmp));
-        LOAD_TRY(upload_raw(a, &L.rms_att, p, 2 * (size_t)c.dim));
+    const SplitKind col = g > 1 ? SPLIT_COLS : SPLIT_NONE, row = g > 1 ? SPLIT_ROWS : SPLIT_NONE;
+    if (src.file) {
+        const uint8_t* p = src.file + 32;
+        LOAD_TRY(upload_raw(a, &m->emb, p, 2 * (size_t)c.vocab_size * c.dim));
+        p += 2 * (size_t)c.vocab_size * c.dim;
+        LOAD_TRY(upload_raw(a, &m->wcls, p + 2 * (size_t)rank * m->v_n * c.dim, 2 * (size_t)m->v_n * c.dim));
+        p += 2 * (size_t)c.vocab_size * c.dim;
+        LOAD_TRY(upload_raw(a, &m->rms_final, p, 2 * (size_t)c.dim));
         p += 2 * (size_t)c.dim;
-        LOAD_TRY(upload_raw(a, &L.rms_ffn, p, 2 * (size_t)c.dim));
-        p += 2 * (size_t)c.dim;
+        std::vector<uint8_t> tmp;
+        for (int l = 0; l < c.n_layers; l++) {
+            DevLayer& L = m->layers[l];
+            HostQ hq, hk, hv, ho, hup, hgate, hdown;
+            p = take_q(p, &hq, c.dim, c.dim);
+            p = take_q(p, &hk, c.dim, kv_dim);
+            p = take_q(p, &hv, c.dim, kv_dim);
+            p = take_q(p, &ho, c.dim, c.dim);
+            p = take_q(p, &hup, c.dim, c.hidden_dim);    // up precedes gate in the file (weight_packer.cpp:283-284)
+            p = take_q(p, &hgate, c.dim, c.hidden_dim);
+            p = take_q(p, &hdown, c.hidden_dim, c.dim);
+            LOAD_TRY(upload_q(a, &L.q, hq, col, rank * m->q_n, m->q_n, tmp));
+            LOAD_TRY(upload_q(a, &L.k, hk, col, rank * m->kv_n, m->kv_n, tmp));
+            LOAD_TRY(upload_q(a, &L.v, hv, col, rank * m->kv_n, m->kv_n, tmp));
+            if (m->column) LOAD_TRY(upload_q(a, &L.o, ho, col, rank * (c.dim / g), c.dim / g, tmp));
+            else LOAD_TRY(upload_q(a, &L.o, ho, row, m->o_kb, m->o_kc, tmp));
+            LOAD_TRY(upload_q(a, &L.up, hup, col, m->h_kb, m->h_kc, tmp));
+            LOAD_TRY(upload_q(a, &L.gate, hgate, col, m->h_kb, m->h_kc, tmp));
+            if (m->column) LOAD_TRY(upload_q(a, &L.down, hdown, col, rank * (c.dim / g), c.dim / g, tmp));
+            else LOAD_TRY(upload_q(a, &L.down, hdown, row, m->h_kb, m->h_kc, tmp));
+            LOAD_TRY(upload_raw(a, &L.rms_att, p, 2 * (size_t)c.dim));
+            p += 2 * (size_t)c.dim;
+            LOAD_TRY(upload_raw(a, &L.rms_ffn, p, 2 * (size_t)c.dim));
+            p += 2 * (size_t)c.dim;
+        }
+    } else {
+        // tensor ids of the generator: 1 embedding, 2 classifier, 16 + (layer * 8 + matrix) * 4 + part (q k v o up gate down; the
+        // part is added by q4_synth_qweight: 0 weights, 1 zero points, 2 scales); the RMSNorm weights are 1.0
+        auto take16 = [&](uint16_t** dst, size_t halfs) { *dst = (uint16_t*)a.take(2 * halfs); return *dst ? Q4_OK : Q4_ERR_BAD_MODEL; };
+        LOAD_TRY(take16(&m->emb, (size_t)c.vocab_size * c.dim));
+        LOAD_TRY(q4_synth_normal(m->emb, (long long)c.vocab_size * c.dim, 0, src.seed, 1));
+        LOAD_TRY(take16(&m->wcls, (size_t)m->v_n * c.dim));
+        LOAD_TRY(q4_synth_normal(m->wcls, (long long)m->v_n * c.dim, (long long)rank * m->v_n * c.dim, src.seed, 2));
+        LOAD_TRY(take16(&m->rms_final, c.dim));
+        LOAD_TRY(q4_synth_const(m->rms_final, c.dim, 0x3C00));
+        for (int l = 0; l < c.n_layers; l++) {
+            DevLayer& L = m->layers[l];
+            auto tid = [&](int matrix) { return 16 + (l * 8 + matrix) * 4; };
+            LOAD_TRY(synth_q(a, &L.q, c.dim, c.dim, col, rank * m->q_n, m->q_n, src.seed, tid(0)));
+            LOAD_TRY(synth_q(a, &L.k, c.dim, kv_dim, col, rank * m->kv_n, m->kv_n, src.seed, tid(1)));
+            LOAD_TRY(synth_q(a, &L.v, c.dim, kv_dim, col, rank * m->kv_n, m->kv_n, src.seed, tid(2)));
+            if (m->column) LOAD_TRY(synth_q(a, &L.o, c.dim, c.dim, col, rank * (c.dim / g), c.dim / g, src.seed, tid(3)));
+            else LOAD_TRY(synth_q(a, &L.o, c.dim, c.dim, row, m->o_kb, m->o_kc, src.seed, tid(3)));
+            LOAD_TRY(synth_q(a, &L.up, c.dim, c.hidden_dim, col, m->h_kb, m->h_kc, src.seed, tid(4)));
+            LOAD_TRY(synth_q(a, &L.gate, c.dim, c.hidden_dim, col, m->h_kb, m->h_kc, src.seed, tid(5)));
+            if (m->column) LOAD_TRY(synth_q(a, &L.down, c.hidden_dim, c.dim, col, rank * (c.dim / g), c.dim / g, src.seed, tid(6)));
+            else LOAD_TRY(synth_q(a, &L.down, c.hidden_dim, c.dim, row, m->h_kb, m->h_kc, src.seed, tid(6)));
+            LOAD_TRY(take16(&L.rms_att, c.dim));
+            LOAD_TRY(q4_synth_const(L.rms_att, c.dim, 0x3C00));
+            LOAD_TRY(take16(&L.rms_ffn, c.dim));
+            LOAD_TRY(q4_synth_const(L.rms_ffn, c.dim, 0x3C00));
+        }
+        LOAD_CUDA(cudaDeviceSynchronize());
     }
     printf("done!\n");
 
@@ -324,6 +356,46 @@ extern "C" int q4_model_load(q4_model** out, const char* path, int rank, int gpu
     return Q4_OK;
 }
 
+extern "C" int q4_model_load(q4_model** out, const char* path, int rank, int gpu_count, int tp_mode, q4_comm* comm) {
+    if (!out || !path || gpu_count < 1 || gpu_count > Q4_MAX_GPUS || rank < 0 || rank >= gpu_count) return Q4_ERR_INVALID;
+    if (gpu_count > 1 && tp_mode != Q4_TP_HYBRID && tp_mode != Q4_TP_COLUMN) return Q4_ERR_INVALID;
+    if (gpu_count > 1 && !comm) return Q4_ERR_INVALID;
+
+    FileMap f;
+    f.fd = open(path, O_RDONLY);
+    if (f.fd < 0) { fprintf(stderr, "Couldn't open file %s\n", path); return Q4_ERR_IO; }
+    struct stat st;
+    if (fstat(f.fd, &st) != 0) return Q4_ERR_IO;
+    f.n = (size_t)st.st_size;
+    if (f.n < sizeof(q4_config)) { fprintf(stderr, "Invalid header size\n"); return Q4_ERR_BAD_MODEL; }
+    void* mp = mmap(nullptr, f.n, PROT_READ, MAP_PRIVATE, f.fd, 0);
+    if (mp == MAP_FAILED) return Q4_ERR_IO;
+    f.p = (const uint8_t*)mp;
+
+    q4_config c;
+    memcpy(&c, f.p, sizeof(c));
+    if (c.dim <= 0 || c.hidden_dim <= 0 || c.n_layers <= 0 || c.n_heads <= 0 || c.n_kv_heads <= 0 || c.vocab_size <= 0 || c.dim % c.n_heads)
+        return Q4_ERR_BAD_MODEL;
+    const int kv_dim = (int)((long long)c.dim * c.n_kv_heads / c.n_heads);
+    const size_t per_layer = 2 * qw_bytes(c.dim, c.dim) + 2 * qw_bytes(c.dim, kv_dim) + 2 * qw_bytes(c.dim, c.hidden_dim) +
+                             qw_bytes(c.hidden_dim, c.dim) + 4 * (size_t)c.dim;
+    const size_t expect = 32 + 4 * (size_t)c.vocab_size * c.dim + 2 * (size_t)c.dim + per_layer * c.n_layers;
+    if (expect != f.n) { fprintf(stderr, "error reading weights"); return Q4_ERR_BAD_MODEL; }
+    ModelSource src;
+    src.file = f.p;
+    return model_build(out, c, rank, gpu_count, tp_mode, comm, src);
+}
+
+extern "C" int q4_model_create_synthetic(q4_model** out, const q4_config* cfg, unsigned long long seed, int rank, int gpu_count, int tp_mode,
+                                         q4_comm* comm) {
+    if (!out || !cfg || gpu_count < 1 || gpu_count > Q4_MAX_GPUS || rank < 0 || rank >= gpu_count) return Q4_ERR_INVALID;
+    if (gpu_count > 1 && tp_mode != Q4_TP_HYBRID && tp_mode != Q4_TP_COLUMN) return Q4_ERR_INVALID;
+    if (gpu_count > 1 && !comm) return Q4_ERR_INVALID;
+    ModelSource src;
+    src.seed = seed;
+    return model_build(out, *cfg, rank, gpu_count, tp_mode, comm, src);
+}
+
 extern "C" int q4_model_config(const q4_model* m, q4_config* out) {
     if (!m || !out) return Q4_ERR_INVALID;
     *out = m->cfg;
@@ -343,7 +415,12 @@ extern "C" int q4_model_read(const q4_model* m, int what, uint16_t* host_out) {
 
 extern "C" int q4_model_reset(q4_model* m, const int* prompt_tokens, int n, int pos) {
     if (!m || n < 0 || n > Q4_MAX_SEQ_LEN || pos < 0 || pos >= m->cfg.seq_len) return Q4_ERR_INVALID;
+    // the embedding gather indexes the table with these ids on the device: refuse anything outside the vocabulary here
+    if (prompt_tokens)
+        for (int i = 0; i < n; i++)
+            if (prompt_tokens[i] < 0 || prompt_tokens[i] >= m->cfg.vocab_size) return Q4_ERR_INVALID;
     Q4_CUDA_TRY(cudaDeviceSynchronize());
+    m->host_pos = pos;
     Q4_CUDA_TRY(cudaMemcpy(m->pos, &pos, sizeof(int), cudaMemcpyHostToDevice));
     m->shared->pos = pos;
     if (n > 0 && prompt_tokens) memcpy((void*)m->shared->tokens, prompt_tokens, sizeof(int) * (size_t)n);
@@ -400,6 +477,11 @@ extern "C" int q4_model_forward(q4_model* m, void* stream, int gen_token, int pa
     cudaStream_t s = (cudaStream_t)stream;
     gen_token = gen_token != 0;
     if (path < 0 || path > 2) return Q4_ERR_INVALID;
+    // One call = one position. The kernels write K/V row `pos` and tokens[pos + 1]: a call past the model's sequence
+    // length would write outside the cache, so it is refused here (the host counts the calls since the last reset; the
+    // device-side position cannot be read without waiting for the stream).
+    if (m->host_pos >= m->cfg.seq_len || m->host_pos >= Q4_MAX_SEQ_LEN - 1) return Q4_ERR_LIMIT;
+    m->host_pos++;
     // sample() draws one coin per call, used or not (sampler.h:79); the greedy branch is taken at temperature 0 and for
     // prompt positions (sampler.h:81)
     const float coin = q4_random_f32(&m->rng_state);
@@ -441,6 +523,13 @@ extern "C" int q4_model_set_sampler(q4_model* m, float temperature, float topp, 
 extern "C" int q4_model_prepare(q4_model* m, int path) {
     if (!m || path < 0 || path > 2) return Q4_ERR_INVALID;
     return path == 2 ? q4_fused_prepare(m) : Q4_OK;
+}
+
+extern "C" int q4_model_set_wait_limit_ns(q4_model* m, unsigned long long ns) {
+    if (!m) return Q4_ERR_INVALID;
+    if (int e = q4_fused_prepare(m)) return e;
+    q4_fused_set_wait_limit(m, ns);
+    return Q4_OK;
 }
 
 extern "C" int q4_model_status(q4_model* m) {
@@ -523,5 +612,69 @@ extern "C" int q4_model_time_ffn(q4_model* m, void* stream, int reps, double* to
     cudaEventDestroy(e1);
     *total_ms = ms;
     *bytes_per_launch = 2.0 * (double)qw_bytes(dim, m->h_kc) + 2.0 * dim + 2.0 * m->h_kc;
+    return e;
+}
+
+// Measurement hook: one W4 wrapper (kind 0 q4_matmul_q4, 1 q4_qkv_matvec, 2 q4_ffn_matvec_silu) over `nmat` distinct
+// matrices of one shape, captured as one CUDA graph (kind 1 takes three, kind 2 two matrices per launch) and replayed
+// `reps` times between two events on `stream`, so that the weights come from HBM and not from L2 and no launch gap is
+// timed. Returns microseconds per launch and the algorithmic bytes of one launch.
+extern "C" int q4_time_q4_op(void* stream, int kind, uint16_t* y, uint16_t* y2, uint16_t* y3, const uint16_t* x, const q4_qweight* mats, int nmat,
+                             int K, int N, int reps, const int* pPos, double* us_per_launch, double* bytes_per_launch) {
+    if (!y || !x || !mats || nmat < 1 || reps < 1 || !us_per_launch || !bytes_per_launch || kind < 0 || kind > 2) return Q4_ERR_INVALID;
+    const int per = kind == 1 ? 3 : kind == 2 ? 2 : 1;
+    if (nmat < per || (kind == 1 && (!y2 || !y3 || !pPos))) return Q4_ERR_INVALID;
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    Q4_CUDA_TRY(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+    int e = Q4_OK, launches = 0;
+    for (int i = 0; i + per <= nmat && e == Q4_OK; i += per, launches++) {
+        if (kind == 0) e = q4_matmul_q4(s, y, x, &mats[i], K, N, 0, 1, -1, nullptr);
+        else if (kind == 1) e = q4_qkv_matvec(s, y, y2, y3, x, &mats[i], &mats[i + 1], &mats[i + 2], K, N, N, 0, pPos);
+        else e = q4_ffn_matvec_silu(s, y, x, &mats[i], &mats[i + 1], K, N);
+    }
+    cudaError_t ce = cudaStreamEndCapture(s, &graph);
+    if (e != Q4_OK) { if (graph) cudaGraphDestroy(graph); return e; }
+    Q4_CUDA_TRY(ce);
+    Q4_CUDA_TRY(cudaGraphInstantiate(&exec, graph, 0));
+    cudaEvent_t e0, e1;
+    Q4_CUDA_TRY(cudaEventCreate(&e0));
+    Q4_CUDA_TRY(cudaEventCreate(&e1));
+    for (int r = 0; r < 3; r++) Q4_CUDA_TRY(cudaGraphLaunch(exec, s));   // warm-up
+    Q4_CUDA_TRY(cudaEventRecord(e0, s));
+    for (int r = 0; r < reps; r++) Q4_CUDA_TRY(cudaGraphLaunch(exec, s));
+    Q4_CUDA_TRY(cudaEventRecord(e1, s));
+    Q4_CUDA_TRY(cudaEventSynchronize(e1));
+    float ms = 0.f;
+    Q4_CUDA_TRY(cudaEventElapsedTime(&ms, e0, e1));
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    cudaGraphExecDestroy(exec);
+    cudaGraphDestroy(graph);
+    *us_per_launch = 1e3 * ms / ((double)reps * launches);
+    *bytes_per_launch = per * (double)qw_bytes(K, N) + 2.0 * K + 2.0 * N * per / (kind == 2 ? 2 : 1);
+    return Q4_OK;
+}
+
+// Measurement hook: `reps` in-place all-reduces of `count` halfs back to back on `stream` between two events (the
+// caller aligns the ranks with a host barrier first and takes the maximum over the ranks).
+extern "C" int q4_time_all_reduce(q4_comm* comm, void* stream, uint16_t* buf, int count, int reps, double* us_per_call) {
+    if (!comm || !buf || reps < 1 || !us_per_call) return Q4_ERR_INVALID;
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaEvent_t e0, e1;
+    Q4_CUDA_TRY(cudaEventCreate(&e0));
+    Q4_CUDA_TRY(cudaEventCreate(&e1));
+    int e = Q4_OK;
+    for (int r = 0; r < 10 && e == Q4_OK; r++) e = q4_all_reduce(comm, s, buf, count);
+    Q4_CUDA_TRY(cudaEventRecord(e0, s));
+    for (int r = 0; r < reps && e == Q4_OK; r++) e = q4_all_reduce(comm, s, buf, count);
+    Q4_CUDA_TRY(cudaEventRecord(e1, s));
+    Q4_CUDA_TRY(cudaEventSynchronize(e1));
+    float ms = 0.f;
+    Q4_CUDA_TRY(cudaEventElapsedTime(&ms, e0, e1));
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    *us_per_call = 1e3 * ms / reps;
     return e;
 }

@@ -45,6 +45,7 @@ struct q4_model {
     float temperature, topp;
     unsigned long long rng_state;
     q4_fused* fused;
+    int host_pos;               // forward calls since the last reset + the reset's position (bounds the K/V row written)
 };
 
 // q4_fused.cu
@@ -53,3 +54,9 @@ int q4_fused_forward(q4_model* m, cudaStream_t s, int gen_token, int no_handoff)
 void q4_fused_reset(q4_model* m);                               // re-arms barrier counters (after q4_model_reset)
 void q4_fused_free(q4_model* m);
 int q4_fused_status(q4_model* m);
+void q4_fused_set_wait_limit(q4_model* m, unsigned long long ns);   // device-side wait limit of the fused kernel (0 = default)
+
+// q4_synth.cu: counter-based synthetic tensors generated on the device, shard by shard (see q4_model_create_synthetic)
+int q4_synth_qweight(uint32_t* w, uint32_t* z, uint16_t* s, int K_full, int K, int k_begin, int N, int n_begin, unsigned long long seed, int tid);
+int q4_synth_normal(uint16_t* dst, long long count, long long idx0, unsigned long long seed, int tid);
+int q4_synth_const(uint16_t* dst, int n, uint16_t value);

@@ -10,10 +10,16 @@ from ._lib import check
 
 
 class Transformer:
-    def __init__(self, checkpoint_path, rank=0, gpu_count=1, tp_mode=_lib.Q4_TP_NONE, comm=None):
-        self._L = _lib.lib()
+    def __init__(self, checkpoint_path, rank=0, gpu_count=1, tp_mode=_lib.Q4_TP_NONE, comm=None, lib=None, synthetic=None):
+        self._L = lib or _lib.lib()
         self.h = C.c_void_p()
-        check(self._L.q4_model_load(C.byref(self.h), checkpoint_path.encode(), rank, gpu_count, tp_mode, comm), "build_transformer")
+        if synthetic is not None:   # (config tuple or q4_config, seed): generated on the device, no file
+            cfg, seed = synthetic
+            if not isinstance(cfg, _lib.q4_config):
+                cfg = _lib.q4_config(*[int(v) for v in cfg[:7]], float(cfg[7]))
+            check(self._L.q4_model_create_synthetic(C.byref(self.h), C.byref(cfg), int(seed), rank, gpu_count, tp_mode, comm), "create_synthetic")
+        else:
+            check(self._L.q4_model_load(C.byref(self.h), checkpoint_path.encode(), rank, gpu_count, tp_mode, comm), "build_transformer")
         self.config = _lib.q4_config()
         check(self._L.q4_model_config(self.h, C.byref(self.config)), "config")
         self.stream = torch.cuda.Stream()
@@ -36,6 +42,13 @@ class Transformer:
 
     def status(self):
         return self._L.q4_model_status(self.h)
+
+    def set_wait_limit_ns(self, ns):
+        """Limit of the fused kernel's device-side waits (0 = default of two seconds)."""
+        check(self._L.q4_model_set_wait_limit_ns(self.h, int(ns)), "set_wait_limit")
+
+    def logits_device_ptr(self):
+        return self._L.q4_model_logits(self.h)
 
     def synchronize(self):
         self.stream.synchronize()

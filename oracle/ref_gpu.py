@@ -97,12 +97,53 @@ def matmul_f16(x, W, n, d):
     return y.cpu().numpy()
 
 
-def generate(path, prompt_tokens, steps, vocab_size):
+def generate(path, prompt_tokens, steps, vocab_size, gpu_count=1):
+    """The reference program's own loader and generation loop; gpu_count > 1 = its hybrid tensor parallelism, one host
+    thread per GPU (devices 0 .. gpu_count-1 of this process)."""
     prompt = np.ascontiguousarray(prompt_tokens, dtype=np.int32)
     out = np.zeros(steps + 2, np.int32)
     logits = np.zeros(vocab_size, np.float16)
     toks, timed, secs = C.c_double(), C.c_int(), C.c_double()
     L = lib()
-    L.ref_generate(path.encode(), prompt.ctypes.data_as(C.c_void_p), prompt.size, steps, out.ctypes.data_as(C.c_void_p),
-                   logits.ctypes.data_as(C.c_void_p), C.byref(toks), C.byref(timed), C.byref(secs))
+    rc = L.ref_generate(path.encode(), prompt.ctypes.data_as(C.c_void_p), prompt.size, steps, int(gpu_count), out.ctypes.data_as(C.c_void_p),
+                        logits.ctypes.data_as(C.c_void_p), C.byref(toks), C.byref(timed), C.byref(secs))
+    assert rc == 0, rc
     return out[:steps + 1], logits, toks.value, timed.value, secs.value
+
+
+def sample(logits16, temperature, topp, seed):
+    """The reference's sample() on fp16 logits: (token, coin)."""
+    a = np.ascontiguousarray(logits16, dtype=np.float16)
+    tok, coin = C.c_int(), C.c_float()
+    rc = lib().ref_sample(a.ctypes.data_as(C.c_void_p), a.size, C.c_float(temperature), C.c_float(topp), C.c_ulonglong(seed), C.byref(tok), C.byref(coin))
+    assert rc == 0, rc
+    return tok.value, coin.value
+
+
+def time_q4(kind, K, N, nmat=32, reps=20, seed=0):
+    """Microseconds per launch of the reference's W4 wrapper (0 matmul, 1 qkv_matvec, 2 ffn_matvec_silu) over `nmat`
+    distinct random matrices of one shape (weights from HBM, not L2)."""
+    per = {0: 1, 1: 3, 2: 2}[kind]
+    nmat = max(per, nmat // per * per)
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    pw, pz, gg = ((K + 31) // 32) * 4, ((K + 127) // 128 + 7) // 8, (K + 127) // 128
+    ws = [torch.randint(-2**31, 2**31 - 1, (N, pw), dtype=torch.int32, device="cuda", generator=g) for _ in range(nmat)]
+    zs = [torch.randint(-2**31, 2**31 - 1, (N, pz), dtype=torch.int32, device="cuda", generator=g) for _ in range(nmat)]
+    ss = [(torch.rand((N, gg), device="cuda", generator=g) * 0.018 + 0.002).half() for _ in range(nmat)]
+    x = torch.randn(K, device="cuda", generator=g).half()
+    ys = [torch.zeros(max(N, 8) * 4, dtype=torch.float16, device="cuda") for _ in range(3)]
+    pos = torch.zeros(1, dtype=torch.int32, device="cuda")
+    arr = lambda ts: (C.c_void_p * len(ts))(*[t.data_ptr() for t in ts])  # noqa: E731
+    us = C.c_double()
+    torch.cuda.synchronize()
+    rc = lib().ref_time_q4(kind, _p(ys[0]), _p(ys[1]), _p(ys[2]), _p(x), arr(ws), arr(zs), arr(ss), nmat, K, N, reps, _p(pos), C.byref(us))
+    assert rc == 0, rc
+    return us.value
+
+
+def time_allreduce(gpu_count, count, reps=200):
+    """Microseconds per call of the reference's cudaAllReduce of `count` halfs on gpu_count GPUs (thread per GPU)."""
+    us = C.c_double()
+    rc = lib().ref_time_allreduce(gpu_count, count, reps, C.byref(us))
+    assert rc == 0, rc
+    return us.value

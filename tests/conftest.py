@@ -33,7 +33,7 @@ def _built():
     """Builds the oracle and the CUDA library when they are missing (nvcc cross-compiles without a GPU)."""
     from llama_cu_awq_b200 import build as b
     from oracle import q4_oracle
-    if not os.path.exists(b.LIB):
+    if not os.path.exists(b.LIB) or not os.path.exists(b.TEST_LIB):
         b.build()
     if not os.path.exists(q4_oracle.LIB_PATH):
         q4_oracle.build()

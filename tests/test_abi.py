@@ -45,3 +45,17 @@ def test_missing_library_fails_loudly(monkeypatch):
     monkeypatch.setattr(_lib, "LIB_PATH", "/nonexistent/libq4b200.so")
     with pytest.raises(RuntimeError, match="no fallback"):
         _lib.lib()
+
+
+def test_measurement_switches_live_in_the_test_build_only():
+    """The product library exports no q4_test_* symbol and reads no environment variable on the decode path; the test
+    build (same sources, -DQ4_TEST_BUILD) exports every switch the tests use."""
+    prod = ctypes.CDLL(_lib.LIB_PATH)
+    test = ctypes.CDLL(_lib.TEST_LIB_PATH)
+    for name in _lib.TEST_SIGNATURES:
+        assert hasattr(test, name), name
+        assert not hasattr(prod, name), name
+    csrc = os.path.join(ROOT, "llama_cu_awq_b200", "csrc")
+    for f in os.listdir(csrc):
+        if f.endswith((".cu", ".cuh", ".h")):
+            assert "getenv" not in open(os.path.join(csrc, f)).read(), f

@@ -124,15 +124,6 @@ def test_greedy_argmax_on_identical_logits(tiny_path, fwd_path):
     t.close()
 
 
-def test_fused_attention_splits(mid_gqa_path, monkeypatch):
-    """Heads split over several CTAs (long contexts): forced here with a tiny split length."""
-    monkeypatch.setenv("Q4_FUSED_SPLIT_LEN", "8")
-    tokens = np.random.default_rng(9).integers(3, 2048, size=60, dtype=np.int32)
-    got, ref = teacher_forced(mid_gqa_path, tokens, 2)
-    for pos in (0, 7, 8, 9, 23, 24, 25, 40, 59):
-        assert_close(got[pos], ref[pos], f"split attention, pos {pos}")
-
-
 def test_long_context_fused_vs_per_op(tmp_path):
     """1100 positions: the fused kernel's attention (four splits per head, several steps per split, RoPE table far out)
     against the per-op path, whose attention kernel is held to the oracle up to position 4095 at op level. The first
@@ -222,3 +213,36 @@ def test_token_bytes_formula(tiny_path):
     exp = L_ * (4 * q(dim, dim) + 2 * q(dim, hid) + q(hid, dim)) + 2 * V * dim + 2 * dim * (2 * L_ + 1) + 2 * dim + 2 * L_ * dim * 2 * (5 + 1) + 2 * L_ * dim * 2
     assert t.token_bytes(5) == exp
     t.close()
+
+
+@pytest.mark.parametrize("cfg", ["tiny-gqa", "mid"])
+def test_device_generated_model_equals_its_packed_file(cfg, tmp_path):
+    """q4_model_create_synthetic (tensors generated on the device, shard by shard) against the same counter-based
+    model written as a packed file by synth.py and loaded through q4_model_load: identical logits, bit for bit, on
+    every forward path, and within tolerance of the oracle run on that file."""
+    path = str(tmp_path / f"{cfg}_counter.bin")
+    synth.write_counter_model_file(path, cfg, seed=11)
+    vocab = synth.CONFIGS[cfg][5]
+    tokens = np.random.default_rng(8).integers(3, vocab, size=10, dtype=np.int32)
+    m = O.Model(open(path, "rb").read())
+    ref = []
+    for pos, tok in enumerate(tokens):
+        m.forward(int(tok), pos, order=1)
+        ref.append(m.logits())
+    for fwd_path in (1, 2):
+        outs = []
+        for synthetic in (None, (synth.CONFIGS[cfg], 11)):
+            t = Transformer(path, synthetic=synthetic)
+            assert fwd_path != 2 or t.best_path() == 2
+            t.reset(tokens, 0)
+            got = []
+            for pos in range(len(tokens)):
+                t.forward(gen_token=False, path=fwd_path)
+                t.synchronize()
+                got.append(t.logits())
+            assert t.status() == 0
+            t.close()
+            outs.append(np.stack(got))
+        assert (outs[0].view(np.uint16) == outs[1].view(np.uint16)).all(), f"path {fwd_path}: device-generated model differs from its file"
+        for pos in range(len(tokens)):
+            assert_close(outs[1][pos], ref[pos], f"{cfg} path {fwd_path} pos {pos}")

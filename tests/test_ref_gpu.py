@@ -58,3 +58,37 @@ def test_reference_model_generation_vs_library(tmp_path):
     t.synchronize()
     assert_close(t.logits(), logits, "final logits vs reference program")
     t.close()
+
+
+@pytest.mark.parametrize("topp", [0.9, 0.5, 0.0])
+def test_sampler_pick_matches_the_reference_away_from_boundaries(topp):
+    """q4_sample_topp against the reference's own sample() (sampler.h:77-115: softmax kernel, radix sort, fp16 prefix
+    sum, threshold search) on the same logits, temperature, top-p and seed. The reference accumulates its prefix sum
+    in fp16 in an order the library leaves open, so only cases are compared where the threshold lies clear of the
+    picked element's boundaries (in exact arithmetic); those must agree, and they must be the large majority."""
+    from test_oracle_sampler import select_float64
+    from test_sampler_gpu import Mailbox
+    n = 32000
+    compared = agreed = 0
+    for seed in range(1, 25):
+        rng = np.random.default_rng(seed)
+        logits = rng.standard_normal(n)
+        logits[rng.choice(n, 12, replace=False)] += rng.uniform(8.0, 12.0, 12)   # a dozen dominant tokens hold most of the mass
+        logits = logits.astype(np.float16)
+        temperature = (0.7, 1.0, 1.3)[seed % 3]
+        ref_tok, coin = R.sample(logits, temperature, topp, seed)
+        tok, p = Mailbox().run(logits, temperature, topp, coin)
+        assert tok == select_float64(p, topp, coin)
+        # distance of the threshold from the nearest prefix-sum boundary of the picked element, in exact arithmetic
+        pf = p.astype(np.float64)
+        order = np.argsort(-pf, kind="stable") if 0.0 < topp < 1.0 else np.arange(n)
+        cum = np.cumsum(pf[order])
+        thr = coin * topp if 0.0 < topp < 1.0 else coin
+        k = int(np.nonzero(order == tok)[0][0])
+        margin = min(cum[k] - thr, thr - (cum[k - 1] if k > 0 else 0.0))
+        if margin < 6e-3:      # fp16 running sums near 0.5-1.0 carry steps of 5e-4-1e-3: too close to call
+            continue
+        compared += 1
+        agreed += int(tok == ref_tok)
+    assert compared >= 8
+    assert agreed == compared, (agreed, compared)

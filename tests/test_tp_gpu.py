@@ -13,12 +13,16 @@ from llama_cu_awq_b200 import synth
 pytestmark = [pytest.mark.gpu, pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")]
 
 
-def _run_tp(cfg, fwd_path, n, tmp_path, mode="hybrid"):
+def _run_tp(cfg, fwd_path, n, tmp_path, mode="hybrid", extra=""):
     path = str(tmp_path / f"{cfg}.bin")
-    synth.write_model_file(path, cfg, seed=7)
+    if extra == "synthetic":
+        synth.write_counter_model_file(path, cfg, seed=7)
+    else:
+        synth.write_model_file(path, cfg, seed=7)
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
-           "--master-port", str(29500 + fwd_path + (10 if cfg == "mid" else 20) + 40 * (n - 2) + (5 if mode == "column" else 0)), os.path.join(ROOT, "tests", "tp_worker.py"), cfg, path, str(fwd_path), mode]
+           "--master-port", str(29500 + fwd_path + (10 if cfg == "mid" else 20) + 40 * (n - 2) + (5 if mode == "column" else 0) + {"": 0, "synthetic": 100, "nccl": 200}[extra]),
+           os.path.join(ROOT, "tests", "tp_worker.py"), cfg, path, str(fwd_path), mode, extra]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert "ranks identical: True" in r.stdout
@@ -42,3 +46,15 @@ def test_tp2_column_mode(cfg, fwd_path, tmp_path):
 def test_tp4_logits_match_single_gpu_oracle(fwd_path, tmp_path):
     """Uneven row split: the 22 groups of the down projection fall 6, 6, 5, 5 on the four ranks."""
     _run_tp("mid", fwd_path, 4, tmp_path)
+
+
+def test_tp2_device_generated_shards(tmp_path):
+    """Shards generated on the device by each rank (q4_model_create_synthetic) form the same model as the packed file
+    of the same generator: TP2 logits against the single-GPU oracle run on that file."""
+    _run_tp("mid", 2, 2, tmp_path, extra="synthetic")
+
+
+@pytest.mark.parametrize("mode", ["hybrid", "column"])
+def test_tp2_nccl_backend(mode, tmp_path):
+    """The per-op paths with their collectives routed through NCCL (the reference's -DENABLE_NCCL build)."""
+    _run_tp("mid", 0, 2, tmp_path, mode=mode, extra="nccl")

@@ -18,12 +18,18 @@ from llama_cu_awq_b200.model import Transformer  # noqa: E402
 def main():
     cfg_name, path, fwd_path = sys.argv[1], sys.argv[2], int(sys.argv[3])
     tp_mode = _lib.Q4_TP_COLUMN if len(sys.argv) > 4 and sys.argv[4] == "column" else _lib.Q4_TP_HYBRID
+    synthetic = len(sys.argv) > 5 and sys.argv[5] == "synthetic"   # shards generated on the device; `path` holds the same model as a file
+    nccl = len(sys.argv) > 5 and sys.argv[5] == "nccl"             # per-op paths: collectives through NCCL instead of the peer push
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     comm = ProcessComm(rank, world, dist)
-    t = Transformer(path, rank=rank, gpu_count=world, tp_mode=tp_mode, comm=comm.handle)
+    if nccl:
+        comm.attach_nccl(dist)
+        comm.set_backend(_lib.Q4_COMM_BACKEND_NCCL)
+    t = Transformer(path, rank=rank, gpu_count=world, tp_mode=tp_mode, comm=comm.handle,
+                    synthetic=(synth.CONFIGS[cfg_name], 7) if synthetic else None)
     vocab = synth.CONFIGS[cfg_name][5]
     tokens = np.random.default_rng(0).integers(3, vocab, size=24, dtype=np.int32)
     t.reset(tokens, 0)
@@ -31,16 +37,29 @@ def main():
         assert t.best_path() == 2, "the fused path must serve this sharded model"
     dist.barrier()   # the fused path exchanges activations between the ranks' kernels: all ranks prepared before any launches
     torch.cuda.synchronize()
-    logits = []
-    for pos in range(len(tokens)):
-        t.forward(gen_token=False, path=fwd_path)
-        t.synchronize()
-        logits.append(t.logits())
-    assert t.status() == 0 and comm.status() == 0
+    def run(sync_every_token):
+        out = []
+        t.reset(tokens, 0)
+        dist.barrier()
+        for pos in range(len(tokens)):
+            t.forward(gen_token=False, path=fwd_path)
+            if sync_every_token or pos == len(tokens) - 1:
+                t.synchronize()
+                out.append(t.logits())
+        assert t.status() == 0 and comm.status() == 0
+        return out
+
+    logits = run(True)
+    # run-to-run reproducibility: a second pass with per-token waits and one queued without any (last position compared)
+    again, queued = run(True), run(False)
+    same = all((a.view(np.uint16) == b.view(np.uint16)).all() for a, b in zip(logits, again))
+    same = same and (queued[-1].view(np.uint16) == logits[-1].view(np.uint16)).all()
     mine = torch.from_numpy(np.stack(logits).view(np.int16).astype(np.int32)).cuda()
     gathered = [torch.empty_like(mine) for _ in range(world)]
     dist.all_gather(gathered, mine)
-    ok = 1
+    ok = 1 if same else 0
+    if not same:
+        print(f"rank {rank}: logits differ between two runs of the same sequence")
     if rank == 0:
         from oracle import q4_oracle as O
         for r in range(1, world):
