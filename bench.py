@@ -270,7 +270,7 @@ def op_kernels(cfg, torch):
     out = {}
     pk, _ = peaks()
     g = torch.Generator(device="cuda").manual_seed(0)
-    s = torch.cuda.current_stream()
+    s = torch.cuda.Stream()   # a stream of its own: the hook captures a CUDA graph, which the default stream does not allow
     for name, kind, K, N, nmat in kernel_shapes(cfg):
         pw, pz, gg = ((K + 31) // 32) * 4, ((K + 127) // 128 + 7) // 8, (K + 127) // 128
         keep, mats = [], (_lib.q4_qweight * nmat)()

@@ -122,6 +122,22 @@ int q4_attention_static(void* stream, uint16_t* output, const uint16_t* q, const
                         const uint16_t* value_cache, int num_heads, int head_size, int kv_mul, int max_seq_len,
                         const int* pPos);
 
+/* Batched form of matmul(QWeight) for prompt (prefill) and multi-sequence batches: Y[M][opSize] = X[M][inpSize] * deq(W),
+ * row m being what q4_matmul_q4 computes for x = X[m] (accum = 0). The reference has no such path: it pushes a prompt
+ * through the batch-1 kernel token by token (llama2_q4.cu:710-735); this is the dense contraction on the tensor cores
+ * (tcgen05.mma with TMEM accumulators, operands staged by TMA). inpSize must be a multiple of 128, opSize of 8; x, y
+ * row-major fp16, 16-byte aligned. `weight_interleaved` is either NULL (the packed words of `w` are used as they lie in
+ * the file) or a copy of w->weight made by q4_gemm_interleave_weights, which saves the kernel four byte permutes per
+ * packed word. `workspace` (device memory, 16-byte aligned, q4_matmul_q4_batched_workspace_bytes(M, inpSize, opSize) bytes,
+ * caller-owned, not shared between calls that overlap on the GPU) holds a status word, tile counters and the fp32
+ * partial sums of the K split. Asynchronous on `stream`; q4_matmul_q4_batched_status synchronises the stream and returns
+ * Q4_OK or the Q4_ERR_TIMEOUT a bounded device-side wait recorded. */
+size_t q4_matmul_q4_batched_workspace_bytes(int M, int inpSize, int opSize);
+int q4_gemm_interleave_weights(void* stream, uint32_t* dst, const uint32_t* weight, int inpSize, int opSize);
+int q4_matmul_q4_batched(void* stream, uint16_t* y, const uint16_t* x, const q4_qweight* w, const uint32_t* weight_interleaved,
+                         int M, int inpSize, int opSize, void* workspace, size_t workspace_bytes);
+int q4_matmul_q4_batched_status(void* stream, const void* workspace);
+
 /* matmul(half*): llama2_q4.cu:357-365, kernel gpu_kernels.h:117-147. fp16 GEMV used for the classifier:
  * xout[d] = alpha * sum_n w[d][n] * x[n]. n and d must be multiples of 8. */
 int q4_matmul_f16(void* stream, uint16_t* xout, const uint16_t* x, const uint16_t* w, int n, int d, float alpha);

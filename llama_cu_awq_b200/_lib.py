@@ -55,6 +55,10 @@ SIGNATURES = {
     "q4_build_arch": (C.c_char_p, []),
     "q4_rmsnorm": (_I, [_P, _P, _P, _P, _I]),
     "q4_matmul_q4": (_I, [_P, _P, _P, _QW, _I, _I, _I, _I, _I, _P]),
+    "q4_matmul_q4_batched_workspace_bytes": (C.c_size_t, [_I, _I, _I]),
+    "q4_gemm_interleave_weights": (_I, [_P, _P, _P, _I, _I]),
+    "q4_matmul_q4_batched": (_I, [_P, _P, _P, _QW, _P, _I, _I, _I, _P, C.c_size_t]),
+    "q4_matmul_q4_batched_status": (_I, [_P, _P]),
     "q4_qkv_matvec": (_I, [_P, _P, _P, _P, _P, _QW, _QW, _QW, _I, _I, _I, _I, _P]),
     "q4_ffn_matvec_silu": (_I, [_P, _P, _P, _QW, _QW, _I, _I]),
     "q4_rope": (_I, [_P, _P, _P, _I, _I, _I, _P, _I, C.c_float]),

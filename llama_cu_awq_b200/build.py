@@ -12,7 +12,7 @@ LIB = os.path.join(HERE, "libq4b200.so")
 CLI = os.path.join(HERE, "llama2_q4")
 TEST_LIB = os.path.join(HERE, "libq4b200_test.so")
 TEST_BUILD_SOURCES = ["q4_comm.cu", "q4_fused.cu"]   # the sources that look at Q4_TEST_BUILD
-LIB_SOURCES = ["q4_gemv.cu", "q4_ops.cu", "q4_attn.cu", "q4_comm.cu", "q4_model.cu", "q4_fused.cu", "q4_sampler.cu", "q4_synth.cu", "q4_tokenizer.cu"]
+LIB_SOURCES = ["q4_gemv.cu", "q4_ops.cu", "q4_attn.cu", "q4_comm.cu", "q4_model.cu", "q4_fused.cu", "q4_sampler.cu", "q4_synth.cu", "q4_tokenizer.cu", "q4_gemm.cu"]
 CLI_SOURCES = ["llama2_q4_main.cpp"]
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo"]
 

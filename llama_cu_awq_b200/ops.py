@@ -108,3 +108,26 @@ def unpack_nibbles(w, K, N, stream=None):
     z = torch.empty((N, G), dtype=torch.uint8, device=w.weight.device)
     check(_lib.lib().q4_unpack_nibbles(_stream(stream), _p(q), _p(z), w.ref, K, N), "unpack_nibbles")
     return q, z
+
+
+class BatchedMatmul:
+    """matmul(QWeight) for M rows at once (q4_matmul_q4_batched): the tcgen05 dequant-GEMM. Holds the workspace and,
+    with interleave=True, the re-ordered copy of the packed weights."""
+
+    def __init__(self, w, inpSize, opSize, max_rows, interleave=True):
+        L = _lib.lib()
+        self.w, self.K, self.N, self.max_rows = w, inpSize, opSize, max_rows
+        self.ws_bytes = max(L.q4_matmul_q4_batched_workspace_bytes(m, inpSize, opSize) for m in {1, 16, 17, 64, 65, max_rows})
+        self.ws = torch.zeros(self.ws_bytes, dtype=torch.uint8, device="cuda")
+        self.wi = None
+        if interleave:
+            self.wi = torch.empty_like(w.weight)
+            check(L.q4_gemm_interleave_weights(_stream(), _p(self.wi), _p(w.weight), inpSize, opSize), "interleave_weights")
+
+    def __call__(self, y, x, rows, stream=None):
+        assert rows <= self.max_rows
+        check(_lib.lib().q4_matmul_q4_batched(_stream(stream), _p(y), _p(x), self.w.ref, _p(self.wi), rows, self.K, self.N, _p(self.ws), self.ws_bytes),
+              "matmul_batched")
+
+    def status(self, stream=None):
+        return _lib.lib().q4_matmul_q4_batched_status(_stream(stream), _p(self.ws))
