@@ -296,6 +296,53 @@ def op_kernels(cfg, torch):
     return out
 
 
+def gemm_table(torch):
+    """The batched / prefill W4 dequant-GEMM (tcgen05) at M = 16, 64, 512 on the four 7B projection shapes, over distinct
+    weight matrices: against the HBM roofline (algorithmic bytes) and against the measured sustained bf16 tensor rate."""
+    from llama_cu_awq_b200 import _lib
+    L = _lib.lib()
+    pk, _ = peaks()
+    g = torch.Generator(device="cuda").manual_seed(1)
+    s = torch.cuda.Stream()
+    out = {}
+    for name, K, N, nmat in (("qkv_4096x12288", 4096, 12288, 6), ("gate_up_4096x22016", 4096, 22016, 4), ("down_11008x4096", 11008, 4096, 6),
+                             ("o_4096x4096", 4096, 4096, 16)):
+        pw, pz, gg = K // 8, ((K + 127) // 128 + 7) // 8, (K + 127) // 128
+        keep, mats, wil = [], (_lib.q4_qweight * nmat)(), (C.c_void_p * nmat)()
+        for i in range(nmat):
+            w = torch.randint(-2**31, 2**31 - 1, (N, pw), dtype=torch.int32, device="cuda", generator=g)
+            z = torch.randint(-2**31, 2**31 - 1, (N, pz), dtype=torch.int32, device="cuda", generator=g)
+            sc = (torch.rand((N, gg), device="cuda", generator=g) * 0.018 + 0.002).half()
+            wi = torch.empty_like(w)
+            L.q4_gemm_interleave_weights(C.c_void_p(s.cuda_stream), C.c_void_p(wi.data_ptr()), C.c_void_p(w.data_ptr()), K, N)
+            keep += [w, z, sc, wi]
+            mats[i] = _lib.q4_qweight(w.data_ptr(), z.data_ptr(), sc.data_ptr())
+            wil[i] = wi.data_ptr()
+        wbytes = N * (pw * 4 + pz * 4 + gg * 2)
+        for M in (16, 64, 512):
+            x = torch.randn((M, K), device="cuda", generator=g).half()
+            y = torch.zeros((M, N), dtype=torch.float16, device="cuda")
+            nws = L.q4_matmul_q4_batched_workspace_bytes(M, K, N)
+            ws = torch.zeros(nws, dtype=torch.uint8, device="cuda")
+            us = C.c_double()
+            torch.cuda.synchronize()
+            st = L.q4_time_matmul_q4_batched(C.c_void_p(s.cuda_stream), C.c_void_p(y.data_ptr()), C.c_void_p(x.data_ptr()), mats, wil, nmat, M, K, N,
+                                             C.c_void_p(ws.data_ptr()), nws, 10, C.byref(us))
+            if st == 0:
+                st = L.q4_matmul_q4_batched_status(C.c_void_p(s.cuda_stream), C.c_void_p(ws.data_ptr()))
+            if st != 0:   # a device-side wait ran out: every further launch would cost the wait limit again
+                out[f"{name}_M{M}"] = {"error": st}
+                return out
+            nbytes = wbytes + 2 * M * K + 2 * M * N
+            tflops = 2.0 * M * K * N / (us.value * 1e-6) / 1e12
+            gbs = nbytes / (us.value * 1e-6) / 1e9
+            out[f"{name}_M{M}"] = {"us": us.value, "gbs": gbs, "frac_of_hbm_peak": gbs / pk["hbm_gbs"], "tflops": tflops,
+                                   "frac_of_bf16_sustained": tflops / pk.get("bf16_tflops_sustained", pk["bf16_tflops"]),
+                                   "bound": "tensor" if M >= 512 else "hbm", "distinct_matrices": nmat}
+        del keep
+    return out
+
+
 def allreduce_table(comm, dist, torch):
     """Microseconds per in-place fp16 all-reduce of one model vector (8, 10, 16 KB) and of 64 KB: peer push vs NCCL."""
     from llama_cu_awq_b200 import _lib
@@ -482,6 +529,7 @@ def main():
     extra = {}
     if world == 1 and not args.no_extras:
         extra["kernels"] = op_kernels(cfg, torch)
+        extra["gemm_tcgen05"] = gemm_table(torch)
     if fwd_path == 2:
         launches_per_token = 1  # one persistent cooperative kernel per token
         roof = {"bound": "hbm", "kernel": "fused_token_kernel (whole token: W4 GEMVs, attention, classifier)",

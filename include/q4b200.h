@@ -130,13 +130,18 @@ int q4_attention_static(void* stream, uint16_t* output, const uint16_t* q, const
  * the file) or a copy of w->weight made by q4_gemm_interleave_weights, which saves the kernel four byte permutes per
  * packed word. `workspace` (device memory, 16-byte aligned, q4_matmul_q4_batched_workspace_bytes(M, inpSize, opSize) bytes,
  * caller-owned, not shared between calls that overlap on the GPU) holds a status word, tile counters and the fp32
- * partial sums of the K split. Asynchronous on `stream`; q4_matmul_q4_batched_status synchronises the stream and returns
+ * partial sums of the K split; zero it once before the first call (and again after a reported time-out). Asynchronous on `stream`; q4_matmul_q4_batched_status synchronises the stream and returns
  * Q4_OK or the Q4_ERR_TIMEOUT a bounded device-side wait recorded. */
 size_t q4_matmul_q4_batched_workspace_bytes(int M, int inpSize, int opSize);
 int q4_gemm_interleave_weights(void* stream, uint32_t* dst, const uint32_t* weight, int inpSize, int opSize);
 int q4_matmul_q4_batched(void* stream, uint16_t* y, const uint16_t* x, const q4_qweight* w, const uint32_t* weight_interleaved,
                          int M, int inpSize, int opSize, void* workspace, size_t workspace_bytes);
 int q4_matmul_q4_batched_status(void* stream, const void* workspace);
+/* Measurement hook: q4_matmul_q4_batched over `nmat` distinct weight matrices of one shape (interleaved[i] may be NULL
+ * or the array itself NULL), captured as one CUDA graph and replayed `reps` times between two events on `stream`. */
+int q4_time_matmul_q4_batched(void* stream, uint16_t* y, const uint16_t* x, const q4_qweight* mats,
+                              const uint32_t* const* interleaved, int nmat, int M, int inpSize, int opSize, void* workspace,
+                              size_t workspace_bytes, int reps, double* us_per_launch);
 
 /* matmul(half*): llama2_q4.cu:357-365, kernel gpu_kernels.h:117-147. fp16 GEMV used for the classifier:
  * xout[d] = alpha * sum_n w[d][n] * x[n]. n and d must be multiples of 8. */

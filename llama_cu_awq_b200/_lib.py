@@ -59,6 +59,7 @@ SIGNATURES = {
     "q4_gemm_interleave_weights": (_I, [_P, _P, _P, _I, _I]),
     "q4_matmul_q4_batched": (_I, [_P, _P, _P, _QW, _P, _I, _I, _I, _P, C.c_size_t]),
     "q4_matmul_q4_batched_status": (_I, [_P, _P]),
+    "q4_time_matmul_q4_batched": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, C.c_size_t, _I, C.POINTER(C.c_double)]),
     "q4_qkv_matvec": (_I, [_P, _P, _P, _P, _P, _QW, _QW, _QW, _I, _I, _I, _I, _P]),
     "q4_ffn_matvec_silu": (_I, [_P, _P, _P, _QW, _QW, _I, _I]),
     "q4_rope": (_I, [_P, _P, _P, _I, _I, _I, _P, _I, C.c_float]),
@@ -126,6 +127,7 @@ TEST_SIGNATURES = {
     "q4_test_fail_fused_alloc": (None, [_I]),
     "q4_test_comm_set_peer": (_I, [_P, _I, _P]),
     "q4_test_fused_gemv": (_I, [_P, _P, _P, _QW, _I, _I]),
+    "q4_test_model_slot_trace": (_I, [_P, _P]),
 }
 
 _lib = None

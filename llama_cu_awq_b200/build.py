@@ -11,6 +11,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libq4b200.so")
 CLI = os.path.join(HERE, "llama2_q4")
 TEST_LIB = os.path.join(HERE, "libq4b200_test.so")
+PACKER = os.path.join(HERE, "weight_packer")   # offline tool, host code only
 TEST_BUILD_SOURCES = ["q4_comm.cu", "q4_fused.cu"]   # the sources that look at Q4_TEST_BUILD
 LIB_SOURCES = ["q4_gemv.cu", "q4_ops.cu", "q4_attn.cu", "q4_comm.cu", "q4_model.cu", "q4_fused.cu", "q4_sampler.cu", "q4_synth.cu", "q4_tokenizer.cu", "q4_gemm.cu"]
 CLI_SOURCES = ["llama2_q4_main.cpp"]
@@ -67,6 +68,9 @@ def build(force=False, verbose=False, test=True):
     if all(os.path.exists(s) for s in cli_srcs) and (force or _newer(CLI, deps + [LIB])):
         cmd = [nvcc] + NVCC_FLAGS + ["-o", CLI] + cli_srcs + [LIB, "-Xlinker", "-rpath=$ORIGIN", "-lpthread"]
         subprocess.run(cmd, check=True)
+    packer_src = os.path.join(CSRC, "weight_packer.cpp")
+    if os.path.exists(packer_src) and (force or _newer(PACKER, [packer_src])):
+        subprocess.run([os.environ.get("CXX", "g++"), "-O2", "-std=c++17", "-o", PACKER, packer_src], check=True)
     return LIB
 
 

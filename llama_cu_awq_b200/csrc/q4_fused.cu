@@ -159,7 +159,8 @@ struct FParams {
     unsigned long long wait_ns;  // limit of every device-side wait on the global timer; on expiry the kernel records Q4_ERR_TIMEOUT
     int n_entries;               // ring entries of kEntryBytes each
     int split_len;               // positions per attention split (a head is split in ceil(T / split_len) parts, at most nsplit)
-    unsigned long long* trace;   // optional: [2 CTAs][nphases][4] device timestamps (ns), or null
+    unsigned long long* trace;   // optional: [2 CTAs][nphases][8] device timestamps (ns), or null
+    unsigned long long* slot_trace;  // test build: [nphases][kCW][kSlotTraceSlots][4] stamps of CTA 0, or null
     // shared memory carve-up (bytes)
     int xq_bytes, meta_off, part_off, part_floats;
 };
@@ -266,6 +267,19 @@ __device__ __forceinline__ void grid_barrier(const FParams& p, unsigned& nbar, i
         if (p.trace && ctid == 0 && (cta == 0 || cta == grid - 1))                                           \
             p.trace[((size_t)(cta == 0 ? 0 : 1) * p.nphases + pi) * kTraceCols + (k)] = global_ns();                  \
     } while (0)
+
+// Test build: per-slot clock stamps of CTA 0 (lane 0 of every consumer warp, first kSlotTraceSlots slots of every GEMV
+// phase): 0 before the wait for the slot's weights, 1 after it, 2 after the math, 3 after finishing a unit.
+constexpr int kSlotTraceSlots = 6;
+#ifdef Q4_TEST_BUILD
+#define SLOT_TRACE(k)                                                                                                      \
+    do {                                                                                                                   \
+        if (p.slot_trace && cta == 0 && lane == 0 && (int)((li - first) / kCW) < kSlotTraceSlots)                           \
+            p.slot_trace[(((size_t)pi * kCW + cw) * kSlotTraceSlots + (li - first) / kCW) * 4 + (k)] = global_ns();         \
+    } while (0)
+#else
+#define SLOT_TRACE(k) do {} while (0)
+#endif
 
 __device__ __forceinline__ float silu_mul(float g, float u) {
     float val = g;
@@ -1105,9 +1119,12 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                 const int eq = fast_div(en, inv_entries), e = (int)en - eq * kEntries;
                 int off = 0;
                 if (li & 1) { const int ktp = kt > 0 ? kt - 1 : nkt - 1; off = min(kSlotGroups, G - ktp * kSlotGroups) * kUnitBytes; }
+                SLOT_TRACE(0);
                 if (!(dbg & 2) && (failed || !mbar_wait(&full_bar[e], eq & 1, p.status, p.wait_ns, &s_round[e], (unsigned)eq))) { failed = true; continue; }
+                SLOT_TRACE(1);
                 if (!(dbg & 1)) gemv_slot(ring + (size_t)e * kEntryBytes + off, ng, kt, xq, xs_scale, xs_sum, part + (size_t)li * 8, lane);
                 __syncwarp();
+                SLOT_TRACE(2);
                 const int ul = fast_div(li, inv_spu);
                 // One arrive instruction, two lanes: lane 0 releases the ring entry (an entry is released by its two slots;
                 // a phase's odd last slot releases it alone), lane 1 counts the slot in for its unit (release: the slot's
@@ -1201,17 +1218,14 @@ __global__ void __launch_bounds__(kThreads, 1) fused_token_kernel(const FParams 
                         if (m.out_plain) m.out_plain[ph.loff + (long long)pos * m.n + n] = hv;   // V row into the cache for later tokens
                     }
                 }
+                SLOT_TRACE(3);
             }
             sbase += nslots;
             ent0 += (nslots + 1) >> 1;
             TRACE(2);
             phase_fetch_wait();
-            if (p.trace && cta == 0 && lane == 0 && (cw == 0 || cw == kCW - 1))
-                p.trace[(size_t)2 * p.nphases * kTraceCols + (size_t)pi * 16 + (cw == 0 ? 11 : 13)] = global_ns();
             if (ph.barrier_after) grid_barrier(p, nbar, ctid, &s_abort);
             else consumer_sync();  // closes the phase
-            if (p.trace && cta == 0 && lane == 0 && (cw == 0 || cw == kCW - 1))
-                p.trace[(size_t)2 * p.nphases * kTraceCols + (size_t)pi * 16 + (cw == 0 ? 12 : 14)] = global_ns();
             TRACE(3);
 
         } else if (ph.type == PH_ATTN) {
@@ -1660,6 +1674,7 @@ struct q4_fused {
     unsigned long long launches = 0;
     bool unsupported = false;
     unsigned long long* trace = nullptr;
+    unsigned long long* slot_trace = nullptr;
     Q4LLArea* ll_local = nullptr;   // this rank's exchange area (inside the communicator's inbox, or own allocation at g = 1)
     size_t attn_part_bytes = 0;
     bool armed = false;             // buffers and counters are in their initial state or in step with the launches so far
@@ -2053,6 +2068,7 @@ int q4_fused_forward(q4_model* m, cudaStream_t s, int gen_token, int no_handoff)
     p.write_token = gen_token;
     p.no_handoff = no_handoff;
     p.trace = f->trace;
+    p.slot_trace = f->slot_trace;
     p.debug = 0;
     p.split_len = kSplitLen;
     p.wait_ns = f->wait_ns;
@@ -2129,6 +2145,20 @@ extern "C" int q4_test_fused_gemv(void* stream, uint16_t* y, const uint16_t* x, 
     cudaFree(blocks);
     Q4_CUDA_TRY(e);
     return Q4_OK;
+}
+// Test build only: arms (first call) and reads back (later calls) the per-slot stamps of CTA 0; returns the phase count.
+extern "C" int q4_test_model_slot_trace(q4_model* m, unsigned long long* out) {
+    if (!m) return Q4_ERR_INVALID;
+    if (int e = q4_fused_prepare(m)) return e;
+    q4_fused* f = m->fused;
+    const size_t n = (size_t)f->nphases * kCW * kSlotTraceSlots * 4;
+    if (!f->slot_trace) {
+        if (int e = fused_alloc(f, (void**)&f->slot_trace, n * sizeof(unsigned long long))) return e;
+        Q4_CUDA_TRY(cudaMemset(f->slot_trace, 0, n * sizeof(unsigned long long)));
+    }
+    Q4_CUDA_TRY(cudaDeviceSynchronize());
+    if (out) Q4_CUDA_TRY(cudaMemcpy(out, f->slot_trace, n * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+    return f->nphases;
 }
 #endif  // Q4_TEST_BUILD
 

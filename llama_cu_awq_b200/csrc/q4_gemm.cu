@@ -8,12 +8,13 @@
 // (16, 64 or 256 rows of X per tile), so small batches still use whole instructions: D[128 x MT] += A[128 x 16] * B[MT x 16]^T.
 //
 // One CTA per SM, persistent over work units (feature tile, batch tile, K split), four roles:
-//   warp 0      producer: TMA (cp.async.bulk.tensor.2d, no multicast, this GPU's memory only) of packed weight chunks
-//               (128 features x 256 inputs = 128 B per row, 128-byte swizzle) into a staging ring and of X tiles
-//               (MT x 64, 128-byte swizzle) straight into the B operand ring
-//   warps 2-9   converters: read the packed nibbles from the staging ring (conflict free thanks to the swizzle), dequantise
-//               to fp16 in registers (LOP3 magic-number unpack, one exact subtract, one rounding multiply) and store them
-//               into the A operand ring in the K-major 128-byte-swizzled layout the MMA descriptors describe
+//   warp 0      weight producer: TMA (cp.async.bulk.tensor.2d, no multicast, this GPU's memory only) of packed weight chunks
+//               (128 features x 256 inputs = 128 B per row, 128-byte swizzle) into a staging ring
+//   warp 14     X producer: TMA of X tiles (MT x 64, 128-byte swizzle) straight into the (deep) B operand ring
+//   warps 2-9   converters: a warp takes every eighth 64-input block, reads its nibbles from the staging ring (conflict free
+//               thanks to the swizzle), dequantises them to fp16 in registers (LOP3 magic-number unpack, one exact
+//               subtract, one rounding multiply) and stores them into its own A operand stage in the K-major
+//               128-byte-swizzled layout the MMA descriptors describe
 //   warp 1      MMA: one elected thread issues tcgen05.mma.cta_group::1.kind::f16 (4 per 64-input stage) into a TMEM
 //               accumulator and tcgen05.commit's the stage back to the producer / converters
 //   warps 10-13 epilogue: tcgen05.ld the accumulator (lane = feature, column = batch row), convert, store
@@ -36,19 +37,29 @@ constexpr int kBK = 64;         // inputs per pipeline stage (one 128-byte swizz
 constexpr int kChunkK = 256;    // inputs per packed-weight copy: 32 words = 128 B per feature row
 constexpr int kKbPerChunk = kChunkK / kBK;
 constexpr int kConvWarps = 8, kEpiWarps = 4;
-constexpr int kFirstConvWarp = 2, kFirstEpiWarp = kFirstConvWarp + kConvWarps;
-constexpr int kGemmThreads = (kFirstEpiWarp + kEpiWarps) * 32;   // 448
+constexpr int kFirstConvWarp = 2, kFirstEpiWarp = kFirstConvWarp + kConvWarps;   // epilogue warps 10..13: warp % 4 covers the four TMEM lane quarters
+constexpr int kXWarp = kFirstEpiWarp + kEpiWarps;                // 14: X-tile producer
+constexpr int kGemmThreads = (kXWarp + 1) * 32;                  // 480
 constexpr int kAStageBytes = kBN * kBK * 2;                      // 16 KB
 constexpr int kPStageBytes = kBN * (kChunkK / 8) * 4;            // 16 KB
-constexpr unsigned long long kGemmWaitNs = 2000ULL * 1000 * 1000;
-constexpr int kMaxStages = 4;
+constexpr unsigned long long kGemmWaitNs = 300ULL * 1000 * 1000;   // limit of every device-side wait
+constexpr int kMaxStages = 16;
 
 template <int MT> struct GemmCfg {
-    static constexpr int kStages = MT >= 256 ? 3 : 4;            // A/B operand stages
-    static constexpr int kPStages = MT >= 256 ? 2 : 3;           // packed-weight staging
+    // Converter warps = A operand stages (each warp owns one 16 KB stage). What is left of the 227 KB goes to the two rings
+    // that hide memory latency: X tiles (MT x 128 B each, from L2, about a microsecond) and packed-weight chunks (16 KB
+    // each, from HBM, about two microseconds); the converters hold up to kConverters blocks more in registers. The staging
+    // ring has an even length, so that a slot always serves the same four converter warps.
+    //              A stages     X ring          weight staging
+    //   MT = 16    8 (128 KB)   16 (32 KB)      4 (64 KB)
+    //   MT = 64    4 (64 KB)     8 (64 KB)      6 (96 KB)
+    //   MT = 256   4 (64 KB)     4 (128 KB)     2 (32 KB)    (bound by the tensor pipe, not by the conversion)
+    static constexpr int kConverters = MT <= 16 ? 8 : 4;
+    static constexpr int kBStages = MT >= 256 ? 4 : MT >= 64 ? 8 : 16;
+    static constexpr int kPStages = MT >= 256 ? 2 : MT >= 64 ? 6 : 4;
     static constexpr int kBStageBytes = MT * kBK * 2;
-    static constexpr int kTmemCols = MT < 32 ? 32 : MT;          // power of two >= 32
-    static constexpr size_t kSmemBytes = (size_t)kStages * (kAStageBytes + kBStageBytes) + (size_t)kPStages * kPStageBytes + 1024;
+    static constexpr int kTmemCols = MT < 32 ? 32 : MT;                    // power of two >= 32
+    static constexpr size_t kSmemBytes = (size_t)kConverters * kAStageBytes + (size_t)kBStages * kBStageBytes + (size_t)kPStages * kPStageBytes + 1024;
 };
 
 struct GemmParams {
@@ -161,27 +172,32 @@ __device__ __forceinline__ UnitInfo unit_info(const GemmParams& p, int u) {
     i.c1 = (int)((long long)p.n_chunks * (i.split + 1) / p.splits);
     return i;
 }
-__device__ __forceinline__ int kb_in_chunk(const GemmParams& p, int c) { return min(kKbPerChunk, (p.K - c * kChunkK + kBK - 1) / kBK); }
 
+// Every chunk is processed as four 64-input blocks, also the last chunk of a K that is not a multiple of 256: TMA fills
+// what lies outside the tensors with zeros on both operands, so the extra blocks add nothing. That keeps the pipeline
+// regular: block q of a CTA (counted over all its units) is converted by converter warp q % NC into operand stage
+// q % NC, which that warp alone ever fills - every barrier is then waited on by one party, phase after phase without
+// gaps (a parity wait cannot tell phase k from phase k + 2).
 template <int MT, bool INTERLEAVED>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 q4_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const GemmParams p) {
     using Cfg = GemmCfg<MT>;
-    constexpr int NS = Cfg::kStages, NP = Cfg::kPStages;
+    constexpr int NC = Cfg::kConverters, NP = Cfg::kPStages, NB = Cfg::kBStages;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* sA = smem;
-    uint8_t* sB = sA + (size_t)NS * kAStageBytes;
-    uint8_t* sP = sB + (size_t)NS * Cfg::kBStageBytes;
-    __shared__ uint64_t full_p[kMaxStages], empty_p[kMaxStages], full_a[kMaxStages], full_b[kMaxStages], empty_ab[kMaxStages], tmem_full, tmem_empty;
+    uint8_t* sB = sA + (size_t)NC * kAStageBytes;
+    uint8_t* sP = sB + (size_t)NB * Cfg::kBStageBytes;
+    __shared__ uint64_t full_p[kMaxStages], empty_p[kMaxStages], full_a[kMaxStages], empty_a[kMaxStages], full_b[kMaxStages], empty_b[kMaxStages], tmem_full,
+        tmem_empty;
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_last;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
         for (int s = 0; s < kMaxStages; s++) {
-            mb_init(&full_p[s], 1); mb_init(&empty_p[s], kConvWarps);
-            mb_init(&full_a[s], kConvWarps); mb_init(&full_b[s], 1); mb_init(&empty_ab[s], 1);
+            mb_init(&full_p[s], 1); mb_init(&empty_p[s], kKbPerChunk);   // a chunk's four blocks go to four converter warps
+            mb_init(&full_a[s], 1); mb_init(&empty_a[s], 1); mb_init(&full_b[s], 1); mb_init(&empty_b[s], 1);
         }
         mb_init(&tmem_full, 1);
         mb_init(&tmem_empty, kEpiWarps);
@@ -195,136 +211,159 @@ q4_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *(volatile uint32_t*)&s_tmem_base;
+    // everything above overlaps the tail of the previous kernel on the stream (programmatic dependent launch); from here
+    // on this kernel reads what that kernel wrote
+    griddep_wait();
+    griddep_launch_dependents();
 
     if (warp == 0) {
-        // ===================== producer =====================
+        // ===================== weight producer =====================
+        // keeps the packed-weight staging ring full: it waits only for free staging slots, so it runs ahead of the math and
+        // across unit boundaries
         if (lane == 0) {
-            unsigned pit = 0, sit = 0;   // packed chunks and operand stages issued so far
+            unsigned pit = 0;
             bool ok = true;
             for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
                 const UnitInfo ui = unit_info(p, u);
-                for (int c = ui.c0; c < ui.c1 && ok; c++) {
+                for (int c = ui.c0; c < ui.c1; c++, pit++) {
                     const int ps = pit % NP;
                     if (!mb_wait(&empty_p[ps], ((pit / NP) & 1) ^ 1, p.status, 0x100)) { ok = false; break; }
                     mb_expect_tx(&full_p[ps], kPStageBytes);
                     tma_load_2d(sP + (size_t)ps * kPStageBytes, &map_w, c * (kChunkK / 8), ui.tile * kBN, &full_p[ps]);
-                    pit++;
-                    const int nkb = kb_in_chunk(p, c);
-                    for (int kbl = 0; kbl < nkb; kbl++) {
-                        const int s = sit % NS;
-                        if (!mb_wait(&empty_ab[s], ((sit / NS) & 1) ^ 1, p.status, 0x200)) { ok = false; break; }
-                        mb_expect_tx(&full_b[s], Cfg::kBStageBytes);
-                        tma_load_2d(sB + (size_t)s * Cfg::kBStageBytes, &map_x, (c * kKbPerChunk + kbl) * kBK, ui.mt * MT, &full_b[s]);
-                        sit++;
-                    }
                 }
             }
-            if (!ok) {
-                // after an error the newest copy of every ring position may still be in flight: give each up to 50 ms
+            if (!ok) {   // after an error the newest copy of every ring position may still be in flight: give each up to 50 ms
                 for (unsigned i = pit > (unsigned)NP ? pit - NP : 0; i < pit; i++) {
                     const unsigned long long t0 = gtimer();
                     while (!mb_try(&full_p[i % NP], (i / NP) & 1) && gtimer() - t0 < 50ULL * 1000 * 1000) {}
                 }
-                for (unsigned i = sit > (unsigned)NS ? sit - NS : 0; i < sit; i++) {
+            }
+        }
+    } else if (warp == kXWarp) {
+        // ===================== X producer =====================
+        // loads the X tile of every 64-input block as soon as the MMA has released that slot of the (deep) B ring
+        if (lane == 0) {
+            unsigned q = 0;
+            bool ok = true;
+            for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
+                const UnitInfo ui = unit_info(p, u);
+                for (int kb = ui.c0 * kKbPerChunk; kb < ui.c1 * kKbPerChunk; kb++, q++) {
+                    const int s = q % NB;
+                    if (!mb_wait(&empty_b[s], ((q / NB) & 1) ^ 1, p.status, 0x200)) { ok = false; break; }
+                    mb_expect_tx(&full_b[s], Cfg::kBStageBytes);
+                    tma_load_2d(sB + (size_t)s * Cfg::kBStageBytes, &map_x, kb * kBK, ui.mt * MT, &full_b[s]);
+                }
+            }
+            if (!ok) {
+                for (unsigned i = q > (unsigned)NB ? q - NB : 0; i < q; i++) {
                     const unsigned long long t0 = gtimer();
-                    while (!mb_try(&full_b[i % NS], (i / NS) & 1) && gtimer() - t0 < 50ULL * 1000 * 1000) {}
+                    while (!mb_try(&full_b[i % NB], (i / NB) & 1) && gtimer() - t0 < 50ULL * 1000 * 1000) {}
                 }
             }
         }
     } else if (warp == 1) {
         // ===================== MMA issuer =====================
-        constexpr uint32_t idesc = umma_idesc(MT);
-        unsigned sit = 0, uit = 0;
-        bool ok = true;
-        for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x, uit++) {
-            const UnitInfo ui = unit_info(p, u);
-            if (!mb_wait(&tmem_empty, (uit & 1) ^ 1, p.status, 0x300)) { ok = false; break; }   // the epilogue has drained the accumulator
-            tc_fence_after();
-            bool first = true;
-            for (int c = ui.c0; c < ui.c1 && ok; c++) {
-                const int nkb = kb_in_chunk(p, c);
-                for (int kbl = 0; kbl < nkb; kbl++) {
-                    const int s = sit % NS;
-                    const uint32_t par = (sit / NS) & 1;
-                    if (!mb_wait(&full_a[s], par, p.status, 0x400) || !mb_wait(&full_b[s], par, p.status, 0x500)) { ok = false; break; }
+        // one thread does it all: the instructions are asynchronous, and at small batch tiles their issue rate is what
+        // bounds the kernel, so nothing else shares this warp's issue slots
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc(MT);
+            const uint64_t adesc0 = umma_desc(smem_addr(sA)), bdesc0 = umma_desc(smem_addr(sB));
+            unsigned q = 0, uit = 0;
+            bool ok = true;
+            for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x, uit++) {
+                const UnitInfo ui = unit_info(p, u);
+                if (!mb_wait(&tmem_empty, (uit & 1) ^ 1, p.status, 0x300)) { ok = false; break; }   // the epilogue has drained the accumulator
+                const int nkb = (ui.c1 - ui.c0) * kKbPerChunk;
+                for (int i = 0; i < nkb; i++, q++) {
+                    const int s = q % NC, sb = q % NB;
+                    if (!mb_wait(&full_a[s], (q / NC) & 1, p.status, 0x400) || !mb_wait(&full_b[sb], (q / NB) & 1, p.status, 0x500)) { ok = false; break; }
                     tc_fence_after();
-                    if (lane == 0) {
-                        const uint64_t ad = umma_desc(smem_addr(sA + (size_t)s * kAStageBytes));
-                        const uint64_t bd = umma_desc(smem_addr(sB + (size_t)s * Cfg::kBStageBytes));
+                    const uint64_t ad = adesc0 + (uint64_t)((s * kAStageBytes) >> 4), bd = bdesc0 + (uint64_t)((sb * Cfg::kBStageBytes) >> 4);
 #pragma unroll
-                        for (int k16 = 0; k16 < kBK / 16; k16++)
-                            tc_mma_f16(tmem_base, ad + 2 * k16, bd + 2 * k16, idesc, (first && k16 == 0) ? 0u : 1u);
-                        tc_commit(&empty_ab[s]);   // arrives when these MMAs have read their operands
-                    }
-                    __syncwarp();
-                    first = false;
-                    sit++;
+                    for (int k16 = 0; k16 < kBK / 16; k16++) tc_mma_f16(tmem_base, ad + 2 * k16, bd + 2 * k16, idesc, (i == 0 && k16 == 0) ? 0u : 1u);
+                    tc_commit(&empty_a[s]);    // both arrive when these MMAs have read their operands
+                    tc_commit(&empty_b[sb]);
                 }
+                tc_commit(&tmem_full);
             }
-            if (lane == 0) tc_commit(&tmem_full);
-            __syncwarp();
         }
     } else if (warp < kFirstEpiWarp) {
         // ===================== converters =====================
+        // Warp w converts blocks q = w, w + NC, ...: a whole 128-feature x 64-input operand stage per block, four feature
+        // rows per lane, so that the fixed cost of a hand-over (barrier round trips, store drain) is paid once per 8192
+        // weights and NC blocks are in flight at once.
         const int cw = warp - kFirstConvWarp;
-        const int r = (cw & 3) * 32 + lane, hf = cw >> 2;   // feature row inside the tile; which 32 of the stage's 64 inputs
-        const int sw = r & 7;
-        unsigned pit = 0, sit = 0;
-        bool ok = true;
-        for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
-            const UnitInfo ui = unit_info(p, u);
-            const int n = ui.tile * kBN + r;
-            const bool valid = n < p.N;
-            // zero points and scales of a chunk's two groups are requested one chunk ahead, so that their latency is
-            // hidden behind the wait for the chunk's nibbles
-            uint32_t zw_next = 0;
-            __half sc_next[2] = {__float2half(0.f), __float2half(0.f)};
-            auto fetch_meta = [&](int c) {
-                const int g0 = c * 2;
-                if (valid && g0 < p.G) {
-                    zw_next = __ldg(p.zeros + (size_t)n * p.PZ + (g0 >> 3)) >> (4 * (g0 & 7));   // g0 is even: both nibbles are in this word
-                    sc_next[0] = __ldg(p.scales + (size_t)n * p.G + g0);
-                    sc_next[1] = g0 + 1 < p.G ? __ldg(p.scales + (size_t)n * p.G + g0 + 1) : __float2half(0.f);
+        if (cw < NC) {
+            const int sw = lane & 7;   // rows lane + 32 i share lane & 7, hence the swizzle term
+            bool ok = true;
+            unsigned q = 0;            // first block of the current unit
+            // zero points and scales of this warp's next block, requested one block of its own ahead
+            uint32_t z_next[4] = {0, 0, 0, 0};
+            __half s_next[4];
+            auto fetch_meta = [&](int tile, int kb) {
+                const int g = kb >> 1;
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int n = tile * kBN + lane + 32 * i;
+                    z_next[i] = 0;
+                    s_next[i] = __float2half(0.f);
+                    if (n < p.N && g < p.G) {
+                        z_next[i] = (__ldg(p.zeros + (size_t)n * p.PZ + (g >> 3)) >> (4 * (g & 7))) & 0xFu;
+                        s_next[i] = __ldg(p.scales + (size_t)n * p.G + g);
+                    }
                 }
             };
-            fetch_meta(ui.c0);
-            for (int c = ui.c0; c < ui.c1 && ok; c++) {
-                const uint32_t zw = zw_next;
-                const __half sc[2] = {sc_next[0], sc_next[1]};
-                if (c + 1 < ui.c1) fetch_meta(c + 1);
-                const int ps = pit % NP;
-                if (!mb_wait(&full_p[ps], (pit / NP) & 1, p.status, 0x600)) { ok = false; break; }
-                const uint8_t* prow = sP + (size_t)ps * kPStageBytes + r * 128;
-                const int nkb = kb_in_chunk(p, c);
-                for (int kbl = 0; kbl < nkb; kbl++) {
-                    const int gl = kbl >> 1;   // which of the chunk's two groups of 128 inputs
-                    uint32_t zlo, zhi;
-                    zero_consts((zw >> (4 * gl)) & 0xFu, zlo, zhi);
-                    const __half2 s2 = __half2half2(sc[gl]);
-                    const int s = sit % NS;
-                    const uint4 pk = *reinterpret_cast<const uint4*>(prow + (((kbl * 2 + hf) ^ sw) << 4));
-                    if (!mb_wait(&empty_ab[s], ((sit / NS) & 1) ^ 1, p.status, 0x700)) { ok = false; break; }
-                    uint8_t* arow = sA + (size_t)s * kAStageBytes + (r >> 3) * 1024 + sw * 128;
-                    const uint32_t words[4] = {pk.x, pk.y, pk.z, pk.w};
+            bool have_meta = false;
+            for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x) {
+                const UnitInfo ui = unit_info(p, u);
+                const unsigned nkb = (unsigned)(ui.c1 - ui.c0) * kKbPerChunk;
+                // this warp's first block of the unit
+                unsigned i = (cw + NC - (q % NC)) % NC;
+                if (!have_meta && i < nkb) fetch_meta(ui.tile, ui.c0 * kKbPerChunk + i);
+                for (; i < nkb && ok; i += NC) {
+                    const unsigned qi = q + i;                      // this block's number: stage qi % NC == cw
+                    const int kb = ui.c0 * kKbPerChunk + (int)i;    // 64-input block inside K
+                    const unsigned pit = qi / kKbPerChunk;          // chunk number (chunks are four blocks, always)
+                    const int kbl = qi % kKbPerChunk, ps = pit % NP;
+                    uint32_t zz[4];
+                    __half ss[4];
 #pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        const uint4 o = valid ? dequant8<INTERLEAVED>(words[j], zlo, zhi, s2) : make_uint4(0, 0, 0, 0);
-                        *reinterpret_cast<uint4*>(arow + (((hf * 4 + j) ^ sw) << 4)) = o;
+                    for (int r4 = 0; r4 < 4; r4++) { zz[r4] = z_next[r4]; ss[r4] = s_next[r4]; }
+                    have_meta = false;
+                    if (i + NC < nkb) { fetch_meta(ui.tile, kb + NC); have_meta = true; }
+                    if (!mb_wait(&full_p[ps], (pit / NP) & 1, p.status, 0x600)) { ok = false; break; }
+                    uint4 pk[8];   // rows lane + 32 r4, the block's two 16-byte pieces of each row
+#pragma unroll
+                    for (int r4 = 0; r4 < 4; r4++)
+#pragma unroll
+                        for (int h = 0; h < 2; h++)
+                            pk[r4 * 2 + h] = *reinterpret_cast<const uint4*>(sP + (size_t)ps * kPStageBytes + (lane + 32 * r4) * 128 + (((kbl * 2 + h) ^ sw) << 4));
+                    __syncwarp();
+                    if (lane == 0) mb_arrive(&empty_p[ps]);   // the nibbles are in registers: one of the chunk's four releases
+                    if (!mb_wait(&empty_a[cw], ((qi / NC) & 1) ^ 1, p.status, 0x700)) { ok = false; break; }
+                    uint8_t* stage = sA + (size_t)cw * kAStageBytes;
+#pragma unroll
+                    for (int r4 = 0; r4 < 4; r4++) {
+                        const int r = lane + 32 * r4;
+                        uint32_t zlo, zhi;
+                        zero_consts(zz[r4], zlo, zhi);
+                        const __half2 s2 = __half2half2(ss[r4]);
+                        uint8_t* arow = stage + (r >> 3) * 1024 + sw * 128;
+                        const uint32_t words[8] = {pk[r4 * 2].x, pk[r4 * 2].y, pk[r4 * 2].z, pk[r4 * 2].w, pk[r4 * 2 + 1].x, pk[r4 * 2 + 1].y, pk[r4 * 2 + 1].z, pk[r4 * 2 + 1].w};
+#pragma unroll
+                        for (int j = 0; j < 8; j++) *reinterpret_cast<uint4*>(arow + ((j ^ sw) << 4)) = dequant8<INTERLEAVED>(words[j], zlo, zhi, s2);
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores before the MMA's async-proxy reads
                     __syncwarp();
-                    if (lane == 0) mb_arrive(&full_a[s]);
-                    sit++;
+                    if (lane == 0) mb_arrive(&full_a[cw]);
                 }
-                __syncwarp();
-                if (lane == 0) mb_arrive(&empty_p[ps]);
-                pit++;
+                q += nkb;
             }
         }
-    } else {
+    } else if (warp < kFirstEpiWarp + kEpiWarps) {
         // ===================== epilogue =====================
-        const int q = warp & 3;              // the TMEM lane quarter this warp may read
-        const int r = q * 32 + lane;
+        const int qtr = warp & 3;              // the TMEM lane quarter this warp may read
+        const int r = qtr * 32 + lane;
         const int etid = (warp - kFirstEpiWarp) * 32 + lane;
         unsigned uit = 0;
         bool ok = true;
@@ -337,7 +376,7 @@ q4_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll 1
             for (int c0 = 0; c0 < MT; c0 += 16) {
                 uint32_t v[16];
-                tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, v);
+                tc_ld16(tmem_base + ((uint32_t)(qtr * 32) << 16) + (uint32_t)c0, v);
                 if (p.splits == 1) {
 #pragma unroll
                     for (int j = 0; j < 16; j++) {
@@ -364,13 +403,24 @@ q4_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 asm volatile("bar.sync 2, %0;" ::"n"(kEpiWarps * 32) : "memory");
                 if (s_last) {
                     __threadfence();
-                    const float* base = p.partials + ((size_t)(ui.tile * p.m_tiles + ui.mt) * p.splits) * MT * kBN;
-                    for (int c = 0; c < MT; c++) {
-                        const int m = ui.mt * MT + c;
-                        if (m >= p.M) break;
-                        float acc = 0.f;
-                        for (int s = 0; s < p.splits; s++) acc += __ldcg(base + ((size_t)s * MT + c) * kBN + r);
-                        if (n < p.N) p.y[(size_t)m * p.N + n] = __float2half(acc);
+                    const float* base = p.partials + ((size_t)(ui.tile * p.m_tiles + ui.mt) * p.splits) * MT * kBN + r;
+                    const int rows = min(MT, p.M - ui.mt * MT);
+                    // eight batch rows at a time, all their loads in flight together (the partial sums come from L2); the
+                    // splits are added in split order, so the result does not depend on which unit arrived last
+                    for (int c0 = 0; c0 < rows; c0 += 8) {
+                        float acc[8];
+#pragma unroll
+                        for (int j = 0; j < 8; j++) acc[j] = 0.f;
+                        for (int s = 0; s < p.splits; s++) {
+                            float v[8];
+#pragma unroll
+                            for (int j = 0; j < 8; j++) v[j] = c0 + j < rows ? __ldcg(base + ((size_t)s * MT + c0 + j) * kBN) : 0.f;
+#pragma unroll
+                            for (int j = 0; j < 8; j++) acc[j] += v[j];
+                        }
+#pragma unroll
+                        for (int j = 0; j < 8; j++)
+                            if (c0 + j < rows && n < p.N) p.y[(size_t)(ui.mt * MT + c0 + j) * p.N + n] = __float2half(acc[j]);
                     }
                 }
                 asm volatile("bar.sync 2, %0;" ::"n"(kEpiWarps * 32) : "memory");   // s_last is rewritten by the next unit
@@ -441,12 +491,15 @@ GemmPlan make_plan(int M, int K, int N, int sms) {
     g.n_chunks = q4_div_up(K, kChunkK);
     const int base = g.n_tiles * g.m_tiles;
     int best = 1;
-    double best_eff = 0;
+    double best_cost = 1e30;
     for (int s = 1; s <= 16 && s <= g.n_chunks; s++) {
         if (s > 1 && g.n_chunks / s < 2) break;   // at least two chunks (512 inputs) per unit
         const int units = base * s;
-        const double eff = (double)units / ((double)q4_div_up(units, sms) * sms);
-        if (eff > best_eff + 0.02) { best_eff = eff; best = s; }
+        // time of the slowest SM in chunk steps: its units' chunks, plus per unit a fixed cost (pipeline fill, epilogue)
+        // and, when K is split, the partial-sum round trip, which grows with the batch tile
+        const double per_unit = (double)q4_div_up(g.n_chunks, s) + 1.0 + (s > 1 ? 0.5 + g.mt / 64.0 : 0.0);
+        const double cost = q4_div_up(units, sms) * per_unit;
+        if (cost < best_cost * 0.97) { best_cost = cost; best = s; }
     }
     g.splits = best;
     g.units = base * best;
@@ -468,8 +521,8 @@ template <int MT, bool IL>
 int launch_gemm(cudaStream_t s, int grid, const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p) {
     const size_t smem = GemmCfg<MT>::kSmemBytes;
     Q4_CUDA_TRY(cudaFuncSetAttribute(q4_gemm_kernel<MT, IL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    q4_gemm_kernel<MT, IL><<<grid, kGemmThreads, smem, s>>>(mw, mx, p);
-    Q4_CUDA_TRY(cudaGetLastError());
+    Q4Launch L(dim3(grid), dim3(kGemmThreads), smem, s);   // programmatic dependent launch: the prologue overlaps the previous kernel's tail
+    Q4_CUDA_TRY(cudaLaunchKernelEx(&L.cfg, q4_gemm_kernel<MT, IL>, mw, mx, p));
     return Q4_OK;
 }
 
@@ -512,8 +565,8 @@ extern "C" int q4_matmul_q4_batched(void* stream, uint16_t* y, const uint16_t* x
     p.G = q4_groups(K);
     p.PZ = q4_pz(K);
     p.n_tiles = g.n_tiles; p.m_tiles = g.m_tiles; p.splits = g.splits; p.n_chunks = g.n_chunks; p.total_units = g.units;
-    // status word and tile counters start at zero (the kernel leaves the counters at zero, but not after an aborted run)
-    Q4_CUDA_TRY(cudaMemsetAsync(workspace, 0, kWsHeader + (size_t)g.n_tiles * g.m_tiles * sizeof(int), s));
+    // (status word and tile counters start at zero: the caller zeroes the workspace once, the kernel leaves the counters at
+    // zero; after a recorded time-out the caller zeroes it again)
     CUtensorMap mw, mx;
     const uint32_t* wsrc = weight_interleaved ? weight_interleaved : w->weight;
     if (int e = make_map_2d(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, wsrc, (uint64_t)q4_pw(K), (uint64_t)N, (uint64_t)q4_pw(K) * 4, kChunkK / 8, kBN)) return e;
@@ -532,4 +585,38 @@ extern "C" int q4_matmul_q4_batched_status(void* stream, const void* workspace) 
     Q4_CUDA_TRY(cudaMemcpy(st, workspace, sizeof(st), cudaMemcpyDeviceToHost));
     if (st[0]) fprintf(stderr, "q4 gemm: a bounded device-side wait ran out (status %d, location 0x%x)\n", st[0], st[1]);
     return st[0];
+}
+
+// Measurement hook: q4_matmul_q4_batched over `nmat` distinct weight matrices of one shape, captured as one CUDA graph
+// and replayed `reps` times between two events on `stream` (weights from HBM rather than L2, no launch gaps timed).
+extern "C" int q4_time_matmul_q4_batched(void* stream, uint16_t* y, const uint16_t* x, const q4_qweight* mats, const uint32_t* const* interleaved, int nmat,
+                                         int M, int K, int N, void* workspace, size_t workspace_bytes, int reps, double* us_per_launch) {
+    if (!mats || nmat < 1 || reps < 1 || !us_per_launch) return Q4_ERR_INVALID;
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    Q4_CUDA_TRY(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+    int e = Q4_OK;
+    for (int i = 0; i < nmat && e == Q4_OK; i++)
+        e = q4_matmul_q4_batched(s, y, x, &mats[i], interleaved ? interleaved[i] : nullptr, M, K, N, workspace, workspace_bytes);
+    cudaError_t ce = cudaStreamEndCapture(s, &graph);
+    if (e != Q4_OK) { if (graph) cudaGraphDestroy(graph); return e; }
+    Q4_CUDA_TRY(ce);
+    Q4_CUDA_TRY(cudaGraphInstantiate(&exec, graph, 0));
+    cudaEvent_t e0, e1;
+    Q4_CUDA_TRY(cudaEventCreate(&e0));
+    Q4_CUDA_TRY(cudaEventCreate(&e1));
+    for (int r = 0; r < 3; r++) Q4_CUDA_TRY(cudaGraphLaunch(exec, s));
+    Q4_CUDA_TRY(cudaEventRecord(e0, s));
+    for (int r = 0; r < reps; r++) Q4_CUDA_TRY(cudaGraphLaunch(exec, s));
+    Q4_CUDA_TRY(cudaEventRecord(e1, s));
+    Q4_CUDA_TRY(cudaEventSynchronize(e1));
+    float ms = 0.f;
+    Q4_CUDA_TRY(cudaEventElapsedTime(&ms, e0, e1));
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    cudaGraphExecDestroy(exec);
+    cudaGraphDestroy(graph);
+    *us_per_launch = 1e3 * ms / ((double)reps * nmat);
+    return Q4_OK;
 }
