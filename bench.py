@@ -104,18 +104,20 @@ def model_file(name, rank, dist):
     return path
 
 
-def cpu_port(path, prompt, n_tokens):
+def cpu_port(path, prompt, n_tokens, order=0):
     """The CPU oracle on positions 0 .. n_tokens of the same workload (teacher-forced with the prompt): tokens/s over
-    positions 1 .. n_tokens (position 0 pages the file in), the thread count, and the logits of every position."""
+    positions 1 .. n_tokens (position 0 pages the file in), the thread count, and the logits of every position.
+    order 0: plain loops (the timed port); order 1: the reference kernels' own summation order (lane-sequential FMA,
+    shuffle tree)."""
     from oracle import q4_oracle as O
     with open(path, "rb") as f:
         m = O.Model(f.read())
     logits = []
-    m.forward(int(prompt[0]), 0)
+    m.forward(int(prompt[0]), 0, order=order)
     logits.append(m.logits().copy())
     t0 = time.perf_counter()
     for pos in range(1, 1 + n_tokens):
-        m.forward(int(prompt[pos]), pos)
+        m.forward(int(prompt[pos]), pos, order=order)
         logits.append(m.logits().copy())
     dt = time.perf_counter() - t0
     cores = O.num_threads()
@@ -355,7 +357,7 @@ def allreduce_table(comm, dist, torch):
     except Exception as e:  # NCCL cannot be opened: the table then has the peer push only
         out["nccl_error"] = str(e)[:120]
     s = torch.cuda.current_stream()
-    for count in (4096, 5120, 8192, 32768):
+    for count in (4096, 5120, 8192, 16384, 32768):
         buf = torch.zeros(count, dtype=torch.float16, device="cuda")
         row = {}
         for name, backend in (("p2p_push", _lib.Q4_COMM_BACKEND_P2P), ("nccl", _lib.Q4_COMM_BACKEND_NCCL)):
@@ -385,7 +387,7 @@ def extra_model(name, rank, world, dist, torch, barrier, pk):
     cfg = synth.CONFIGS[name]
     prompt = synth.synth_prompt(N_PROMPT, cfg[5], seed=0)
     res = {}
-    for which in ("product", "exchange_local"):
+    for which in ("product", "test_build", "exchange_local"):
         lib = _lib.lib() if which == "product" else _lib.test_lib()
         if which == "exchange_local":
             lib.q4_test_set_fused_debug(16)
@@ -403,10 +405,12 @@ def extra_model(name, rank, world, dist, torch, barrier, pk):
             mean_bytes = sum(t.token_bytes(p) for p in range(STEPS_PER_GEN - 1)) / (STEPS_PER_GEN - 1)
             res.update({"tok_s": toks, "us_per_token": 1e6 / toks, "bytes_per_token_per_gpu": mean_bytes,
                         "token_roofline_frac": mean_bytes * toks / 1e9 / pk["hbm_gbs"], "status": st})
+        elif which == "test_build":
+            res["exchange"] = {"us_per_token": 1e6 / toks, "build": "test build of the library (same kernel plus its measurement switches)"}
         else:
             lib.q4_test_set_fused_debug(0)
-            res["us_per_token_exchange_local"] = 1e6 / toks
-            res["exposed_exchange_pct"] = 100.0 * (res["us_per_token"] - 1e6 / toks) / res["us_per_token"]
+            res["exchange"]["us_per_token_exchange_kept_local"] = 1e6 / toks
+            res["exposed_exchange_pct"] = 100.0 * (res["exchange"]["us_per_token"] - 1e6 / toks) / res["exchange"]["us_per_token"]
         t.close()
         comm.close()
         barrier()
@@ -519,8 +523,18 @@ def main():
     if cpu is not None:
         rels, coss = zip(*[compare(a, b) for a, b in zip(got, cpu[2])])
         parity.update({"positions": len(rels), "max_rel": max(rels), "cosine": min(coss), "against": "CPU oracle, same file, teacher-forced prompt"})
+        # How far two faithful evaluations of the reference arithmetic lie apart on this very model: the oracle in the
+        # reference kernels' summation order against the oracle with plain loops (fp32 sums in another order, nothing
+        # else). Thirty-two layers of random weights amplify a last-bit difference, so this, not the per-op tolerance, is
+        # the resolution of a whole-model logits comparison.
+        ref_order = cpu_port(path, prompt, PARITY_POSITIONS, order=1)
+        floor = max(compare(a, b)[0] for a, b in zip(ref_order[2], cpu[2]))
+        rels1 = [compare(a, b)[0] for a, b in zip(got, ref_order[2])]
+        parity.update({"oracle_reorder_max_rel": floor, "max_rel_vs_reference_order": max(rels1),
+                       "accept": "cosine >= limit and max_rel <= max(limit, 2 x oracle_reorder_max_rel)"})
     parity["device_status"] = t.status()
-    parity["ok"] = bool(tokens_match and parity["device_status"] == 0 and (cpu is None or (parity["max_rel"] <= MAX_REL and parity["cosine"] >= MIN_COS)))
+    parity["ok"] = bool(tokens_match and parity["device_status"] == 0 and
+                        (cpu is None or (parity["cosine"] >= MIN_COS and parity["max_rel"] <= max(MAX_REL, 2.0 * parity["oracle_reorder_max_rel"]))))
 
     # ---- dominant kernel against the HBM roofline ----
     pk, pk_kind = peaks()

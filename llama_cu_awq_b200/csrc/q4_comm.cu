@@ -311,13 +311,13 @@ extern "C" int q4_comm_set_backend(q4_comm* comm, int backend) {
     return Q4_OK;
 }
 
-// Which implementation serves a message of `count` halfs. AUTO follows the measured latency table (one 8-16 KB
-// vector: the one-shot push is several times faster than an NCCL call at every group size): peer push for
-// everything its inbox holds, NCCL beyond that when it is attached.
+// Which implementation serves a message of `count` halfs. AUTO follows the measured latency table: the one-shot peer
+// push for the vectors of this path (8-16 KB), NCCL for large messages when it is attached.
+constexpr int kAutoNcclAbove = 16384;   // halfs (32 KB): measured on 2 B200s, the peer push takes 8.5-9.0 us up to 16 KB against NCCL's 10.2-10.3 us; at 64 KB NCCL wins (10.8 vs 11.9 us)
 static bool use_nccl(const q4_comm* c, int count) {
     if (!c->nccl) return false;
     if (c->backend == Q4_COMM_BACKEND_NCCL) return true;
-    return c->backend == Q4_COMM_BACKEND_AUTO && count > Q4_COMM_MAX_HALFS;
+    return c->backend == Q4_COMM_BACKEND_AUTO && count > kAutoNcclAbove;
 }
 
 extern "C" int q4_comm_set_wait_limit_ns(q4_comm* comm, unsigned long long ns) {
