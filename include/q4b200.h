@@ -136,6 +136,11 @@ size_t q4_matmul_q4_batched_workspace_bytes(int M, int inpSize, int opSize);
 int q4_gemm_interleave_weights(void* stream, uint32_t* dst, const uint32_t* weight, int inpSize, int opSize);
 int q4_matmul_q4_batched(void* stream, uint16_t* y, const uint16_t* x, const q4_qweight* w, const uint32_t* weight_interleaved,
                          int M, int inpSize, int opSize, void* workspace, size_t workspace_bytes);
+/* The same with the fused residual of matmul(QWeight)'s accum form (gpu_kernels.h:237-238) for every row:
+ * y = product + residual * residual_scale, rounded to fp16 once; residual is [M][opSize] and may be y itself. */
+int q4_matmul_q4_batched_residual(void* stream, uint16_t* y, const uint16_t* x, const q4_qweight* w,
+                                  const uint32_t* weight_interleaved, int M, int inpSize, int opSize, const uint16_t* residual,
+                                  float residual_scale, void* workspace, size_t workspace_bytes);
 int q4_matmul_q4_batched_status(void* stream, const void* workspace);
 /* Measurement hook: q4_matmul_q4_batched over `nmat` distinct weight matrices of one shape (interleaved[i] may be NULL
  * or the array itself NULL), captured as one CUDA graph and replayed `reps` times between two events on `stream`. */
@@ -271,6 +276,31 @@ int q4_model_forward(q4_model* model, void* stream, int gen_token, int path);
  * as much extra device memory as the quantized weights). Q4_ERR_UNSUPPORTED_SIZE when the path cannot serve
  * this model; q4_model_forward calls it on demand. */
 int q4_model_prepare(q4_model* model, int path);
+
+/* Prompt prefill: the next n_tokens positions of the model's sequence (token ids from the mailbox, starting at the
+ * current position) in ONE pass through the network instead of n_tokens calls of q4_model_forward - what replaces the
+ * reference's token-by-token prompt loop (llama2_q4.cu:710-735; gen_token there is false for all prompt positions but the
+ * last). The projections run as W4 dequant-GEMMs on the tensor cores (q4_matmul_q4_batched), attention is causal over the
+ * cache, every K/V row lands in the cache the decode paths use, and the last row goes through the batch-1 tail: final
+ * norm, classifier, hand-off (tokens[pos + n_tokens] when gen_token != 0), both position words advanced by n_tokens.
+ * Hybrid tensor parallelism as q4_model_forward; its [n_tokens x dim] all-reduces go through NCCL when it is attached to
+ * the communicator and the backend choice allows it (Q4_COMM_BACKEND_AUTO / _NCCL), else through the peer push in pieces.
+ * Head size 128, dim a multiple of 128. The first call builds a re-ordered copy of the packed weights (as much device
+ * memory again as the quantized weights) and the row buffers. Asynchronous on `stream`. */
+int q4_model_prefill(q4_model* model, void* stream, int n_tokens, int gen_token);
+
+/* Batched decode: n_seq (<= 16) sequences that share the model's weights, each with its own K/V cache and position; one
+ * call of q4_batch_forward advances every sequence by one position (greedy), the weights are streamed once per step
+ * instead of once per sequence. The reference holds a single sequence (RunState, common.h:62-78) and has no counterpart.
+ * q4_batch_reset takes [n_seq][n_prompt] prompt ids (all sequences start at position 0); ids past a sequence's prompt are
+ * generated. q4_batch_logits: device pointer, [n_seq][vocab_size] halfs of the last step. */
+typedef struct q4_batch q4_batch;
+int q4_batch_create(q4_batch** batch, q4_model* model, int n_seq);
+int q4_batch_reset(q4_batch* batch, const int* prompts, int n_prompt);
+int q4_batch_forward(q4_batch* batch, void* stream);
+const uint16_t* q4_batch_logits(const q4_batch* batch);
+int q4_batch_read_tokens(const q4_batch* batch, int* out, int len);
+int q4_batch_free(q4_batch* batch);
 
 /* build_sampler (sampler.h:28-45). temperature 0 (the state after q4_model_load) decodes greedily; otherwise every
  * generating q4_model_forward ends with q4_sample_topp instead of the argmax. One coin is drawn from the xorshift*

@@ -58,6 +58,7 @@ SIGNATURES = {
     "q4_matmul_q4_batched_workspace_bytes": (C.c_size_t, [_I, _I, _I]),
     "q4_gemm_interleave_weights": (_I, [_P, _P, _P, _I, _I]),
     "q4_matmul_q4_batched": (_I, [_P, _P, _P, _QW, _P, _I, _I, _I, _P, C.c_size_t]),
+    "q4_matmul_q4_batched_residual": (_I, [_P, _P, _P, _QW, _P, _I, _I, _I, _P, C.c_float, _P, C.c_size_t]),
     "q4_matmul_q4_batched_status": (_I, [_P, _P]),
     "q4_time_matmul_q4_batched": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, C.c_size_t, _I, C.POINTER(C.c_double)]),
     "q4_qkv_matvec": (_I, [_P, _P, _P, _P, _P, _QW, _QW, _QW, _I, _I, _I, _I, _P]),
@@ -101,6 +102,13 @@ SIGNATURES = {
     "q4_model_reset": (_I, [_P, C.POINTER(C.c_int), _I, _I]),
     "q4_model_forward": (_I, [_P, _P, _I, _I]),
     "q4_model_prepare": (_I, [_P, _I]),
+    "q4_model_prefill": (_I, [_P, _P, _I, _I]),
+    "q4_batch_create": (_I, [C.POINTER(_P), _P, _I]),
+    "q4_batch_reset": (_I, [_P, C.POINTER(_I), _I]),
+    "q4_batch_forward": (_I, [_P, _P]),
+    "q4_batch_logits": (_P, [_P]),
+    "q4_batch_read_tokens": (_I, [_P, C.POINTER(_I), _I]),
+    "q4_batch_free": (_I, [_P]),
     "q4_model_set_sampler": (_I, [_P, C.c_float, C.c_float, C.c_ulonglong]),
     "q4_model_status": (_I, [_P]),
     "q4_model_set_wait_limit_ns": (_I, [_P, C.c_ulonglong]),

@@ -320,6 +320,8 @@ static bool use_nccl(const q4_comm* c, int count) {
     return c->backend == Q4_COMM_BACKEND_AUTO && count > kAutoNcclAbove;
 }
 
+bool q4_comm_prefers_nccl(const q4_comm* c, int count) { return c && use_nccl(c, count); }
+
 extern "C" int q4_comm_set_wait_limit_ns(q4_comm* comm, unsigned long long ns) {
     if (!comm) return Q4_ERR_INVALID;
     comm->wait_ns = ns ? ns : kDefaultWaitNs;

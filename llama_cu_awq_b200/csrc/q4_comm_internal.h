@@ -20,3 +20,5 @@ int q4_comm_world(const q4_comm* c);
 int q4_comm_rank(const q4_comm* c);
 // LL area of rank `peer`, as a pointer that is valid on the calling rank's device.
 Q4LLArea* q4_comm_ll_area(const q4_comm* c, int peer);
+// True when a message of `count` halfs goes through NCCL on this communicator (backend choice, NCCL attached).
+bool q4_comm_prefers_nccl(const q4_comm* c, int count);

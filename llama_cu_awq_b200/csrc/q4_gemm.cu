@@ -66,6 +66,8 @@ struct GemmParams {
     const uint32_t* zeros;
     const __half* scales;
     __half* y;
+    const __half* residual;   // optional [M][N]: y = product + residual * residual_scale, rounded once (may alias y)
+    float residual_scale;
     float* partials;     // [feature tile][batch tile][split][MT][128] fp32, used when splits > 1
     int* counters;       // [feature tile][batch tile]
     int* status;         // [0] error code, [1] where
@@ -381,7 +383,11 @@ q4_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
                     for (int j = 0; j < 16; j++) {
                         const int m = ui.mt * MT + c0 + j;
-                        if (n < p.N && m < p.M) p.y[(size_t)m * p.N + n] = __float2half(__uint_as_float(v[j]));
+                        if (n < p.N && m < p.M) {
+                            float val = __uint_as_float(v[j]);
+                            if (p.residual) val += __half2float(p.residual[(size_t)m * p.N + n]) * p.residual_scale;
+                            p.y[(size_t)m * p.N + n] = __float2half(val);
+                        }
                     }
                 } else {
 #pragma unroll
@@ -420,7 +426,11 @@ q4_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         }
 #pragma unroll
                         for (int j = 0; j < 8; j++)
-                            if (c0 + j < rows && n < p.N) p.y[(size_t)(ui.mt * MT + c0 + j) * p.N + n] = __float2half(acc[j]);
+                            if (c0 + j < rows && n < p.N) {
+                                const size_t at = (size_t)(ui.mt * MT + c0 + j) * p.N + n;
+                                if (p.residual) acc[j] += __half2float(p.residual[at]) * p.residual_scale;
+                                p.y[at] = __float2half(acc[j]);
+                            }
                     }
                 }
                 asm volatile("bar.sync 2, %0;" ::"n"(kEpiWarps * 32) : "memory");   // s_last is rewritten by the next unit
@@ -546,6 +556,11 @@ extern "C" int q4_gemm_interleave_weights(void* stream, uint32_t* dst, const uin
 
 extern "C" int q4_matmul_q4_batched(void* stream, uint16_t* y, const uint16_t* x, const q4_qweight* w, const uint32_t* weight_interleaved, int M, int K,
                                     int N, void* workspace, size_t workspace_bytes) {
+    return q4_matmul_q4_batched_residual(stream, y, x, w, weight_interleaved, M, K, N, nullptr, 0.f, workspace, workspace_bytes);
+}
+
+extern "C" int q4_matmul_q4_batched_residual(void* stream, uint16_t* y, const uint16_t* x, const q4_qweight* w, const uint32_t* weight_interleaved, int M,
+                                             int K, int N, const uint16_t* residual, float residual_scale, void* workspace, size_t workspace_bytes) {
     if (!y || !x || !w || !workspace || M <= 0 || K <= 0 || N <= 0) return Q4_ERR_INVALID;
     if ((K % 128) || (N % 8)) return Q4_ERR_UNSUPPORTED_SIZE;
     if (((uintptr_t)x & 15) || ((uintptr_t)w->weight & 15) || ((uintptr_t)weight_interleaved & 15) || ((uintptr_t)workspace & 15)) return Q4_ERR_INVALID;
@@ -558,6 +573,8 @@ extern "C" int q4_matmul_q4_batched(void* stream, uint16_t* y, const uint16_t* x
     p.zeros = w->zeros;
     p.scales = (const __half*)w->scales;
     p.y = (__half*)y;
+    p.residual = (const __half*)residual;
+    p.residual_scale = residual_scale;
     p.status = (int*)workspace;
     p.counters = (int*)((char*)workspace + kWsHeader);
     p.partials = (float*)((char*)workspace + kWsHeader + align_up16((size_t)g.n_tiles * g.m_tiles * sizeof(int)));

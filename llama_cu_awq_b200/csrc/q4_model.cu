@@ -168,6 +168,7 @@ int upload_raw(Arena& a, uint16_t** dst, const void* src, size_t bytes) {
 extern "C" int q4_model_free(q4_model* m) {
     if (!m) return Q4_OK;
     q4_fused_free(m);
+    q4_rows_free(m);
     for (int i = 0; i < 3; i++)
         if (m->graph_ready[i]) cudaGraphExecDestroy(m->graph[i]);
     cudaFree(m->arena);
@@ -236,6 +237,7 @@ static int model_build(q4_model** out, const q4_config& c, int rank, int gpu_cou
     m->topp = 0.f;
     m->rng_state = 0;
     m->fused = nullptr;
+    m->rows = nullptr;
     m->host_pos = 0;
     m->arena = nullptr;
     m->x = m->xb = m->hb = m->q = m->logits = m->kc = m->vc = nullptr;

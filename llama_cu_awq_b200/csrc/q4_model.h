@@ -3,6 +3,7 @@
 #include <vector>
 
 #include "q4_common.cuh"
+#include "q4_comm_internal.h"
 
 struct DevQW {
     q4_qweight w;
@@ -18,6 +19,7 @@ static inline size_t qw_bytes(int K, int N) { return (size_t)N * ((size_t)q4_pw(
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct q4_fused;  // state of the fused (persistent-kernel) path, q4_fused.cu
+struct q4_rows;   // row buffers of the prefill / batched-decode path, q4_batch.cu
 
 struct q4_model {
     q4_config cfg;
@@ -45,6 +47,7 @@ struct q4_model {
     float temperature, topp;
     unsigned long long rng_state;
     q4_fused* fused;
+    q4_rows* rows;
     int host_pos;               // forward calls since the last reset + the reset's position (bounds the K/V row written)
 };
 
@@ -54,6 +57,7 @@ int q4_fused_forward(q4_model* m, cudaStream_t s, int gen_token, int no_handoff)
 void q4_fused_reset(q4_model* m);                               // re-arms barrier counters (after q4_model_reset)
 void q4_fused_free(q4_model* m);
 int q4_fused_status(q4_model* m);
+void q4_rows_free(q4_model* m);   // q4_batch.cu
 void q4_fused_set_wait_limit(q4_model* m, unsigned long long ns);   // device-side wait limit of the fused kernel (0 = default)
 
 // q4_synth.cu: counter-based synthetic tensors generated on the device, shard by shard (see q4_model_create_synthetic)

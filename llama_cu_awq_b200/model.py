@@ -31,6 +31,10 @@ class Transformer:
     def forward(self, gen_token=True, path=1):
         check(self._L.q4_model_forward(self.h, C.c_void_p(self.stream.cuda_stream), int(bool(gen_token)), path), "run_transformer")
 
+    def prefill(self, n_tokens, gen_token=True):
+        """The next n_tokens prompt positions in one pass (q4_model_prefill)."""
+        check(self._L.q4_model_prefill(self.h, C.c_void_p(self.stream.cuda_stream), int(n_tokens), int(bool(gen_token))), "prefill")
+
     def set_sampler(self, temperature, topp, seed):
         """build_sampler (sampler.h:28): temperature 0 decodes greedily."""
         check(self._L.q4_model_set_sampler(self.h, float(temperature), float(topp), int(seed)), "build_sampler")
@@ -90,3 +94,45 @@ class Transformer:
             self.close()
         except Exception:
             pass
+
+
+class Batch:
+    """Batched decode of several sequences over one model (q4_batch_*)."""
+
+    def __init__(self, transformer, n_seq):
+        self.t, self._L, self.n_seq = transformer, transformer._L, n_seq
+        self.h = C.c_void_p()
+        check(self._L.q4_batch_create(C.byref(self.h), transformer.h, n_seq), "batch_create")
+
+    def reset(self, prompts):
+        arr = np.ascontiguousarray(prompts, dtype=np.int32)
+        assert arr.ndim == 2 and arr.shape[0] == self.n_seq
+        check(self._L.q4_batch_reset(self.h, arr.ctypes.data_as(C.POINTER(C.c_int)), arr.shape[1]), "batch_reset")
+
+    def forward(self):
+        check(self._L.q4_batch_forward(self.h, C.c_void_p(self.t.stream.cuda_stream)), "batch_forward")
+
+    def logits(self):
+        n = self.n_seq * self.t.config.vocab_size
+        out = np.empty(n, np.float16)
+        self.t.synchronize()
+        ptr = self._L.q4_batch_logits(self.h)
+        src = torch.as_tensor(_DevView(ptr, n), device="cuda")
+        return src.cpu().numpy().reshape(self.n_seq, -1)
+
+    def tokens(self, length):
+        out = np.zeros((self.n_seq, length), np.int32)
+        check(self._L.q4_batch_read_tokens(self.h, out.ctypes.data_as(C.POINTER(C.c_int)), length), "batch_read_tokens")
+        return out
+
+    def close(self):
+        if self.h:
+            self._L.q4_batch_free(self.h)
+            self.h = C.c_void_p()
+
+
+class _DevView:
+    """A device pointer as something torch.as_tensor accepts (CUDA array interface)."""
+
+    def __init__(self, ptr, n, typestr="<f2"):
+        self.__cuda_array_interface__ = {"shape": (n,), "typestr": typestr, "data": (int(ptr), False), "version": 2}

@@ -1,0 +1,135 @@
+"""Prompt prefill in one pass (q4_model_prefill) and batched decode of several sequences (q4_batch_*): both run the
+projections as W4 dequant-GEMMs on the tensor cores and must agree with the token-by-token decode paths and the oracle."""
+import numpy as np
+import pytest
+
+from conftest import MAX_REL, assert_close
+from llama_cu_awq_b200 import _lib, synth
+from llama_cu_awq_b200.model import Batch, Transformer
+from oracle import q4_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def mid_path(tmp_path_factory):
+    p = tmp_path_factory.mktemp("models") / "mid_gqa.bin"
+    synth.write_model_file(str(p), "mid-gqa", seed=4)
+    return str(p)
+
+
+def token_by_token(path, tokens, fwd_path, keep):
+    t = Transformer(path)
+    t.reset(tokens, 0)
+    out = {}
+    for pos in range(len(tokens)):
+        t.forward(gen_token=False, path=fwd_path)
+        if pos in keep:
+            t.synchronize()
+            out[pos] = t.logits()
+    t.synchronize()
+    assert t.status() == 0
+    t.close()
+    return out
+
+
+@pytest.mark.parametrize("n_prompt", [1, 5, 37, 100])
+def test_prefill_matches_token_by_token_and_the_oracle(mid_path, n_prompt):
+    """The prompt in one pass, then decoding goes on through the fused path on the cache the prefill filled: logits of the
+    last prompt position and of later positions against the oracle and against the token-by-token run."""
+    vocab = synth.CONFIGS["mid-gqa"][5]
+    extra = 6
+    tokens = np.random.default_rng(n_prompt).integers(3, vocab, size=n_prompt + extra, dtype=np.int32)
+    keep = {n_prompt - 1, n_prompt + 2, n_prompt + extra - 1}
+    ref = token_by_token(mid_path, tokens, 1, keep)
+    t = Transformer(mid_path)
+    assert t.best_path() == 2
+    t.reset(tokens, 0)
+    t.prefill(n_prompt, gen_token=False)
+    t.synchronize()
+    got = {n_prompt - 1: t.logits()}
+    assert t.shared().pos == n_prompt
+    for pos in range(n_prompt, n_prompt + extra):
+        t.forward(gen_token=False, path=2)
+        if pos in keep:
+            t.synchronize()
+            got[pos] = t.logits()
+    t.synchronize()
+    assert t.status() == 0
+    t.close()
+    m = O.Model(open(mid_path, "rb").read())
+    for pos, tok in enumerate(tokens):
+        m.forward(int(tok), pos, order=0)
+        if pos in keep:
+            assert_close(got[pos], m.logits(), f"prefill {n_prompt}, logits at pos {pos} vs oracle")
+            assert_close(got[pos], ref[pos], f"prefill {n_prompt}, logits at pos {pos} vs token by token", max_rel=2 * MAX_REL)
+    m.close()
+
+
+def test_prefill_hand_off_and_pieces(mid_path):
+    """gen_token writes the greedy id after the prompt; a prompt fed in two pieces gives the same cache (to tolerance)."""
+    vocab = synth.CONFIGS["mid-gqa"][5]
+    tokens = np.random.default_rng(7).integers(3, vocab, size=48, dtype=np.int32)
+    t = Transformer(mid_path)
+    t.reset(tokens[:40], 0)
+    t.prefill(40, gen_token=True)
+    t.synchronize()
+    one = t.logits()
+    assert int(t.shared().tokens[40]) == O.argmax(one) and t.shared().pos == 40
+    t.reset(tokens[:40], 0)
+    t.prefill(23, gen_token=False)
+    t.prefill(17, gen_token=True)
+    t.synchronize()
+    two = t.logits()
+    assert t.shared().pos == 40
+    assert_close(two, one, "prompt in two pieces vs one piece", max_rel=2 * MAX_REL)
+    # a prompt that does not fit what is left of the sequence is refused
+    L = _lib.lib()
+    import ctypes as C
+    assert L.q4_model_prefill(t.h, C.c_void_p(t.stream.cuda_stream), synth.CONFIGS["mid-gqa"][6], 0) == _lib.Q4_ERR_LIMIT
+    t.close()
+
+
+def test_prefill_512_tokens_on_7b_layer_shapes(tmp_path):
+    """512 prompt positions through four layers of the 7B shapes: last-position logits against the fused decode path."""
+    path = str(tmp_path / "7b4l.bin")
+    synth.write_model_file(path, "llama2-7b-4l", seed=0)
+    tokens = np.random.default_rng(1).integers(3, 32000, size=512, dtype=np.int32)
+    ref = token_by_token(path, tokens, 2, {511})
+    t = Transformer(path)
+    t.reset(tokens, 0)
+    t.prefill(512, gen_token=False)
+    t.synchronize()
+    assert t.status() == 0
+    assert_close(t.logits(), ref[511], "512-token prefill vs token-by-token fused path", max_rel=2 * MAX_REL)
+    t.close()
+
+
+@pytest.mark.parametrize("n_seq", [1, 8])
+def test_batched_decode_matches_single_sequence_decode(mid_path, n_seq):
+    """n_seq sequences with different prompts advance together; each one's logits equal (to tolerance) what the single-
+    sequence path computes when it is fed that sequence's tokens, and the ids it generated are the argmax of its logits."""
+    vocab = synth.CONFIGS["mid-gqa"][5]
+    n_prompt, steps = 5, 14
+    prompts = np.random.default_rng(3).integers(3, vocab, size=(n_seq, n_prompt), dtype=np.int32)
+    t = Transformer(mid_path)
+    b = Batch(t, n_seq)
+    b.reset(prompts)
+    per_step = []
+    for _ in range(steps):
+        b.forward()
+        per_step.append(b.logits())
+    toks = b.tokens(steps + 1)
+    assert (toks[:, :n_prompt] == prompts).all()
+    for s in range(n_seq):
+        for pos in range(n_prompt - 1, steps):
+            assert toks[s, pos + 1] == O.argmax(per_step[pos][s]), (s, pos)
+    b.close()
+    for s in range(n_seq):
+        t.reset(toks[s], 0)
+        for pos in range(steps):
+            t.forward(gen_token=False, path=1)
+            if pos in (0, n_prompt - 1, steps - 1):
+                t.synchronize()
+                assert_close(per_step[pos][s], t.logits(), f"sequence {s} of {n_seq}, pos {pos}", max_rel=2 * MAX_REL)
+    t.close()
