@@ -256,6 +256,15 @@ void q4_rows_free(q4_model* m) {
     m->rows = nullptr;
 }
 
+// Status word of the GEMM workspace (Q4_ERR_TIMEOUT after a bounded device-side wait ran out); the device is idle.
+int q4_rows_status(q4_model* m) {
+    if (!m->rows || !m->rows->ws) return Q4_OK;
+    int st[2] = {0, 0};
+    Q4_CUDA_TRY(cudaMemcpy(st, m->rows->ws, sizeof(st), cudaMemcpyDeviceToHost));
+    if (st[0]) fprintf(stderr, "q4 prefill / batch path: a bounded device-side wait of the GEMM ran out (status %d, location 0x%x)\n", st[0], st[1]);
+    return st[0];
+}
+
 static const DevQW* layer_mats(const DevLayer& L, int i) {
     const DevQW* a[7] = {&L.q, &L.k, &L.v, &L.o, &L.gate, &L.up, &L.down};
     return a[i];

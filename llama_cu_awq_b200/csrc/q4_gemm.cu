@@ -524,8 +524,11 @@ int sm_count(int* out) {
     return Q4_OK;
 }
 
-constexpr size_t kWsHeader = 256;   // status words
-size_t align_up16(size_t v) { return (v + 15) & ~(size_t)15; }
+// Workspace layout, the same for every shape, so that calls of different shapes can share one workspace (the tile counters
+// must read zero at the start of every call): status words | tile counters | fp32 partial sums.
+constexpr size_t kWsHeader = 256;
+constexpr int kWsMaxTiles = 8192;
+constexpr size_t kWsPartials = kWsHeader + sizeof(int) * kWsMaxTiles;
 
 template <int MT, bool IL>
 int launch_gemm(cudaStream_t s, int grid, const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p) {
@@ -543,7 +546,7 @@ extern "C" size_t q4_matmul_q4_batched_workspace_bytes(int M, int K, int N) {
     int sms = 148;
     sm_count(&sms);
     const GemmPlan g = make_plan(M, K, N, sms);
-    return kWsHeader + align_up16((size_t)g.n_tiles * g.m_tiles * sizeof(int)) + g.partial_floats * sizeof(float);
+    return kWsPartials + g.partial_floats * sizeof(float);
 }
 
 extern "C" int q4_gemm_interleave_weights(void* stream, uint32_t* dst, const uint32_t* weight, int K, int N) {
@@ -577,7 +580,8 @@ extern "C" int q4_matmul_q4_batched_residual(void* stream, uint16_t* y, const ui
     p.residual_scale = residual_scale;
     p.status = (int*)workspace;
     p.counters = (int*)((char*)workspace + kWsHeader);
-    p.partials = (float*)((char*)workspace + kWsHeader + align_up16((size_t)g.n_tiles * g.m_tiles * sizeof(int)));
+    p.partials = (float*)((char*)workspace + kWsPartials);
+    if (g.n_tiles * g.m_tiles > kWsMaxTiles) return Q4_ERR_UNSUPPORTED_SIZE;
     p.M = M; p.K = K; p.N = N;
     p.G = q4_groups(K);
     p.PZ = q4_pz(K);

@@ -538,6 +538,7 @@ extern "C" int q4_model_status(q4_model* m) {
     if (!m) return Q4_ERR_INVALID;
     Q4_CUDA_TRY(cudaDeviceSynchronize());
     int st = q4_fused_status(m);
+    if (st == Q4_OK) st = q4_rows_status(m);
     if (st == Q4_OK && m->comm) st = q4_comm_status(m->comm);
     return st;
 }

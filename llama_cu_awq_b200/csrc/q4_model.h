@@ -58,6 +58,7 @@ void q4_fused_reset(q4_model* m);                               // re-arms barri
 void q4_fused_free(q4_model* m);
 int q4_fused_status(q4_model* m);
 void q4_rows_free(q4_model* m);   // q4_batch.cu
+int q4_rows_status(q4_model* m);
 void q4_fused_set_wait_limit(q4_model* m, unsigned long long ns);   // device-side wait limit of the fused kernel (0 = default)
 
 // q4_synth.cu: counter-based synthetic tensors generated on the device, shard by shard (see q4_model_create_synthetic)
