@@ -377,6 +377,75 @@ def allreduce_table(comm, dist, torch):
     return out
 
 
+def prefill_and_batch(t, cfg, fwd_path, value, rank, world, dist, torch, barrier, pk):
+    """The two callers either side of the batch-1 decode step on the same model: a 512-token prompt processed in one
+    pass (W4 GEMMs on the tensor cores) against the same 512 positions fed token by token, and eight sequences decoded
+    together against eight times the batch-1 rate."""
+    from llama_cu_awq_b200 import synth
+    from llama_cu_awq_b200.model import Batch
+    out = {}
+    n_pre = 512
+    ids = synth.synth_prompt(n_pre, cfg[5], seed=1)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def timed(fn, reps):
+        best = []
+        for _ in range(reps):
+            t.reset(ids, 0)
+            barrier()
+            with torch.cuda.stream(t.stream):
+                e0.record(t.stream)
+                fn()
+                e1.record(t.stream)
+            t.synchronize()
+            ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
+            if dist is not None:
+                dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+            best.append(float(ms.item()))
+        return sum(best[1:]) / (len(best) - 1)   # the first repetition warms up (workspaces, interleaved weight copies)
+
+    def by_token():
+        for _ in range(n_pre):
+            t.forward(gen_token=False, path=fwd_path)
+
+    ms_pre = timed(lambda: t.prefill(n_pre, gen_token=False), 4)
+    one_pass = t.logits()
+    ms_tok = timed(by_token, 2)
+    rel, cos = compare(one_pass, t.logits())
+    n_layers, dim, hidden = cfg[2], cfg[0], cfg[1]
+    kv_dim = dim * cfg[4] // cfg[3]
+    flops = 2.0 * n_pre * n_layers * (2 * dim * dim + 2 * dim * kv_dim + 3 * dim * hidden) / world
+    out["prefill_512"] = {"ms": ms_pre, "tok_s": n_pre / ms_pre * 1e3, "ms_token_by_token": ms_tok, "speedup_vs_token_by_token": ms_tok / ms_pre,
+                          "w4_gemm_tflops_per_gpu": flops / (ms_pre * 1e-3) / 1e12, "frac_of_bf16_sustained": flops / (ms_pre * 1e-3) / 1e12 / pk.get("bf16_tflops_sustained", pk["bf16_tflops"]),
+                          "last_logits_vs_token_by_token": {"max_rel": rel, "cosine": cos}, "status": t.status()}
+
+    n_seq, steps = 8, 64
+    b = Batch(t, n_seq)
+    prompts = np.stack([synth.synth_prompt(N_PROMPT, cfg[5], seed=10 + i) for i in range(n_seq)])
+    times = []
+    for rep in range(3):
+        b.reset(prompts)
+        for _ in range(N_PROMPT):
+            b.forward()
+        t.synchronize()
+        barrier()
+        with torch.cuda.stream(t.stream):
+            e0.record(t.stream)
+            for _ in range(steps):
+                b.forward()
+            e1.record(t.stream)
+        t.synchronize()
+        ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
+        if dist is not None:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        times.append(float(ms.item()))
+    ms_step = sum(times[1:]) / (len(times) - 1) / steps
+    out["batch8_decode"] = {"ms_per_step": ms_step, "tok_s_all_sequences": n_seq / ms_step * 1e3, "vs_batch1_rate": n_seq / ms_step * 1e3 / value,
+                            "positions": f"{N_PROMPT}..{N_PROMPT + steps}", "status": t.status()}
+    b.close()
+    return out
+
+
 def extra_model(name, rank, world, dist, torch, barrier, pk):
     """A larger model of the metric at this tensor-parallel degree, generated on the device: tok/s, fraction of the
     weight-streaming roofline, and the share of the step that waits for the exchange between the ranks (step time minus
@@ -555,6 +624,14 @@ def main():
         k = (extra.get("kernels") or {}).get("ffn_gate_up_silu") or {}
         roof = {"bound": "hbm", "kernel": "q4_gemv_kernel (fused gate/up + SiLU)", "achieved": k.get("gbs"), "peak": pk["hbm_gbs"], "unit": "GB/s",
                 "frac": k.get("frac_of_hbm_peak"), "peak_kind": pk_kind, "traffic": None, "bytes_per_launch": k.get("bytes"), "us_per_launch": k.get("us")}
+    if not args.no_extras:
+        try:
+            if comm is not None and _lib.lib().q4_comm_nccl_available():
+                comm.attach_nccl(dist)   # the [rows x dim] all-reduces of the GEMM paths go through NCCL; one-token ones stay on the peer push
+                comm.set_backend(_lib.Q4_COMM_BACKEND_AUTO)
+            extra.update(prefill_and_batch(t, cfg, fwd_path, value, rank, world, dist, torch, barrier, pk))
+        except Exception as e:   # reported, not fatal: the headline line stays valid
+            extra["prefill_batch_error"] = str(e)[:300]
     t.close()
     if comm:
         comm.close()

@@ -142,6 +142,21 @@ int q4_matmul_q4_batched_residual(void* stream, uint16_t* y, const uint16_t* x, 
                                   const uint32_t* weight_interleaved, int M, int inpSize, int opSize, const uint16_t* residual,
                                   float residual_scale, void* workspace, size_t workspace_bytes);
 int q4_matmul_q4_batched_status(void* stream, const void* workspace);
+
+/* The same products for a handful of rows (1 <= M <= 16): the projections of batched decode, where every sequence adds one
+ * row and the weights are still read once per step. HBM-bound like the batch-1 kernels they widen (mat_vec_kernel_int4,
+ * qkv_matvec_kernel, ffn_matvec_silu_kernel: gpu_kernels.h:179-283), so no tcgen05 tiles here: packed words straight from
+ * global memory into mma.sync fragments, fp32 accumulation, group scale applied in fp32, no workspace, results
+ * bit-reproducible. x is [M][inpSize], every y [M][its opSize], row-major fp16; inpSize a multiple of 128.
+ *   q4_matmul_q4_rows : y = x * deq(w) [+ residual * residual_scale when residual is not NULL; residual may be y]; opSize % 16 == 0
+ *   q4_qkv_matmul_rows: q, k, v from one read of x (opSize, kvSize multiples of 32)
+ *   q4_ffn_silu_rows  : h = silu(x * deq(gate)) * (x * deq(up)), gate and up kept in fp32 until the product; opSize % 16 == 0 */
+int q4_matmul_q4_rows(void* stream, uint16_t* y, const uint16_t* x, const q4_qweight* w, int M, int inpSize, int opSize,
+                      const uint16_t* residual, float residual_scale);
+int q4_qkv_matmul_rows(void* stream, uint16_t* q, uint16_t* k, uint16_t* v, const uint16_t* x, const q4_qweight* qw,
+                       const q4_qweight* kw, const q4_qweight* vw, int M, int inpSize, int opSize, int kvSize);
+int q4_ffn_silu_rows(void* stream, uint16_t* h, const uint16_t* x, const q4_qweight* gate_w, const q4_qweight* up_w, int M,
+                     int inpSize, int opSize);
 /* Measurement hook: q4_matmul_q4_batched over `nmat` distinct weight matrices of one shape (interleaved[i] may be NULL
  * or the array itself NULL), captured as one CUDA graph and replayed `reps` times between two events on `stream`. */
 int q4_time_matmul_q4_batched(void* stream, uint16_t* y, const uint16_t* x, const q4_qweight* mats,
@@ -336,6 +351,10 @@ int q4_model_time_ffn(q4_model* model, void* stream, int reps, double* total_ms,
  * launch gap is timed. Returns microseconds and algorithmic bytes per launch. */
 int q4_time_q4_op(void* stream, int kind, uint16_t* y, uint16_t* y2, uint16_t* y3, const uint16_t* x, const q4_qweight* mats,
                   int nmat, int K, int N, int reps, const int* pPos, double* us_per_launch, double* bytes_per_launch);
+/* The same for the few-rows forms with M rows of x: kind 0 q4_matmul_q4_rows, 1 q4_qkv_matmul_rows (kvSize = opSize),
+ * 2 q4_ffn_silu_rows. */
+int q4_time_q4_rows_op(void* stream, int kind, int M, uint16_t* y, uint16_t* y2, uint16_t* y3, const uint16_t* x, const q4_qweight* mats,
+                       int nmat, int K, int N, int reps, double* us_per_launch, double* bytes_per_launch);
 /* Measurement hook: `reps` in-place q4_all_reduce calls of `count` halfs back to back between two events on `stream`. */
 int q4_time_all_reduce(q4_comm* comm, void* stream, uint16_t* buf, int count, int reps, double* us_per_call);
 

@@ -60,6 +60,9 @@ SIGNATURES = {
     "q4_matmul_q4_batched": (_I, [_P, _P, _P, _QW, _P, _I, _I, _I, _P, C.c_size_t]),
     "q4_matmul_q4_batched_residual": (_I, [_P, _P, _P, _QW, _P, _I, _I, _I, _P, C.c_float, _P, C.c_size_t]),
     "q4_matmul_q4_batched_status": (_I, [_P, _P]),
+    "q4_matmul_q4_rows": (_I, [_P, _P, _P, _QW, _I, _I, _I, _P, C.c_float]),
+    "q4_qkv_matmul_rows": (_I, [_P, _P, _P, _P, _P, _QW, _QW, _QW, _I, _I, _I, _I]),
+    "q4_ffn_silu_rows": (_I, [_P, _P, _P, _QW, _QW, _I, _I, _I]),
     "q4_time_matmul_q4_batched": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, C.c_size_t, _I, C.POINTER(C.c_double)]),
     "q4_qkv_matvec": (_I, [_P, _P, _P, _P, _P, _QW, _QW, _QW, _I, _I, _I, _I, _P]),
     "q4_ffn_matvec_silu": (_I, [_P, _P, _P, _QW, _QW, _I, _I]),
@@ -116,6 +119,7 @@ SIGNATURES = {
     "q4_model_token_bytes": (C.c_double, [_P, _I]),
     "q4_model_time_ffn": (_I, [_P, _P, _I, C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "q4_time_q4_op": (_I, [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, C.POINTER(C.c_double), C.POINTER(C.c_double)]),
+    "q4_time_q4_rows_op": (_I, [_P, _I, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "q4_time_all_reduce": (_I, [_P, _P, _P, _I, _I, C.POINTER(C.c_double)]),
     "q4_model_trace": (_I, [_P, _P, _P, _I]),
     "q4_tokenizer_load": (_I, [C.POINTER(_P), C.c_char_p, _I]),

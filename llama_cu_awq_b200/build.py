@@ -13,7 +13,7 @@ CLI = os.path.join(HERE, "llama2_q4")
 TEST_LIB = os.path.join(HERE, "libq4b200_test.so")
 PACKER = os.path.join(HERE, "weight_packer")   # offline tool, host code only
 TEST_BUILD_SOURCES = ["q4_comm.cu", "q4_fused.cu"]   # the sources that look at Q4_TEST_BUILD
-LIB_SOURCES = ["q4_gemv.cu", "q4_ops.cu", "q4_attn.cu", "q4_comm.cu", "q4_model.cu", "q4_fused.cu", "q4_sampler.cu", "q4_synth.cu", "q4_tokenizer.cu", "q4_gemm.cu", "q4_batch.cu"]
+LIB_SOURCES = ["q4_gemv.cu", "q4_ops.cu", "q4_attn.cu", "q4_comm.cu", "q4_model.cu", "q4_fused.cu", "q4_sampler.cu", "q4_synth.cu", "q4_tokenizer.cu", "q4_gemm.cu", "q4_skinny.cu", "q4_batch.cu"]
 CLI_SOURCES = ["llama2_q4_main.cpp"]
 NVCC_FLAGS = ["-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo"]
 

@@ -372,12 +372,31 @@ q4_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         for (int u = blockIdx.x; u < p.total_units && ok; u += gridDim.x, uit++) {
             const UnitInfo ui = unit_info(p, u);
             const int n = ui.tile * kBN + r;
+            // The residual may be y itself, so a residual load cannot be moved across a store of y by the compiler: the
+            // loads of a 16-row chunk are issued together and one chunk ahead of the stores, the first chunk's while the MMAs
+            // of the unit still run.
+            float res_next[16];
+            auto load_res = [&](int c0, float (&res)[16]) {
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    const int m = ui.mt * MT + c0 + j;
+                    res[j] = (n < p.N && m < p.M) ? __half2float(p.residual[(size_t)m * p.N + n]) : 0.f;
+                }
+            };
+            const bool add_res = p.residual != nullptr && p.splits == 1;
+            if (add_res) load_res(0, res_next);
             if (!mb_wait(&tmem_full, uit & 1, p.status, 0x800)) { ok = false; break; }
             tc_fence_after();
             float* part = p.partials + (((size_t)(ui.tile * p.m_tiles + ui.mt) * p.splits + ui.split) * MT) * kBN;
 #pragma unroll 1
             for (int c0 = 0; c0 < MT; c0 += 16) {
                 uint32_t v[16];
+                float res[16];
+                if (add_res) {
+#pragma unroll
+                    for (int j = 0; j < 16; j++) res[j] = res_next[j];
+                    if (c0 + 16 < MT) load_res(c0 + 16, res_next);
+                }
                 tc_ld16(tmem_base + ((uint32_t)(qtr * 32) << 16) + (uint32_t)c0, v);
                 if (p.splits == 1) {
 #pragma unroll
@@ -385,7 +404,7 @@ q4_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         const int m = ui.mt * MT + c0 + j;
                         if (n < p.N && m < p.M) {
                             float val = __uint_as_float(v[j]);
-                            if (p.residual) val += __half2float(p.residual[(size_t)m * p.N + n]) * p.residual_scale;
+                            if (add_res) val += res[j] * p.residual_scale;
                             p.y[(size_t)m * p.N + n] = __float2half(val);
                         }
                     }
@@ -417,6 +436,10 @@ q4_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         float acc[8];
 #pragma unroll
                         for (int j = 0; j < 8; j++) acc[j] = 0.f;
+                        float res[8];
+#pragma unroll
+                        for (int j = 0; j < 8; j++)   // all eight before any store of y (the residual may be y)
+                            res[j] = (p.residual && c0 + j < rows && n < p.N) ? __half2float(p.residual[(size_t)(ui.mt * MT + c0 + j) * p.N + n]) : 0.f;
                         for (int s = 0; s < p.splits; s++) {
                             float v[8];
 #pragma unroll
@@ -428,7 +451,7 @@ q4_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         for (int j = 0; j < 8; j++)
                             if (c0 + j < rows && n < p.N) {
                                 const size_t at = (size_t)(ui.mt * MT + c0 + j) * p.N + n;
-                                if (p.residual) acc[j] += __half2float(p.residual[at]) * p.residual_scale;
+                                if (p.residual) acc[j] += res[j] * p.residual_scale;
                                 p.y[at] = __float2half(acc[j]);
                             }
                     }

@@ -660,6 +660,45 @@ extern "C" int q4_time_q4_op(void* stream, int kind, uint16_t* y, uint16_t* y2, 
     return Q4_OK;
 }
 
+// The same for the few-rows forms (kind 0 q4_matmul_q4_rows, 1 q4_qkv_matmul_rows, 2 q4_ffn_silu_rows) with M rows of x.
+extern "C" int q4_time_q4_rows_op(void* stream, int kind, int M, uint16_t* y, uint16_t* y2, uint16_t* y3, const uint16_t* x, const q4_qweight* mats,
+                                  int nmat, int K, int N, int reps, double* us_per_launch, double* bytes_per_launch) {
+    if (!y || !x || !mats || nmat < 1 || reps < 1 || !us_per_launch || !bytes_per_launch || kind < 0 || kind > 2) return Q4_ERR_INVALID;
+    const int per = kind == 1 ? 3 : kind == 2 ? 2 : 1;
+    if (nmat < per || (kind == 1 && (!y2 || !y3))) return Q4_ERR_INVALID;
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    Q4_CUDA_TRY(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+    int e = Q4_OK, launches = 0;
+    for (int i = 0; i + per <= nmat && e == Q4_OK; i += per, launches++) {
+        if (kind == 0) e = q4_matmul_q4_rows(s, y, x, &mats[i], M, K, N, nullptr, 0.f);
+        else if (kind == 1) e = q4_qkv_matmul_rows(s, y, y2, y3, x, &mats[i], &mats[i + 1], &mats[i + 2], M, K, N, N);
+        else e = q4_ffn_silu_rows(s, y, x, &mats[i], &mats[i + 1], M, K, N);
+    }
+    cudaError_t ce = cudaStreamEndCapture(s, &graph);
+    if (e != Q4_OK) { if (graph) cudaGraphDestroy(graph); return e; }
+    Q4_CUDA_TRY(ce);
+    Q4_CUDA_TRY(cudaGraphInstantiate(&exec, graph, 0));
+    cudaEvent_t e0, e1;
+    Q4_CUDA_TRY(cudaEventCreate(&e0));
+    Q4_CUDA_TRY(cudaEventCreate(&e1));
+    for (int r = 0; r < 3; r++) Q4_CUDA_TRY(cudaGraphLaunch(exec, s));   // warm-up
+    Q4_CUDA_TRY(cudaEventRecord(e0, s));
+    for (int r = 0; r < reps; r++) Q4_CUDA_TRY(cudaGraphLaunch(exec, s));
+    Q4_CUDA_TRY(cudaEventRecord(e1, s));
+    Q4_CUDA_TRY(cudaEventSynchronize(e1));
+    float ms = 0.f;
+    Q4_CUDA_TRY(cudaEventElapsedTime(&ms, e0, e1));
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    cudaGraphExecDestroy(exec);
+    cudaGraphDestroy(graph);
+    *us_per_launch = 1e3 * ms / ((double)reps * launches);
+    *bytes_per_launch = per * (double)qw_bytes(K, N) + 2.0 * M * K + 2.0 * M * N * per / (kind == 2 ? 2 : 1);
+    return Q4_OK;
+}
+
 // Measurement hook: `reps` in-place all-reduces of `count` halfs back to back on `stream` between two events (the
 // caller aligns the ranks with a host barrier first and takes the maximum over the ranks).
 extern "C" int q4_time_all_reduce(q4_comm* comm, void* stream, uint16_t* buf, int count, int reps, double* us_per_call) {

@@ -131,3 +131,19 @@ class BatchedMatmul:
 
     def status(self, stream=None):
         return _lib.lib().q4_matmul_q4_batched_status(_stream(stream), _p(self.ws))
+
+
+def matmul_rows(y, x, w, rows, inpSize, opSize, residual=None, residual_scale=1.0, stream=None):
+    """matmul(QWeight) for 1..16 rows (q4_matmul_q4_rows): y[m] = x[m] * deq(w) [+ residual[m] * residual_scale]."""
+    check(_lib.lib().q4_matmul_q4_rows(_stream(stream), _p(y), _p(x), w.ref, rows, inpSize, opSize, _p(residual), residual_scale), "matmul_rows")
+
+
+def qkv_matmul_rows(q, k, v, x, qw, kw, vw, rows, inpSize, opSize, kvSize, stream=None):
+    """qkv_matvec for 1..16 rows (q4_qkv_matmul_rows); K and V rows land in plain [rows][kvSize] buffers."""
+    check(_lib.lib().q4_qkv_matmul_rows(_stream(stream), _p(q), _p(k), _p(v), _p(x), qw.ref, kw.ref, vw.ref, rows, inpSize, opSize, kvSize),
+          "qkv_matmul_rows")
+
+
+def ffn_silu_rows(h, x, gate_w, up_w, rows, inpSize, opSize, stream=None):
+    """ffn_matvec_silu for 1..16 rows (q4_ffn_silu_rows)."""
+    check(_lib.lib().q4_ffn_silu_rows(_stream(stream), _p(h), _p(x), gate_w.ref, up_w.ref, rows, inpSize, opSize), "ffn_silu_rows")

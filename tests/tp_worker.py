@@ -20,6 +20,7 @@ def main():
     tp_mode = _lib.Q4_TP_COLUMN if len(sys.argv) > 4 and sys.argv[4] == "column" else _lib.Q4_TP_HYBRID
     synthetic = len(sys.argv) > 5 and sys.argv[5] == "synthetic"   # shards generated on the device; `path` holds the same model as a file
     nccl = len(sys.argv) > 5 and sys.argv[5] == "nccl"             # per-op paths: collectives through NCCL instead of the peer push
+    prefill = len(sys.argv) > 5 and sys.argv[5] in ("prefill", "prefill-p2p")   # the first 17 positions in one pass (GEMM path), the rest token by token
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
@@ -28,6 +29,9 @@ def main():
     if nccl:
         comm.attach_nccl(dist)
         comm.set_backend(_lib.Q4_COMM_BACKEND_NCCL)
+    if prefill and sys.argv[5] == "prefill":   # large all-reduces of the prefill through NCCL, the decode steps' small ones stay on the peer push
+        comm.attach_nccl(dist)
+        comm.set_backend(_lib.Q4_COMM_BACKEND_AUTO)
     t = Transformer(path, rank=rank, gpu_count=world, tp_mode=tp_mode, comm=comm.handle,
                     synthetic=(synth.CONFIGS[cfg_name], 7) if synthetic else None)
     vocab = synth.CONFIGS[cfg_name][5]
@@ -41,7 +45,13 @@ def main():
         out = []
         t.reset(tokens, 0)
         dist.barrier()
-        for pos in range(len(tokens)):
+        first = 0
+        if prefill:
+            first = 17
+            t.prefill(first, gen_token=False)
+            t.synchronize()
+            out += [None] * (first - 1) + [t.logits()]
+        for pos in range(first, len(tokens)):
             t.forward(gen_token=False, path=fwd_path)
             if sync_every_token or pos == len(tokens) - 1:
                 t.synchronize()
@@ -52,9 +62,9 @@ def main():
     logits = run(True)
     # run-to-run reproducibility: a second pass with per-token waits and one queued without any (last position compared)
     again, queued = run(True), run(False)
-    same = all((a.view(np.uint16) == b.view(np.uint16)).all() for a, b in zip(logits, again))
+    same = all((a.view(np.uint16) == b.view(np.uint16)).all() for a, b in zip(logits, again) if a is not None)
     same = same and (queued[-1].view(np.uint16) == logits[-1].view(np.uint16)).all()
-    mine = torch.from_numpy(np.stack(logits).view(np.int16).astype(np.int32)).cuda()
+    mine = torch.from_numpy(np.stack([l for l in logits if l is not None]).view(np.int16).astype(np.int32)).cuda()
     gathered = [torch.empty_like(mine) for _ in range(world)]
     dist.all_gather(gathered, mine)
     ok = 1 if same else 0
@@ -70,6 +80,8 @@ def main():
         worst = 0.0
         for pos, tok in enumerate(tokens):
             m.forward(int(tok), pos, order=1)
+            if logits[pos] is None:
+                continue
             ref = m.logits().astype(np.float64)
             got = logits[pos].astype(np.float64)
             err = np.abs(got - ref).max() / np.abs(ref).max()
