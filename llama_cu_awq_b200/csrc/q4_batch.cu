@@ -396,6 +396,27 @@ __global__ void silu_mul_rows_kernel(__half* h, const __half* gate, const __half
     }
 }
 
+// x = y + x * scale: the residual of matmul(QWeight)'s accum form (gpu_kernels.h:237-238) applied to a GEMM result that
+// was written without it (the GEMM's own residual epilogue reads x element by element behind the tile's fp32 sums, which
+// costs more than this pass over two small matrices). fp32 inside, rounded once. n % 8 == 0.
+__global__ void add_residual_rows_kernel(__half* x, const __half* y, float scale, size_t n) {
+    griddep_wait();   // launched with programmatic stream serialisation: wait for the producer, then let the consumer's prologue start
+    griddep_launch_dependents();
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n / 8; i += (size_t)gridDim.x * blockDim.x) {
+        const uint4 xv = reinterpret_cast<const uint4*>(x)[i], yv = reinterpret_cast<const uint4*>(y)[i];
+        const __half2* xh = reinterpret_cast<const __half2*>(&xv);
+        const __half2* yh = reinterpret_cast<const __half2*>(&yv);
+        uint4 o;
+        __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float2 a = __half22float2(xh[j]), b = __half22float2(yh[j]);
+            oh[j] = __floats2half2_rn(b.x + a.x * scale, b.y + a.y * scale);
+        }
+        reinterpret_cast<uint4*>(x)[i] = o;
+    }
+}
+
 // both position words (device, pinned host) to `pos`, in stream order
 __global__ void set_pos_kernel(int* pos_dev, volatile int* pos_pinned, int pos) {
     griddep_wait();   // launched with programmatic stream serialisation: wait for the producer, then let the consumer's prologue start
@@ -687,7 +708,10 @@ static int rows_layers(q4_model* m, cudaStream_t s, int n, __half* kc, __half* v
             launch_pdl(attention_rows_kernel, dim3(heads, n), dim3(kAttWarps * 32), 0, s, r->ATT, r->Q, kc, vc, heads, m->kv_mul, r->row_seq, r->row_pos, seq_stride, loff, m->kv_n);
         // x = o_proj(att) + x / g, summed over the ranks (gpu_kernels.h:237-238, llama2_q4.cu:472-476)
         if (skinny) OP(q4_matmul_q4_rows(s, (uint16_t*)r->X, (const uint16_t*)r->ATT, &L.o.w, n, m->o_kc, dim, (const uint16_t*)r->X, 1.0f / g));
-        else OP(gemm(r->X, r->ATT, l, 3, r->X, 1.0f / g));
+        else {   // the normalised rows in XB are spent: the projection lands there, then x = projection + x / g
+            OP(gemm(r->XB, r->ATT, l, 3, nullptr, 0.f));
+            launch_pdl(add_residual_rows_kernel, dim3(148 * 4), dim3(256), 0, s, r->X, (const __half*)r->XB, 1.0f / g, (size_t)n * dim);
+        }
         OP(rows_all_reduce(m, s, r->X, (size_t)n * dim));
         launch_pdl(rmsnorm_rows_kernel, dim3(n), dim3(kRowThreads), 0, s, r->XB, r->X, (const __half*)L.rms_ffn, dim);
         if (skinny) {
@@ -698,7 +722,8 @@ static int rows_layers(q4_model* m, cudaStream_t s, int n, __half* kc, __half* v
             OP(gemm(r->G, r->XB, l, 4, nullptr, 0.f));
             OP(gemm(r->U, r->XB, l, 5, nullptr, 0.f));
             launch_pdl(silu_mul_rows_kernel, dim3(148 * 4), dim3(256), 0, s, r->G, r->G, r->U, (size_t)n * m->h_kc);
-            OP(gemm(r->X, r->G, l, 6, r->X, 1.0f / g));
+            OP(gemm(r->XB, r->G, l, 6, nullptr, 0.f));
+            launch_pdl(add_residual_rows_kernel, dim3(148 * 4), dim3(256), 0, s, r->X, (const __half*)r->XB, 1.0f / g, (size_t)n * dim);
         }
         OP(rows_all_reduce(m, s, r->X, (size_t)n * dim));
     }

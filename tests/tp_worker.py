@@ -12,7 +12,52 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 from llama_cu_awq_b200 import _lib, synth  # noqa: E402
 from llama_cu_awq_b200.comm import ProcessComm  # noqa: E402
-from llama_cu_awq_b200.model import Transformer  # noqa: E402
+from llama_cu_awq_b200.model import Batch, Transformer  # noqa: E402
+
+
+def batch_mode(t, comm, cfg_name, path, rank, world):
+    """Three sequences decoded together on the sharded model (q4_batch_*): eight prompt positions, then four generated ones;
+    each sequence's logits against the single-GPU oracle fed the same ids, every rank holding the same bits."""
+    vocab = synth.CONFIGS[cfg_name][5]
+    prompts = np.random.default_rng(1).integers(3, vocab, size=(3, 8), dtype=np.int32)
+    b = Batch(t, 3)
+    runs = []
+    for _ in range(2):   # twice: the step graph is replayed, and the results must repeat bit for bit
+        b.reset(prompts)
+        dist.barrier()
+        for _ in range(12):
+            b.forward()
+        t.synchronize()
+        runs.append((b.logits().copy(), b.tokens(13).copy()))
+    assert t.status() == 0 and comm.status() == 0
+    ok = 1
+    if not ((runs[0][0].view(np.uint16) == runs[1][0].view(np.uint16)).all() and (runs[0][1] == runs[1][1]).all()):
+        print(f"rank {rank}: batched decode differs between two runs")
+        ok = 0
+    logits, toks = runs[0]
+    mine = torch.from_numpy(logits.view(np.int16).astype(np.int32)).cuda()
+    gathered = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(gathered, mine)
+    if rank == 0:
+        from oracle import q4_oracle as O
+        ok = ok if all(torch.equal(gathered[0], g) for g in gathered[1:]) else 0
+        image = open(path, "rb").read()
+        worst = 0.0
+        for s in range(3):
+            assert (toks[s, :8] == prompts[s]).all()
+            m = O.Model(image)
+            for pos in range(12):
+                m.forward(int(toks[s, pos]), pos, order=1)
+            ref, got = m.logits().astype(np.float64), logits[s].astype(np.float64)
+            err = np.abs(got - ref).max() / np.abs(ref).max()
+            cos = got @ ref / (np.linalg.norm(got) * np.linalg.norm(ref))
+            worst = max(worst, err)
+            if err > 1e-2 or cos < 0.999:
+                print(f"sequence {s}: rel err {err:.3e} cos {cos:.6f}")
+                ok = 0
+        print(f"TP{world} {cfg_name} batched decode: worst rel err vs single-GPU oracle {worst:.3e}; ranks identical: {bool(ok)}")
+    b.close()
+    return ok
 
 
 def main():
@@ -41,6 +86,16 @@ def main():
         assert t.best_path() == 2, "the fused path must serve this sharded model"
     dist.barrier()   # the fused path exchanges activations between the ranks' kernels: all ranks prepared before any launches
     torch.cuda.synchronize()
+    if len(sys.argv) > 5 and sys.argv[5] == "batch":
+        ok = batch_mode(t, comm, cfg_name, path, rank, world)
+        flag = torch.tensor([ok], device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        t.close()
+        comm.close()
+        dist.barrier()
+        dist.destroy_process_group()
+        sys.exit(0 if int(flag.item()) == 1 else 1)
+
     def run(sync_every_token):
         out = []
         t.reset(tokens, 0)
