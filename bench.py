@@ -265,8 +265,9 @@ def time_generations(t, prompt, fwd_path, steps, warmup, barrier, torch, dist, o
     return (STEPS_PER_GEN - 1) * steps / (total_ms / 1e3), total_ms, tokens
 
 
-def op_kernels(cfg, torch):
-    """Every W4 op of one layer (and the single 4096 x 4096 layer) timed alone over distinct matrices."""
+def op_kernels(cfg, torch, rows=0):
+    """Every W4 op of one layer (and the single 4096 x 4096 layer) timed alone over distinct matrices: the batch-1 kernels
+    (rows = 0) or their few-rows forms for batched decode with `rows` rows of x."""
     from llama_cu_awq_b200 import _lib
     L = _lib.lib()
     out = {}
@@ -282,13 +283,19 @@ def op_kernels(cfg, torch):
             sc = (torch.rand((N, gg), device="cuda", generator=g) * 0.018 + 0.002).half()
             keep += [w, z, sc]
             mats[i] = _lib.q4_qweight(w.data_ptr(), z.data_ptr(), sc.data_ptr())
-        x = torch.randn(K, device="cuda", generator=g).half()
-        ys = [torch.zeros(4 * N, dtype=torch.float16, device="cuda") for _ in range(3)]
+        x = torch.randn(max(rows, 1) * K, device="cuda", generator=g).half()
+        ys = [torch.zeros(max(4, rows) * N, dtype=torch.float16, device="cuda") for _ in range(3)]
         pos = torch.zeros(1, dtype=torch.int32, device="cuda")
         us, nbytes = C.c_double(), C.c_double()
         torch.cuda.synchronize()
-        st = L.q4_time_q4_op(C.c_void_p(s.cuda_stream), kind, C.c_void_p(ys[0].data_ptr()), C.c_void_p(ys[1].data_ptr()), C.c_void_p(ys[2].data_ptr()),
-                             C.c_void_p(x.data_ptr()), mats, nmat, K, N, 20, C.c_void_p(pos.data_ptr()), C.byref(us), C.byref(nbytes))
+        if rows:
+            if K % 128 or N % 32:
+                continue
+            st = L.q4_time_q4_rows_op(C.c_void_p(s.cuda_stream), kind, rows, C.c_void_p(ys[0].data_ptr()), C.c_void_p(ys[1].data_ptr()), C.c_void_p(ys[2].data_ptr()),
+                                      C.c_void_p(x.data_ptr()), mats, nmat, K, N, 20, C.byref(us), C.byref(nbytes))
+        else:
+            st = L.q4_time_q4_op(C.c_void_p(s.cuda_stream), kind, C.c_void_p(ys[0].data_ptr()), C.c_void_p(ys[1].data_ptr()), C.c_void_p(ys[2].data_ptr()),
+                                 C.c_void_p(x.data_ptr()), mats, nmat, K, N, 20, C.c_void_p(pos.data_ptr()), C.byref(us), C.byref(nbytes))
         if st != 0:
             out[name] = {"error": st}
             continue
@@ -377,7 +384,7 @@ def allreduce_table(comm, dist, torch):
     return out
 
 
-def prefill_and_batch(t, cfg, fwd_path, value, rank, world, dist, torch, barrier, pk):
+def prefill_and_batch(t, cfg, fwd_path, value, rank, world, dist, torch, barrier, pk, per_op_anchor=True):
     """The two callers either side of the batch-1 decode step on the same model: a 512-token prompt processed in one
     pass (W4 GEMMs on the tensor cores) against the same 512 positions fed token by token, and eight sequences decoded
     together against eight times the batch-1 rate."""
@@ -408,16 +415,31 @@ def prefill_and_batch(t, cfg, fwd_path, value, rank, world, dist, torch, barrier
         for _ in range(n_pre):
             t.forward(gen_token=False, path=fwd_path)
 
+    def by_token_per_op():
+        for _ in range(n_pre):
+            t.forward(gen_token=False, path=1)
+
     ms_pre = timed(lambda: t.prefill(n_pre, gen_token=False), 4)
     one_pass = t.logits()
     ms_tok = timed(by_token, 2)
-    rel, cos = compare(one_pass, t.logits())
+    fused = t.logits()
+    if per_op_anchor:
+        timed(by_token_per_op, 2)
+        per_op = t.logits()   # the per-op kernels follow the reference's arithmetic op by op: the anchor of this comparison
+        rel, cos = compare(one_pass, per_op)
+        rel_f, cos_f = compare(fused, per_op)
+    else:
+        rel, cos = compare(one_pass, fused)
+        rel_f, cos_f = None, None
     n_layers, dim, hidden = cfg[2], cfg[0], cfg[1]
     kv_dim = dim * cfg[4] // cfg[3]
     flops = 2.0 * n_pre * n_layers * (2 * dim * dim + 2 * dim * kv_dim + 3 * dim * hidden) / world
     out["prefill_512"] = {"ms": ms_pre, "tok_s": n_pre / ms_pre * 1e3, "ms_token_by_token": ms_tok, "speedup_vs_token_by_token": ms_tok / ms_pre,
                           "w4_gemm_tflops_per_gpu": flops / (ms_pre * 1e-3) / 1e12, "frac_of_bf16_sustained": flops / (ms_pre * 1e-3) / 1e12 / pk.get("bf16_tflops_sustained", pk["bf16_tflops"]),
-                          "last_logits_vs_token_by_token": {"max_rel": rel, "cosine": cos}, "status": t.status()}
+                          # position 511 of a 32-layer random-weight model: every path (this one, the fused token kernel) lies this far from
+                          # the per-op kernels, whose own distance to the oracle grows the same way with depth and position
+                          ("last_logits_vs_per_op_path" if per_op_anchor else "last_logits_vs_fused_token_path"): {"max_rel": rel, "cosine": cos},
+                          "fused_token_path_vs_per_op_path": {"max_rel": rel_f, "cosine": cos_f}, "status": t.status()}
 
     n_seq, steps = 8, 64
     b = Batch(t, n_seq)
@@ -474,6 +496,13 @@ def extra_model(name, rank, world, dist, torch, barrier, pk):
             mean_bytes = sum(t.token_bytes(p) for p in range(STEPS_PER_GEN - 1)) / (STEPS_PER_GEN - 1)
             res.update({"tok_s": toks, "us_per_token": 1e6 / toks, "bytes_per_token_per_gpu": mean_bytes,
                         "token_roofline_frac": mean_bytes * toks / 1e9 / pk["hbm_gbs"], "status": st})
+            try:   # the same model's 512-token prefill and batch-8 decode at this degree
+                if _lib.lib().q4_comm_nccl_available():
+                    comm.attach_nccl(dist)
+                    comm.set_backend(_lib.Q4_COMM_BACKEND_AUTO)
+                res.update(prefill_and_batch(t, cfg, 2, toks, rank, world, dist, torch, barrier, pk, per_op_anchor=False))
+            except Exception as e:
+                res["prefill_batch_error"] = str(e)[:300]
         elif which == "test_build":
             res["exchange"] = {"us_per_token": 1e6 / toks, "build": "test build of the library (same kernel plus its measurement switches)"}
         else:
@@ -612,6 +641,7 @@ def main():
     extra = {}
     if world == 1 and not args.no_extras:
         extra["kernels"] = op_kernels(cfg, torch)
+        extra["kernels_rows8"] = op_kernels(cfg, torch, rows=8)
         extra["gemm_tcgen05"] = gemm_table(torch)
     if fwd_path == 2:
         launches_per_token = 1  # one persistent cooperative kernel per token

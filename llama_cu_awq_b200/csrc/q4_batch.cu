@@ -109,17 +109,11 @@ __global__ void __launch_bounds__(256) rope_store_rows_kernel(__half* q, const _
                                                               int head_size, const int* row_seq, const int* row_pos, long long seq_stride, long long loff, float theta) {
     griddep_wait();   // launched with programmatic stream serialisation: wait for the producer, then let the consumer's prologue start
     griddep_launch_dependents();
-    __shared__ float s_cos[128], s_sin[128];
+    __shared__ float2 table[128];
     const int m = blockIdx.x;
     const int pos = row_pos[m];
     const int half_hs = head_size / 2;
-    for (int i = threadIdx.x; i < half_hs; i += blockDim.x) {
-        const int head_dim = (i * 2) % head_size;
-        const float freq = 1.0f / powf(theta, head_dim / (float)head_size);
-        const float val = pos * freq;
-        s_cos[i] = cosf(val);
-        s_sin[i] = sinf(val);
-    }
+    for (int i = threadIdx.x; i < half_hs; i += blockDim.x) table[i] = rope_cos_sin(pos, i, head_size, theta);
     __syncthreads();
     __half* qr = q + (size_t)m * n_heads * head_size;
     const size_t src0 = (size_t)m * n_kv_heads * head_size;
@@ -127,18 +121,13 @@ __global__ void __launch_bounds__(256) rope_store_rows_kernel(__half* q, const _
     const int h_first = blockIdx.y * kRopeHeads, h_end = min(h_first + kRopeHeads, n_heads + n_kv_heads);
     for (int e = threadIdx.x; e < (h_end - h_first) * half_hs; e += blockDim.x) {
         const int hh = h_first + e / half_hs, i = e % half_hs;
-        const float fcr = s_cos[i], fci = s_sin[i];
         if (hh < n_heads) {
             __half* p = qr + (size_t)hh * head_size;
-            const float q0 = __half2float(p[i]), q1 = __half2float(p[i + half_hs]);
-            p[i] = __float2half(q0 * fcr - q1 * fci);
-            p[i + half_hs] = __float2half(q0 * fci + q1 * fcr);
+            rope_rotate(p + i, p + i + half_hs, p + i, p + i + half_hs, table[i]);
         } else {
             const int h = hh - n_heads;
             const size_t src = src0 + (size_t)h * head_size, dst = dst0 + (size_t)h * head_size;
-            const float k0 = __half2float(k[src + i]), k1 = __half2float(k[src + i + half_hs]);
-            kc[dst + i] = __float2half(k0 * fcr - k1 * fci);
-            kc[dst + i + half_hs] = __float2half(k0 * fci + k1 * fcr);
+            rope_rotate(k + src + i, k + src + i + half_hs, kc + dst + i, kc + dst + i + half_hs, table[i]);
             vc[dst + i] = v[src + i];
             vc[dst + i + half_hs] = v[src + i + half_hs];
         }
@@ -662,13 +651,15 @@ static int rows_prepare(q4_model* m, int rows) {
     return Q4_OK;
 }
 
-// Sum of the ranks' partial [count] vectors: NCCL when it is attached and the communicator's choice says so (large messages),
-// else the one-shot peer push in pieces its inbox holds.
-static int rows_all_reduce(q4_model* m, cudaStream_t s, __half* buf, size_t count) {
+// Sum of the ranks' partial [count] vectors: NCCL when it is attached, the communicator's choice says so (large messages)
+// and the caller allows it (a prompt's rows); else the one-shot peer push in pieces its inbox holds (always for the
+// batched-decode step, which is replayed from a CUDA graph and keeps to kernels of this library).
+static int rows_all_reduce(q4_model* m, cudaStream_t s, __half* buf, size_t count, bool allow_nccl) {
     if (m->g == 1) return Q4_OK;
     for (size_t at = 0; at < count;) {
-        const size_t n = q4_comm_prefers_nccl(m->comm, (int)std::min<size_t>(count - at, (size_t)1 << 30)) ? count - at : std::min<size_t>(count - at, (size_t)Q4_COMM_MAX_HALFS);
-        if (int e = q4_all_reduce(m->comm, s, (uint16_t*)(buf + at), (int)n)) return e;
+        const bool nccl = allow_nccl && q4_comm_prefers_nccl(m->comm, (int)std::min<size_t>(count - at, (size_t)1 << 30));
+        const size_t n = nccl ? count - at : std::min<size_t>(count - at, (size_t)Q4_COMM_MAX_HALFS);
+        if (int e = nccl ? q4_all_reduce(m->comm, s, (uint16_t*)(buf + at), (int)n) : q4_all_reduce_peer_push(m->comm, s, (uint16_t*)(buf + at), (int)n)) return e;
         at += n;
     }
     return Q4_OK;
@@ -712,7 +703,7 @@ static int rows_layers(q4_model* m, cudaStream_t s, int n, __half* kc, __half* v
             OP(gemm(r->XB, r->ATT, l, 3, nullptr, 0.f));
             launch_pdl(add_residual_rows_kernel, dim3(148 * 4), dim3(256), 0, s, r->X, (const __half*)r->XB, 1.0f / g, (size_t)n * dim);
         }
-        OP(rows_all_reduce(m, s, r->X, (size_t)n * dim));
+        OP(rows_all_reduce(m, s, r->X, (size_t)n * dim, pos0 >= 0));
         launch_pdl(rmsnorm_rows_kernel, dim3(n), dim3(kRowThreads), 0, s, r->XB, r->X, (const __half*)L.rms_ffn, dim);
         if (skinny) {
             // gate and up stay in fp32 until silu(gate) * up, as in ffn_matvec_silu_kernel (gpu_kernels.h:278-281)
@@ -725,7 +716,7 @@ static int rows_layers(q4_model* m, cudaStream_t s, int n, __half* kc, __half* v
             OP(gemm(r->XB, r->G, l, 6, nullptr, 0.f));
             launch_pdl(add_residual_rows_kernel, dim3(148 * 4), dim3(256), 0, s, r->X, (const __half*)r->XB, 1.0f / g, (size_t)n * dim);
         }
-        OP(rows_all_reduce(m, s, r->X, (size_t)n * dim));
+        OP(rows_all_reduce(m, s, r->X, (size_t)n * dim, pos0 >= 0));
     }
     Q4_CUDA_TRY(cudaGetLastError());
 #undef OP

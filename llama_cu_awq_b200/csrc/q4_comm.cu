@@ -345,6 +345,11 @@ extern "C" int q4_all_reduce(q4_comm* comm, void* stream, uint16_t* buf, int cou
     return comm_launch(comm, (cudaStream_t)stream, (__half*)buf, nullptr, count, 0);
 }
 
+int q4_all_reduce_peer_push(q4_comm* comm, void* stream, uint16_t* buf, int count) {
+    if (comm && comm->gpu_count == 1) return Q4_OK;
+    return comm_launch(comm, (cudaStream_t)stream, (__half*)buf, nullptr, count, 0);
+}
+
 extern "C" int q4_all_gather(q4_comm* comm, void* stream, const uint16_t* send, uint16_t* recv, int sendcount) {
     if (!send) return Q4_ERR_INVALID;
     if (comm && comm->gpu_count == 1) {

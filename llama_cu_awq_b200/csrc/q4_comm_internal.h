@@ -22,3 +22,5 @@ int q4_comm_rank(const q4_comm* c);
 Q4LLArea* q4_comm_ll_area(const q4_comm* c, int peer);
 // True when a message of `count` halfs goes through NCCL on this communicator (backend choice, NCCL attached).
 bool q4_comm_prefers_nccl(const q4_comm* c, int count);
+// The in-place sum all-reduce through the peer-push kernel whatever the backend setting (count <= Q4_COMM_MAX_HALFS).
+int q4_all_reduce_peer_push(q4_comm* c, void* stream, uint16_t* buf, int count);

@@ -102,6 +102,22 @@ __device__ __forceinline__ float h2sum(__half2 h) {
     return f.x + f.y;
 }
 
+// Rotation of pair `pair` (elements pair and pair + head_size / 2) of a head at position `pos`: angle =
+// pos / theta^(2 pair / head_size), evaluated in fp32 with powf, cosf and sinf exactly as RoPERotation_kernel evaluates it
+// (gpu_kernels.h:346-350), so that rotated values round as the reference's do. Returns (cos, sin).
+__device__ __forceinline__ float2 rope_cos_sin(int pos, int pair, int head_size, float theta) {
+    const int even_dim = (2 * pair) % head_size;
+    const float inv_wavelength = 1.0f / powf(theta, even_dim / (float)head_size);
+    const float angle = pos * inv_wavelength;
+    return make_float2(cosf(angle), sinf(angle));
+}
+// (lo, hi) <- (lo cos - hi sin, lo sin + hi cos), fp32 inside, each rounded to fp16 once
+__device__ __forceinline__ void rope_rotate(const __half* src_lo, const __half* src_hi, __half* dst_lo, __half* dst_hi, float2 cs) {
+    const float a = __half2float(*src_lo), b = __half2float(*src_hi);
+    *dst_lo = __float2half(a * cs.x - b * cs.y);
+    *dst_hi = __float2half(a * cs.y + b * cs.x);
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

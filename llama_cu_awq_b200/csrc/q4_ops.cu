@@ -74,28 +74,27 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(__half* o, const __half* 
     }
 }
 
-// rotate-half RoPE, pairs (i, i + head_size/2): gpu_kernels.h:340-363. One block per head.
-__global__ void rope_kernel(__half* sq, __half* sk_base, int num_kv_heads, int head_size, const int* pPos, long long loff,
-                            float theta) {
+// RoPERotation_kernel (gpu_kernels.h:340-363): rotate-half RoPE of the query heads in place and of the key heads of cache
+// row `pos`. A block takes kRopeHeadsPerBlock heads; the angles depend on the position only, so the block evaluates the
+// head_size / 2 (cos, sin) pairs once into shared memory and every head of the block reuses them. head_size <= 512.
+constexpr int kRopeHeadsPerBlock = 4;
+__global__ void __launch_bounds__(256) rope_kernel(__half* q, __half* key_cache, int num_heads, int num_kv_heads, int head_size, const int* pPos,
+                                                   long long loff, float theta) {
     griddep_wait();
     griddep_launch_dependents();
-    const int pos = *pPos;
-    const int h = blockIdx.x;
-    const int half_hs = head_size / 2;
-    for (int i = threadIdx.x; i < half_hs; i += blockDim.x) {
-        const int head_dim = (i * 2) % head_size;
-        const float freq = 1.0f / powf(theta, head_dim / (float)head_size);
-        const float val = pos * freq;
-        const float fcr = cosf(val), fci = sinf(val);
-        __half* q = sq + (size_t)h * head_size;
-        const float q0 = __half2float(q[i]), q1 = __half2float(q[i + half_hs]);
-        q[i] = __float2half(q0 * fcr - q1 * fci);
-        q[i + half_hs] = __float2half(q0 * fci + q1 * fcr);
-        if (h < num_kv_heads) {
-            __half* k = sk_base + loff + (long long)pos * num_kv_heads * head_size + (size_t)h * head_size;
-            const float k0 = __half2float(k[i]), k1 = __half2float(k[i + half_hs]);
-            k[i] = __float2half(k0 * fcr - k1 * fci);
-            k[i + half_hs] = __float2half(k0 * fci + k1 * fcr);
+    __shared__ float2 table[256];
+    const int pos = *pPos, pairs = head_size / 2;
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) table[i] = rope_cos_sin(pos, i, head_size, theta);
+    __syncthreads();
+    __half* key_row = key_cache + loff + (long long)pos * num_kv_heads * head_size;
+    const int first = blockIdx.x * kRopeHeadsPerBlock, last = min(first + kRopeHeadsPerBlock, num_heads);
+    for (int e = threadIdx.x; e < (last - first) * pairs; e += blockDim.x) {
+        const int head = first + e / pairs, i = e % pairs;
+        __half* qh = q + (size_t)head * head_size;
+        rope_rotate(qh + i, qh + i + pairs, qh + i, qh + i + pairs, table[i]);
+        if (head < num_kv_heads) {
+            __half* kh = key_row + (size_t)head * head_size;
+            rope_rotate(kh + i, kh + i + pairs, kh + i, kh + i + pairs, table[i]);
         }
     }
 }
@@ -250,8 +249,9 @@ extern "C" int q4_rmsnorm(void* stream, uint16_t* o, const uint16_t* x, const ui
 extern "C" int q4_rope(void* stream, uint16_t* q, uint16_t* k, int num_heads, int num_kv_heads, int head_size, const int* pPos,
                        int loff, float rope_theta) {
     if (!q || !k || !pPos || num_heads <= 0 || head_size <= 0 || (head_size & 1) || num_kv_heads > num_heads) return Q4_ERR_INVALID;
-    Q4Launch L(dim3(num_heads), dim3(head_size / 2 > 1024 ? 1024 : head_size / 2), 0, (cudaStream_t)stream);
-    Q4_CUDA_TRY(cudaLaunchKernelEx(&L.cfg, rope_kernel, (__half*)q, (__half*)k, num_kv_heads, head_size, pPos, (long long)loff, rope_theta));
+    if (head_size > 512) return Q4_ERR_UNSUPPORTED_SIZE;
+    Q4Launch L(dim3(q4_div_up(num_heads, kRopeHeadsPerBlock)), dim3(256), 0, (cudaStream_t)stream);
+    Q4_CUDA_TRY(cudaLaunchKernelEx(&L.cfg, rope_kernel, (__half*)q, (__half*)k, num_heads, num_kv_heads, head_size, pPos, (long long)loff, rope_theta));
     return Q4_OK;
 }
 
