@@ -19,12 +19,16 @@ namespace {
 
 constexpr int kRowThreads = 256;
 
-// Every kernel of this file is launched with programmatic stream serialisation and starts with griddepcontrol.wait +
-// launch_dependents: its successor (often a weight-streaming kernel whose first loads do not depend on it) may begin its
-// prologue while this one runs, and waits for this one's completion before it touches anything produced here.
+// Every kernel of this file starts with griddepcontrol.wait + launch_dependents, so it may be launched with programmatic
+// stream serialisation: its successor (often a weight-streaming kernel whose first loads do not depend on it) then begins
+// its prologue while this one runs, and waits for this one's completion before it touches anything produced here. The
+// batched-decode step (a handful of rows, latency-bound small kernels) is launched that way. A prompt's rows are not:
+// with hundreds of rows the overlap buys nothing measurable, and with the rotation and attention kernels launched that way
+// two runs of the same 512-token prompt did not always give the same bits on this GPU and driver (about one run in ten
+// differed in the last bits of a few logits; cause not found), so those launches keep plain stream order.
 template <typename... KArgs, typename... Args>
-cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
-    Q4Launch L(grid, block, smem, s);
+cudaError_t launch_rows(bool overlap, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+    Q4Launch L(grid, block, smem, s, overlap);
     return cudaLaunchKernelEx(&L.cfg, kernel, KArgs(args)...);
 }
 
@@ -680,10 +684,11 @@ static int rows_layers(q4_model* m, cudaStream_t s, int n, __half* kc, __half* v
                                              r->ws, r->ws_bytes);
     };
     const bool skinny = n <= kSkinnyRows;
+    const bool overlap = pos0 < 0;   // batched decode: programmatic dependent launches (see launch_rows)
     for (int l = 0; l < c.n_layers; l++) {
         const DevLayer& L = m->layers[l];
         const long long loff = (long long)l * c.seq_len * m->kv_n;
-        launch_pdl(rmsnorm_rows_kernel, dim3(n), dim3(kRowThreads), 0, s, r->XB, r->X, (const __half*)L.rms_att, dim);
+        launch_rows(overlap, rmsnorm_rows_kernel, dim3(n), dim3(kRowThreads), 0, s, r->XB, r->X, (const __half*)L.rms_att, dim);
         if (skinny) {
             OP(q4_qkv_matmul_rows(s, (uint16_t*)r->Q, (uint16_t*)r->K, (uint16_t*)r->V, (const uint16_t*)r->XB, &L.q.w, &L.k.w, &L.v.w, n, dim, m->q_n, m->kv_n));
         } else {
@@ -691,20 +696,20 @@ static int rows_layers(q4_model* m, cudaStream_t s, int n, __half* kc, __half* v
             OP(gemm(r->K, r->XB, l, 1, nullptr, 0.f));
             OP(gemm(r->V, r->XB, l, 2, nullptr, 0.f));
         }
-        launch_pdl(rope_store_rows_kernel, dim3(n, q4_div_up(heads + kv_heads, kRopeHeads)), dim3(256), 0, s, r->Q, r->K, r->V, kc, vc, heads, kv_heads, hs, r->row_seq, r->row_pos, seq_stride,
+        launch_rows(overlap, rope_store_rows_kernel, dim3(n, q4_div_up(heads + kv_heads, kRopeHeads)), dim3(256), 0, s, r->Q, r->K, r->V, kc, vc, heads, kv_heads, hs, r->row_seq, r->row_pos, seq_stride,
                                                                               loff, c.rope_theta);
         if (pos0 >= 0 && n > 16)
-            launch_pdl(attention_prefill_kernel, dim3(dim3(heads, q4_div_up(n, kAtRows))), dim3(128), 0, s, r->ATT, r->Q, kc + loff, vc + loff, heads, m->kv_mul, n, pos0, m->kv_n);
+            launch_rows(overlap, attention_prefill_kernel, dim3(dim3(heads, q4_div_up(n, kAtRows))), dim3(128), 0, s, r->ATT, r->Q, kc + loff, vc + loff, heads, m->kv_mul, n, pos0, m->kv_n);
         else
-            launch_pdl(attention_rows_kernel, dim3(heads, n), dim3(kAttWarps * 32), 0, s, r->ATT, r->Q, kc, vc, heads, m->kv_mul, r->row_seq, r->row_pos, seq_stride, loff, m->kv_n);
+            launch_rows(overlap, attention_rows_kernel, dim3(heads, n), dim3(kAttWarps * 32), 0, s, r->ATT, r->Q, kc, vc, heads, m->kv_mul, r->row_seq, r->row_pos, seq_stride, loff, m->kv_n);
         // x = o_proj(att) + x / g, summed over the ranks (gpu_kernels.h:237-238, llama2_q4.cu:472-476)
         if (skinny) OP(q4_matmul_q4_rows(s, (uint16_t*)r->X, (const uint16_t*)r->ATT, &L.o.w, n, m->o_kc, dim, (const uint16_t*)r->X, 1.0f / g));
         else {   // the normalised rows in XB are spent: the projection lands there, then x = projection + x / g
             OP(gemm(r->XB, r->ATT, l, 3, nullptr, 0.f));
-            launch_pdl(add_residual_rows_kernel, dim3(148 * 4), dim3(256), 0, s, r->X, (const __half*)r->XB, 1.0f / g, (size_t)n * dim);
+            launch_rows(overlap, add_residual_rows_kernel, dim3(148 * 4), dim3(256), 0, s, r->X, (const __half*)r->XB, 1.0f / g, (size_t)n * dim);
         }
         OP(rows_all_reduce(m, s, r->X, (size_t)n * dim, pos0 >= 0));
-        launch_pdl(rmsnorm_rows_kernel, dim3(n), dim3(kRowThreads), 0, s, r->XB, r->X, (const __half*)L.rms_ffn, dim);
+        launch_rows(overlap, rmsnorm_rows_kernel, dim3(n), dim3(kRowThreads), 0, s, r->XB, r->X, (const __half*)L.rms_ffn, dim);
         if (skinny) {
             // gate and up stay in fp32 until silu(gate) * up, as in ffn_matvec_silu_kernel (gpu_kernels.h:278-281)
             OP(q4_ffn_silu_rows(s, (uint16_t*)r->G, (const uint16_t*)r->XB, &L.gate.w, &L.up.w, n, dim, m->h_kc));
@@ -712,9 +717,9 @@ static int rows_layers(q4_model* m, cudaStream_t s, int n, __half* kc, __half* v
         } else {
             OP(gemm(r->G, r->XB, l, 4, nullptr, 0.f));
             OP(gemm(r->U, r->XB, l, 5, nullptr, 0.f));
-            launch_pdl(silu_mul_rows_kernel, dim3(148 * 4), dim3(256), 0, s, r->G, r->G, r->U, (size_t)n * m->h_kc);
+            launch_rows(overlap, silu_mul_rows_kernel, dim3(148 * 4), dim3(256), 0, s, r->G, r->G, r->U, (size_t)n * m->h_kc);
             OP(gemm(r->XB, r->G, l, 6, nullptr, 0.f));
-            launch_pdl(add_residual_rows_kernel, dim3(148 * 4), dim3(256), 0, s, r->X, (const __half*)r->XB, 1.0f / g, (size_t)n * dim);
+            launch_rows(overlap, add_residual_rows_kernel, dim3(148 * 4), dim3(256), 0, s, r->X, (const __half*)r->XB, 1.0f / g, (size_t)n * dim);
         }
         OP(rows_all_reduce(m, s, r->X, (size_t)n * dim, pos0 >= 0));
     }
@@ -735,13 +740,14 @@ extern "C" int q4_model_prefill(q4_model* m, void* stream, int n_tokens, int gen
     q4_rows* r = m->rows;
     cudaStream_t s = (cudaStream_t)stream;
     const int n = n_tokens;
-    launch_pdl(iota_rows_kernel, dim3(q4_div_up(n, 256)), dim3(256), 0, s, r->row_seq, r->row_pos, n, 0, pos0, 0);
-    launch_pdl(embed_rows_kernel, dim3(n), dim3(kRowThreads), 0, s, r->X, (const __half*)m->emb, c.dim, (const int*)m->shared->tokens, 0, r->row_seq, r->row_pos, c.vocab_size);
+    const bool overlap = false;
+    launch_rows(overlap, iota_rows_kernel, dim3(q4_div_up(n, 256)), dim3(256), 0, s, r->row_seq, r->row_pos, n, 0, pos0, 0);
+    launch_rows(overlap, embed_rows_kernel, dim3(n), dim3(kRowThreads), 0, s, r->X, (const __half*)m->emb, c.dim, (const int*)m->shared->tokens, 0, r->row_seq, r->row_pos, c.vocab_size);
     if (int e = rows_layers(m, s, n, (__half*)m->kc, (__half*)m->vc, 0, pos0)) return e;
     // the last row goes on through the batch-1 tail (llama2_q4.cu:528-537, sampler.h:77-84): final norm, classifier,
     // [all-gather], hand-off; the position words are moved to that row first, the hand-off then steps them past it
     Q4_CUDA_TRY(cudaMemcpyAsync(m->x, r->X + (size_t)(n - 1) * c.dim, 2 * (size_t)c.dim, cudaMemcpyDeviceToDevice, s));
-    launch_pdl(set_pos_kernel, dim3(1), dim3(1), 0, s, m->pos, &m->shared->pos, pos0 + n - 1);
+    launch_rows(overlap, set_pos_kernel, dim3(1), dim3(1), 0, s, m->pos, &m->shared->pos, pos0 + n - 1);
     int e;
     if ((e = q4_rmsnorm(s, m->x, m->x, m->rms_final, c.dim)) != Q4_OK) return e;
     if ((e = q4_matmul_f16(s, m->logits + (size_t)m->rank * m->v_n, m->x, m->wcls, c.dim, m->v_n, 1.0f)) != Q4_OK) return e;
@@ -851,25 +857,26 @@ static int batch_step(q4_batch* b, cudaStream_t s) {
     q4_rows* r = m->rows;
     const q4_config& c = m->cfg;
     const int n = b->n_seq;
-    launch_pdl(iota_rows_kernel, dim3(1), dim3(32), 0, s, r->row_seq, nullptr, n, 0, 0, 1);
+    const bool overlap = true;
+    launch_rows(overlap, iota_rows_kernel, dim3(1), dim3(32), 0, s, r->row_seq, nullptr, n, 0, 0, 1);
     Q4_CUDA_TRY(cudaMemcpyAsync(r->row_pos, b->pos, sizeof(int) * n, cudaMemcpyDeviceToDevice, s));
-    launch_pdl(embed_rows_kernel, dim3(n), dim3(kRowThreads), 0, s, r->X, (const __half*)m->emb, c.dim, b->tokens, b->max_len + 1, r->row_seq, r->row_pos, c.vocab_size);
+    launch_rows(overlap, embed_rows_kernel, dim3(n), dim3(kRowThreads), 0, s, r->X, (const __half*)m->emb, c.dim, b->tokens, b->max_len + 1, r->row_seq, r->row_pos, c.vocab_size);
     if (int e = rows_layers(m, s, n, b->kc, b->vc, b->seq_stride, -1)) return e;
-    launch_pdl(rmsnorm_rows_kernel, dim3(n), dim3(kRowThreads), 0, s, b->xf, r->X, (const __half*)m->rms_final, c.dim);
+    launch_rows(overlap, rmsnorm_rows_kernel, dim3(n), dim3(kRowThreads), 0, s, b->xf, r->X, (const __half*)m->rms_final, c.dim);
     const size_t smem = 2 * (size_t)n * c.dim;
     __half* cls_out = m->g == 1 ? b->logits : b->part;   // TP: every rank computes its vocabulary slice of every row; the slices are gathered row by row
     const int cls_stride = m->g == 1 ? c.vocab_size : m->v_n;
     if (c.dim % 32 == 0 && m->v_n % 16 == 0) {
-        if (n <= 8) launch_pdl(classifier_rows_kernel<1>, dim3(q4_div_up(m->v_n / 16, 8)), dim3(256), 0, s, cls_out, b->xf, (const __half*)m->wcls, c.dim, m->v_n, n, cls_stride);
-        else launch_pdl(classifier_rows_kernel<2>, dim3(q4_div_up(m->v_n / 16, 8)), dim3(256), 0, s, cls_out, b->xf, (const __half*)m->wcls, c.dim, m->v_n, n, cls_stride);
+        if (n <= 8) launch_rows(overlap, classifier_rows_kernel<1>, dim3(q4_div_up(m->v_n / 16, 8)), dim3(256), 0, s, cls_out, b->xf, (const __half*)m->wcls, c.dim, m->v_n, n, cls_stride);
+        else launch_rows(overlap, classifier_rows_kernel<2>, dim3(q4_div_up(m->v_n / 16, 8)), dim3(256), 0, s, cls_out, b->xf, (const __half*)m->wcls, c.dim, m->v_n, n, cls_stride);
     } else {
-        launch_pdl(matvec_f16_rows_kernel, dim3(148 * 2), dim3(256), smem, s, cls_out, b->xf, (const __half*)m->wcls, c.dim, m->v_n, n, cls_stride);
+        launch_rows(overlap, matvec_f16_rows_kernel, dim3(148 * 2), dim3(256), smem, s, cls_out, b->xf, (const __half*)m->wcls, c.dim, m->v_n, n, cls_stride);
     }
     if (m->g > 1) {
         for (int i = 0; i < n; i++)
             if (int e = q4_all_gather(m->comm, s, (const uint16_t*)(b->part + (size_t)i * m->v_n), (uint16_t*)(b->logits + (size_t)i * c.vocab_size), m->v_n)) return e;
     }
-    launch_pdl(argmax_rows_kernel, dim3(n), dim3(1024), 0, s, b->logits, c.vocab_size, b->tokens, b->max_len + 1, b->pos, b->n_prompt);
+    launch_rows(overlap, argmax_rows_kernel, dim3(n), dim3(1024), 0, s, b->logits, c.vocab_size, b->tokens, b->max_len + 1, b->pos, b->n_prompt);
     Q4_CUDA_TRY(cudaGetLastError());
     return Q4_OK;
 }

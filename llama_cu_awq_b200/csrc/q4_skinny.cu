@@ -59,89 +59,81 @@ __device__ __forceinline__ void unpack8(uint32_t w, uint32_t zlo, uint32_t zhi, 
 }
 
 #ifndef SK_WARPS
-#define SK_WARPS 8
+#define SK_WARPS 16
 #endif
-#ifndef SK_D11
-#define SK_D11 4
-#endif
-#ifndef SK_D12
-#define SK_D12 3
+#ifndef SK_D1
+#define SK_D1 3
 #endif
 #ifndef SK_D2
 #define SK_D2 2
 #endif
-#ifndef SK_MINB
-#define SK_MINB 2
-#endif
-constexpr int kWarps = SK_WARPS;
+// warps of a CTA = K slices of a unit; the 2 x 2-tile variant keeps 8 warps (its accumulators and operands need the registers)
+__host__ __device__ constexpr int warps_of(int MT, int NT) { return MT * NT == 4 ? 8 : SK_WARPS; }
 
-// MT: 16-feature tiles per CTA (1 or 2); NT: 8-row batch tiles (1: M <= 8, 2: M <= 16); SILU: tile 0 = gate, tile 1 = up.
+// MT: 16-feature tiles per unit (1 or 2); NT: 8-row batch tiles (1: M <= 8, 2: M <= 16); SILU: tile 0 = gate, tile 1 = up.
+// Persistent: one CTA per SM walks units blockIdx.x, blockIdx.x + gridDim.x, ...; a warp's loads run D groups ahead of
+// its math ACROSS unit boundaries (a unit gives a warp only G / kWarps groups - two at K = 4096 - so a pipeline that
+// restarted per unit would spend its time on load latency, and one-unit CTAs would quantise the work badly over the SMs).
 template <int MT, int NT, bool SILU>
-__global__ void __launch_bounds__(kWarps * 32, (MT * NT == 4) ? 1 : SK_MINB) q4_skinny_kernel(const SkParams p) {
-    __shared__ float red[kWarps][MT][NT][4][32];
+__global__ void __launch_bounds__(warps_of(MT, NT) * 32, 1) q4_skinny_kernel(const SkParams p) {
+    constexpr int kWarps = warps_of(MT, NT);
+    extern __shared__ float red_raw[];
+    float (*red)[kWarps][MT][NT][4][32] = reinterpret_cast<float (*)[kWarps][MT][NT][4][32]>(red_raw);   // [2]: double buffered by unit parity
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const int units = SILU ? p.total_tiles : p.total_tiles / MT;
+    const int my_units = blockIdx.x < units ? (units - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    // this warp's groups of every unit
+    const int g_begin = (int)((long long)p.G * warp / kWarps), g_end = (int)((long long)p.G * (warp + 1) / kWarps);
+    const int gpw = g_end - g_begin;
+    const int total = my_units * gpw;   // (unit, group) steps of this warp, unit-major
 
-    // the CTA's tiles: feature rows and their matrix
-    const uint4* wrow[MT][2];
-    const uint32_t* zrow[MT][2];
-    const __half* srow[MT][2];
-    int mat_of[MT], f0[MT];
-#pragma unroll
-    for (int mt = 0; mt < MT; mt++) {
-        int mi, tile;
+    // rows of unit u: tile mt holds features f0 .. f0 + 15 of matrix mi
+    auto unit_tile = [&](int u, int mt, int& mi, int& f0) {
+        const int unit = blockIdx.x + u * gridDim.x;
+        int tile;
         if (SILU) {
             mi = mt;
-            tile = blockIdx.x;
+            tile = unit;
         } else {
-            tile = blockIdx.x * MT + mt;
+            tile = unit * MT + mt;
             mi = 0;
             if (p.nmat > 1 && tile >= p.m[1].tile0) mi = 1;
             if (p.nmat > 2 && tile >= p.m[2].tile0) mi = 2;
             tile -= p.m[mi].tile0;
         }
-        mat_of[mt] = mi;
-        f0[mt] = tile * 16;
-#pragma unroll
-        for (int hh = 0; hh < 2; hh++) {
-            const size_t row = (size_t)f0[mt] + g + 8 * hh;
-            wrow[mt][hh] = reinterpret_cast<const uint4*>(p.m[mi].w + row * p.PW) + t;
-            zrow[mt][hh] = p.m[mi].z + row * p.PZ;
-            srow[mt][hh] = p.m[mi].s + row * p.G;
-        }
-    }
-    // this warp's groups
-    const int g_begin = (int)((long long)p.G * warp / kWarps), g_end = (int)((long long)p.G * (warp + 1) / kWarps);
+        f0 = tile * 16;
+    };
 
-    float acc[MT][NT][4];
-#pragma unroll
-    for (int mt = 0; mt < MT; mt++)
-#pragma unroll
-        for (int nt = 0; nt < NT; nt++) acc[mt][nt][0] = acc[mt][nt][1] = acc[mt][nt][2] = acc[mt][nt][3] = 0.f;
-
-    // A group's operands per thread: 16 bytes of packed weights, the zeros word and the scale for each of its 2 MT rows.
-    // D groups are in flight ahead of the math (the loads of a warp's first D groups leave before anything else happens;
-    // short K slices - 4 groups per warp at K = 4096 - are then covered whole).
-    constexpr int D = (MT == 1) ? (NT == 1 ? SK_D11 : SK_D12) : SK_D2;
+    // A step's operands per thread: 16 bytes of packed weights, the zeros word and the scale for each of its 2 MT rows.
+    constexpr int D = MT == 1 ? SK_D1 : SK_D2;
     struct Stage {
         uint4 w[MT][2];
         uint32_t zw[MT][2];
         __half sc[MT][2];
     };
     Stage st[D];
-    auto load_stage = [&](Stage& d, int grp) {
-        if (grp < g_end) {
+    int pf = 0, pf_u = 0, pf_gi = 0;   // prefetch cursor: step index, its unit and its group within the warp's slice
+    auto prefetch = [&](Stage& d) {
+        if (pf < total) {
+            const int grp = g_begin + pf_gi;
 #pragma unroll
-            for (int mt = 0; mt < MT; mt++)
+            for (int mt = 0; mt < MT; mt++) {
+                int mi, f0;
+                unit_tile(pf_u, mt, mi, f0);
 #pragma unroll
                 for (int hh = 0; hh < 2; hh++) {
-                    d.w[mt][hh] = ldg_stream(wrow[mt][hh] + 4 * grp);
-                    d.zw[mt][hh] = __ldg(zrow[mt][hh] + (grp >> 3));
-                    d.sc[mt][hh] = __ldg(srow[mt][hh] + grp);
+                    const size_t row = (size_t)f0 + g + 8 * hh;
+                    d.w[mt][hh] = ldg_stream(reinterpret_cast<const uint4*>(p.m[mi].w + row * p.PW) + t + 4 * grp);
+                    d.zw[mt][hh] = __ldg(p.m[mi].z + row * p.PZ + (grp >> 3));
+                    d.sc[mt][hh] = __ldg(p.m[mi].s + row * p.G + grp);
                 }
+            }
+            pf++;
+            if (++pf_gi == gpw) { pf_gi = 0; pf_u++; }
         }
     };
 #pragma unroll
-    for (int d = 0; d < D; d++) load_stage(st[d], g_begin + d);
+    for (int d = 0; d < D; d++) prefetch(st[d]);
     griddep_wait();
     griddep_launch_dependents();
 
@@ -153,13 +145,76 @@ __global__ void __launch_bounds__(kWarps * 32, (MT * NT == 4) ? 1 : SK_MINB) q4_
         xrow[nt] = p.x + (size_t)(xok[nt] ? g + 8 * nt : 0) * p.K + 32 * t;
     }
 
-    for (int base = g_begin; base < g_end; base += D) {
+    float acc[MT][NT][4];
+    auto clear_acc = [&]() {
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) acc[mt][nt][0] = acc[mt][nt][1] = acc[mt][nt][2] = acc[mt][nt][3] = 0.f;
+    };
+    clear_acc();
+
+    // End of unit u for this warp: its K slice goes to shared memory; after the CTA barrier the first NT * 4 warps add the
+    // kWarps slices in warp order (fixed order: bit-reproducible), apply the epilogue and store, while the others move on.
+    auto unit_end = [&](int u) {
+        const int par = u & 1;
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) red[par][warp][mt][nt][e][lane] = acc[mt][nt][e];
+        clear_acc();
+        __syncthreads();
+        // thread = (nt, e, lane): element (feature f0 + g + 8 (e >> 1), batch row 8 nt + 2 t + (e & 1)) of every tile
+        for (int i = threadIdx.x; i < NT * 4 * 32; i += kWarps * 32) {
+            const int l = i & 31, e = (i >> 5) & 3, nt = i >> 7;
+            const int row = 8 * nt + 2 * (l & 3) + (e & 1);
+            float v[MT];
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++) {
+                float sum = 0.f;
+#pragma unroll
+                for (int w = 0; w < kWarps; w++) sum += red[par][w][mt][nt][e][l];
+                v[mt] = sum;
+            }
+            if (row >= p.M) continue;
+            if (SILU) {
+                int mi, f0;
+                unit_tile(u, 0, mi, f0);
+                float val = v[0];
+                val *= 1.0f / (1.0f + expf(-val));
+                val *= v[MT - 1];
+                p.m[0].y[(size_t)row * p.m[0].ldy + f0 + (l >> 2) + 8 * (e >> 1)] = __float2half(val);
+            } else {
+#pragma unroll
+                for (int mt = 0; mt < MT; mt++) {
+                    int mi, f0;
+                    unit_tile(u, mt, mi, f0);
+                    const SkMat& mm = p.m[mi];
+                    const size_t at = (size_t)row * mm.ldy + f0 + (l >> 2) + 8 * (e >> 1);
+                    float val = v[mt];
+                    if (p.residual) val += __half2float(p.residual[at]) * p.rscale;
+                    mm.y[at] = __float2half(val);
+                }
+            }
+        }
+        // the buffer of parity `par` is written again at unit u + 2, after every thread has passed the barrier of unit u + 1,
+        // which the threads that read it here reach only when they are done
+    };
+
+    if (gpw == 0) {   // fewer groups than warps: this warp only takes part in the reductions
+        for (int u = 0; u < my_units; u++) unit_end(u);
+        return;
+    }
+    int u = 0, gi = 0;
+    for (int base = 0; base < total; base += D) {
 #pragma unroll
         for (int d = 0; d < D; d++) {
-            const int grp = base + d;
-            if (grp >= g_end) break;
+            if (base + d >= total) break;
+            const int grp = g_begin + gi;
             const Stage cur = st[d];
-            load_stage(st[d], grp + D);
+            prefetch(st[d]);
             // the batch rows' 32 inputs of this thread's quarter of the group, in the unpack's pairing
             uint32_t xp[NT][4][4];
 #pragma unroll
@@ -206,47 +261,16 @@ __global__ void __launch_bounds__(kWarps * 32, (MT * NT == 4) ? 1 : SK_MINB) q4_
                     acc[mt][nt][3] = fmaf(sc[1], c[nt][3], acc[mt][nt][3]);
                 }
             }
-        }
-    }
-
-    // the eight K slices, summed in warp order
-#pragma unroll
-    for (int mt = 0; mt < MT; mt++)
-#pragma unroll
-        for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-            for (int e = 0; e < 4; e++) red[warp][mt][nt][e][lane] = acc[mt][nt][e];
-    __syncthreads();
-    // thread = (nt, e, lane) for all tiles: element (feature f0 + g + 8 (e >> 1), batch row 8 nt + 2 t + (e & 1))
-    for (int i = threadIdx.x; i < NT * 4 * 32; i += kWarps * 32) {
-        const int l = i & 31, e = (i >> 5) & 3, nt = i >> 7;
-        const int row = 8 * nt + 2 * (l & 3) + (e & 1);
-        float v[MT];
-#pragma unroll
-        for (int mt = 0; mt < MT; mt++) {
-            float s = 0.f;
-#pragma unroll
-            for (int w = 0; w < kWarps; w++) s += red[w][mt][nt][e][l];
-            v[mt] = s;
-        }
-        if (row >= p.M) continue;
-        if (SILU) {
-            float val = v[0];
-            val *= 1.0f / (1.0f + expf(-val));
-            val *= v[MT - 1];
-            p.m[0].y[(size_t)row * p.m[0].ldy + f0[0] + (l >> 2) + 8 * (e >> 1)] = __float2half(val);
-        } else {
-#pragma unroll
-            for (int mt = 0; mt < MT; mt++) {
-                const SkMat& mm = p.m[mat_of[mt]];
-                const size_t at = (size_t)row * mm.ldy + f0[mt] + (l >> 2) + 8 * (e >> 1);
-                float val = v[mt];
-                if (p.residual) val += __half2float(p.residual[at]) * p.rscale;
-                mm.y[at] = __float2half(val);
+            if (++gi == gpw) {
+                unit_end(u);
+                gi = 0;
+                u++;
             }
         }
     }
 }
+
+constexpr size_t red_bytes(int MT, int NT) { return 2 * (size_t)warps_of(MT, NT) * MT * NT * 4 * 32 * sizeof(float); }
 
 int fill(SkParams& p, const uint16_t* x, int M, int K) {
     if (!x || M < 1 || M > 16) return Q4_ERR_INVALID;
@@ -271,26 +295,30 @@ SkMat sk_mat(const q4_qweight* w, uint16_t* y, int ldy, int tile0) {
     return m;
 }
 
+template <int MT, int NT, bool SILU>
+int launch_variant(const SkParams& p, cudaStream_t s) {
+    static bool attr_set = false;   // (the attribute is per function and per device context; setting it again is harmless)
+    const size_t smem = red_bytes(MT, NT);
+    if (!attr_set) {
+        Q4_CUDA_TRY(cudaFuncSetAttribute(q4_skinny_kernel<MT, NT, SILU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_set = true;
+    }
+    const int units = SILU ? p.total_tiles : p.total_tiles / MT;
+    Q4Launch L(dim3(units < 148 ? units : 148), dim3(warps_of(MT, NT) * 32), smem, s);
+    Q4_CUDA_TRY(cudaLaunchKernelEx(&L.cfg, q4_skinny_kernel<MT, NT, SILU>, p));
+    return Q4_OK;
+}
+
 template <bool SILU>
 int launch(const SkParams& p, cudaStream_t s) {
     const bool two = p.M > 8;
-    if (SILU) {
-        Q4Launch L(dim3(p.total_tiles), dim3(kWarps * 32), 0, s);
-        if (two) Q4_CUDA_TRY(cudaLaunchKernelEx(&L.cfg, q4_skinny_kernel<2, 2, true>, p));
-        else Q4_CUDA_TRY(cudaLaunchKernelEx(&L.cfg, q4_skinny_kernel<2, 1, true>, p));
-        return Q4_OK;
-    }
-    // two tiles per CTA halve the x traffic; one tile per CTA when that is what it takes to put two CTAs on every SM
-    const bool pair = (p.total_tiles % 2 == 0) && p.total_tiles >= 4 * 148;
-    Q4Launch L(dim3(pair ? p.total_tiles / 2 : p.total_tiles), dim3(kWarps * 32), 0, s);
-    if (pair) {
-        if (two) Q4_CUDA_TRY(cudaLaunchKernelEx(&L.cfg, q4_skinny_kernel<2, 2, false>, p));
-        else Q4_CUDA_TRY(cudaLaunchKernelEx(&L.cfg, q4_skinny_kernel<2, 1, false>, p));
-    } else {
-        if (two) Q4_CUDA_TRY(cudaLaunchKernelEx(&L.cfg, q4_skinny_kernel<1, 2, false>, p));
-        else Q4_CUDA_TRY(cudaLaunchKernelEx(&L.cfg, q4_skinny_kernel<1, 1, false>, p));
-    }
-    return Q4_OK;
+    if (SILU) return two ? launch_variant<2, 2, true>(p, s) : launch_variant<2, 1, true>(p, s);
+    // Two tiles per unit halve the reads of x but double the grain the work is dealt in: take pairs when the most loaded
+    // SM then carries no more features than with single tiles.
+    const int t = p.total_tiles;
+    const bool pair = (t % 2 == 0) && 2 * q4_div_up(t / 2, 148) <= q4_div_up(t, 148);
+    if (pair) return two ? launch_variant<2, 2, false>(p, s) : launch_variant<2, 1, false>(p, s);
+    return two ? launch_variant<1, 2, false>(p, s) : launch_variant<1, 1, false>(p, s);
 }
 
 }  // namespace

@@ -90,18 +90,77 @@ def test_prefill_hand_off_and_pieces(mid_path):
     t.close()
 
 
-def test_prefill_512_tokens_on_7b_layer_shapes(tmp_path):
-    """512 prompt positions through four layers of the 7B shapes: last-position logits against the fused decode path."""
-    path = str(tmp_path / "7b4l.bin")
-    synth.write_model_file(path, "llama2-7b-4l", seed=0)
+@pytest.fixture(scope="module")
+def path_7b4l(tmp_path_factory):
+    p = tmp_path_factory.mktemp("models") / "7b4l.bin"
+    synth.write_model_file(str(p), "llama2-7b-4l", seed=0)
+    return str(p)
+
+
+def test_prefill_512_tokens_on_7b_layer_shapes(path_7b4l):
+    """512 prompt positions through four layers of the 7B shapes: last-position logits against the per-op kernels fed token
+    by token (the path that follows the reference's arithmetic op by op). At position 511 of this random-weight model any
+    two of the three paths lie about 2e-2 apart (fused vs per-op 2.0e-2, prefill vs per-op 2.3e-2, prefill vs fused 1.8e-2;
+    the long-context case against the oracle itself is the next test), so the bound here is 3e-2 and the cosine limit holds."""
     tokens = np.random.default_rng(1).integers(3, 32000, size=512, dtype=np.int32)
-    ref = token_by_token(path, tokens, 2, {511})
-    t = Transformer(path)
+    ref = token_by_token(path_7b4l, tokens, 1, {511})
+    t = Transformer(path_7b4l)
     t.reset(tokens, 0)
     t.prefill(512, gen_token=False)
     t.synchronize()
     assert t.status() == 0
-    assert_close(t.logits(), ref[511], "512-token prefill vs token-by-token fused path", max_rel=2 * MAX_REL)
+    assert_close(t.logits(), ref[511], "512-token prefill vs token-by-token per-op path", max_rel=3 * MAX_REL)
+    t.close()
+
+
+def test_prefill_long_prompt_against_the_oracle(tmp_path):
+    """600 positions in one pass on the long-context model (ten 64-row attention tiles, ragged last one): the last position's
+    logits against the CPU oracle that walked the same 600 tokens one by one."""
+    path = str(tmp_path / "midlong.bin")
+    synth.write_model_file(path, "mid-long", seed=2)
+    vocab = synth.CONFIGS["mid-long"][5]
+    tokens = np.random.default_rng(5).integers(3, vocab, size=600, dtype=np.int32)
+    t = Transformer(path)
+    t.reset(tokens, 0)
+    t.prefill(600, gen_token=False)
+    t.synchronize()
+    got = t.logits()
+    assert t.status() == 0
+    t.close()
+    m = O.Model(open(path, "rb").read())
+    for pos, tok in enumerate(tokens):
+        m.forward(int(tok), pos, order=0)
+    assert_close(got, m.logits(), "600-token prefill, last logits vs oracle")
+    m.close()
+
+
+def test_prefill_and_batched_decode_are_bit_reproducible(path_7b4l):
+    """Two different prompts alternate through the same model object (so that stale rows of the other prompt would show);
+    every run of a prompt must give the same bits, for the 512-token prefill and for eight sequences decoded together."""
+    prompts = [np.random.default_rng(s).integers(3, 32000, size=512, dtype=np.int32) for s in (1, 2)]
+    t = Transformer(path_7b4l)
+    first = {}
+    for rep in range(10):
+        k = rep & 1
+        t.reset(prompts[k], 0)
+        t.prefill(512, gen_token=False)
+        t.synchronize()
+        bits = t.logits().view(np.uint16)
+        assert (first.setdefault(k, bits) == bits).all(), f"prefill run {rep} differs from the first run of prompt {k}"
+    b = Batch(t, 8)
+    sets = [np.stack([synth.synth_prompt(16, 32000, seed=s * 100 + i) for i in range(8)]) for s in (1, 2)]
+    first = {}
+    for rep in range(6):
+        k = rep & 1
+        b.reset(sets[k])
+        for _ in range(40):
+            b.forward()
+        t.synchronize()
+        bits, toks = b.logits().view(np.uint16), b.tokens(41)
+        ref = first.setdefault(k, (bits, toks))
+        assert (ref[0] == bits).all() and (ref[1] == toks).all(), f"batched decode run {rep} differs from the first run of prompt set {k}"
+    assert t.status() == 0
+    b.close()
     t.close()
 
 
