@@ -525,6 +525,8 @@ def main():
     ap.add_argument("--path", type=int, default=-1, help="forward path: 1 = CUDA-graph replay of per-op kernels (default: best available)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the per-op kernel table, the all-reduce table and the larger models")
+    ap.add_argument("--leg", default="all", choices=["all", "prefill-batch"],
+                    help="prefill-batch: only the 512-token prefill and the batch-8 decode of --model (profiling-sized run; prints their numbers, not the metric line)")
     ap.add_argument("--positions", type=int, default=0, help="positions per generation (default 272 = 16 prompt + 256 decode); smaller for profiling runs")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
@@ -577,6 +579,23 @@ def main():
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
+
+    if args.leg == "prefill-batch":
+        pk, _ = peaks()
+        if comm is not None and _lib.lib().q4_comm_nccl_available():
+            comm.attach_nccl(dist)
+            comm.set_backend(_lib.Q4_COMM_BACKEND_AUTO)
+        res = prefill_and_batch(t, cfg, fwd_path, 1.0, rank, world, dist, torch, barrier, pk, per_op_anchor=False)
+        res["batch8_decode"].pop("vs_batch1_rate", None)
+        if rank == 0:
+            print(json.dumps({"leg": "prefill-batch", "model": args.model, "n_gpus": world, **res}))
+        t.close()
+        if comm:
+            comm.close()
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
 
     # ---- device-timed value ----
     sampler = ClockSampler(local_rank)
