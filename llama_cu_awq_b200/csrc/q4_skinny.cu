@@ -59,21 +59,26 @@ __device__ __forceinline__ void unpack8(uint32_t w, uint32_t zlo, uint32_t zhi, 
 }
 
 #ifndef SK_WARPS
-#define SK_WARPS 16
+#define SK_WARPS 8
 #endif
 #ifndef SK_D1
-#define SK_D1 3
+#define SK_D1 4
 #endif
 #ifndef SK_D2
-#define SK_D2 2
+#define SK_D2 4
 #endif
-// warps of a CTA = K slices of a unit; the 2 x 2-tile variant keeps 8 warps (its accumulators and operands need the registers)
-__host__ __device__ constexpr int warps_of(int MT, int NT) { return MT * NT == 4 ? 8 : SK_WARPS; }
+#ifndef SK_D22
+#define SK_D22 3
+#endif
+// warps of a CTA = K slices of a unit
+__host__ __device__ constexpr int warps_of(int MT, int NT) { return SK_WARPS; }
 
 // MT: 16-feature tiles per unit (1 or 2); NT: 8-row batch tiles (1: M <= 8, 2: M <= 16); SILU: tile 0 = gate, tile 1 = up.
-// Persistent: one CTA per SM walks units blockIdx.x, blockIdx.x + gridDim.x, ...; a warp's loads run D groups ahead of
-// its math ACROSS unit boundaries (a unit gives a warp only G / kWarps groups - two at K = 4096 - so a pipeline that
-// restarted per unit would spend its time on load latency, and one-unit CTAs would quantise the work badly over the SMs).
+// Persistent: one CTA per SM walks units blockIdx.x, blockIdx.x + gridDim.x, ...; a warp's weight loads run D groups ahead
+// of its math ACROSS unit boundaries and its x fragments one group ahead (a unit gives a warp only G / kWarps groups - four
+// at K = 4096 - so a pipeline that restarted per unit would spend its time on load latency, and one-unit CTAs would
+// quantise the work badly over the SMs). Few warps with everything they need already in flight, rather than many warps
+// that each wait: the registers of the SM go to the prefetch stages.
 template <int MT, int NT, bool SILU>
 __global__ void __launch_bounds__(warps_of(MT, NT) * 32, 1) q4_skinny_kernel(const SkParams p) {
     constexpr int kWarps = warps_of(MT, NT);
@@ -105,38 +110,56 @@ __global__ void __launch_bounds__(warps_of(MT, NT) * 32, 1) q4_skinny_kernel(con
     };
 
     // A step's operands per thread: 16 bytes of packed weights, the zeros word and the scale for each of its 2 MT rows.
-    constexpr int D = MT == 1 ? SK_D1 : SK_D2;
+    constexpr int D = MT == 1 ? SK_D1 : (NT == 1 ? SK_D2 : SK_D22);
     struct Stage {
         uint4 w[MT][2];
         uint32_t zw[MT][2];
         __half sc[MT][2];
     };
     Stage st[D];
-    int pf = 0, pf_u = 0, pf_gi = 0;   // prefetch cursor: step index, its unit and its group within the warp's slice
+    // prefetch cursor: step index, its unit, its group within the warp's slice, and the unit's row pointers (row g of each
+    // tile; row g + 8 lies 8 rows further)
+    int pf = 0, pf_u = 0, pf_gi = 0;
+    const uint4* pw[MT];
+    const uint32_t* pz[MT];
+    const __half* ps[MT];
+    auto set_rows = [&](int u) {
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++) {
+            int mi, f0;
+            unit_tile(u, mt, mi, f0);
+            const size_t row = (size_t)f0 + g;
+            pw[mt] = reinterpret_cast<const uint4*>(p.m[mi].w + row * p.PW) + t;
+            pz[mt] = p.m[mi].z + row * p.PZ;
+            ps[mt] = p.m[mi].s + row * p.G;
+        }
+    };
     auto prefetch = [&](Stage& d) {
         if (pf < total) {
             const int grp = g_begin + pf_gi;
 #pragma unroll
-            for (int mt = 0; mt < MT; mt++) {
-                int mi, f0;
-                unit_tile(pf_u, mt, mi, f0);
+            for (int mt = 0; mt < MT; mt++)
 #pragma unroll
                 for (int hh = 0; hh < 2; hh++) {
-                    const size_t row = (size_t)f0 + g + 8 * hh;
-                    d.w[mt][hh] = ldg_stream(reinterpret_cast<const uint4*>(p.m[mi].w + row * p.PW) + t + 4 * grp);
-                    d.zw[mt][hh] = __ldg(p.m[mi].z + row * p.PZ + (grp >> 3));
-                    d.sc[mt][hh] = __ldg(p.m[mi].s + row * p.G + grp);
+                    d.w[mt][hh] = ldg_stream(pw[mt] + hh * 2 * p.PW + 4 * grp);
+                    d.zw[mt][hh] = __ldg(pz[mt] + hh * 8 * p.PZ + (grp >> 3));
+                    d.sc[mt][hh] = __ldg(ps[mt] + hh * 8 * p.G + grp);
                 }
-            }
             pf++;
-            if (++pf_gi == gpw) { pf_gi = 0; pf_u++; }
+            if (++pf_gi == gpw) {
+                pf_gi = 0;
+                pf_u++;
+                if (pf < total) set_rows(pf_u);
+            }
         }
     };
+    if (total > 0) set_rows(0);
 #pragma unroll
     for (int d = 0; d < D; d++) prefetch(st[d]);
     griddep_wait();
     griddep_launch_dependents();
 
+    // x: the batch rows' 32 inputs of this thread's quarter of a group, fetched one step ahead
     const __half* xrow[NT];
     bool xok[NT];
 #pragma unroll
@@ -144,6 +167,16 @@ __global__ void __launch_bounds__(warps_of(MT, NT) * 32, 1) q4_skinny_kernel(con
         xok[nt] = g + 8 * nt < p.M;
         xrow[nt] = p.x + (size_t)(xok[nt] ? g + 8 * nt : 0) * p.K + 32 * t;
     }
+    uint4 xn[NT][4];
+    auto load_x = [&](int grp) {
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                xn[nt][j] = make_uint4(0, 0, 0, 0);
+                if (xok[nt]) xn[nt][j] = *reinterpret_cast<const uint4*>(xrow[nt] + 128 * grp + 8 * j);
+            }
+    };
 
     float acc[MT][NT][4];
     auto clear_acc = [&]() {
@@ -208,24 +241,21 @@ __global__ void __launch_bounds__(warps_of(MT, NT) * 32, 1) q4_skinny_kernel(con
         return;
     }
     int u = 0, gi = 0;
+    load_x(g_begin);
     for (int base = 0; base < total; base += D) {
 #pragma unroll
         for (int d = 0; d < D; d++) {
             if (base + d >= total) break;
             const int grp = g_begin + gi;
-            const Stage cur = st[d];
-            prefetch(st[d]);
-            // the batch rows' 32 inputs of this thread's quarter of the group, in the unpack's pairing
+            // this step's x pairs in the unpack's order; the next step's x leaves now
             uint32_t xp[NT][4][4];
 #pragma unroll
-            for (int nt = 0; nt < NT; nt++) {
+            for (int nt = 0; nt < NT; nt++)
 #pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    uint4 xv = make_uint4(0, 0, 0, 0);
-                    if (xok[nt]) xv = *reinterpret_cast<const uint4*>(xrow[nt] + 128 * grp + 8 * j);
-                    permute_x8(xv, xp[nt][j]);
-                }
-            }
+                for (int j = 0; j < 4; j++) permute_x8(xn[nt][j], xp[nt][j]);
+            const int gi_next = gi + 1 == gpw ? 0 : gi + 1;
+            if (base + d + 1 < total) load_x(g_begin + gi_next);
+            const Stage& cur = st[d];
 #pragma unroll
             for (int mt = 0; mt < MT; mt++) {
                 uint32_t zlo[2], zhi[2];
@@ -261,6 +291,7 @@ __global__ void __launch_bounds__(warps_of(MT, NT) * 32, 1) q4_skinny_kernel(con
                     acc[mt][nt][3] = fmaf(sc[1], c[nt][3], acc[mt][nt][3]);
                 }
             }
+            prefetch(st[d]);   // the stage is spent: its next occupant, D steps ahead, leaves now
             if (++gi == gpw) {
                 unit_end(u);
                 gi = 0;

@@ -49,7 +49,7 @@ def test_matvec_parity(K, N):
 
 
 def test_config0_single_layer():
-    """BASELINE config 0: fp16 [1,4096] ~ N(0,1), 4096x4096 W4 g128, scales U[0.002,0.02], seed 0."""
+    """The single-layer configuration of the metric: fp16 [1,4096] ~ N(0,1), 4096x4096 W4 g128, scales U[0.002,0.02], seed 0."""
     q, x, _ = mk(4096, 4096, seed=0)
     W = ops.QWeight.from_numpy(q)
     y = torch.empty(4096, dtype=torch.float16, device="cuda")

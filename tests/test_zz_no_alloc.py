@@ -45,6 +45,32 @@ def test_static_scratch_matches_caller_scratch_twice_in_a_row():
         assert (out.view(np.uint16) == ref.view(np.uint16)).all()  # same kernels, same arithmetic
 
 
+def test_static_call_allocates_and_frees_nothing():
+    """The advertised property: after the first call on a device (which looks the array's address up once), a call leaves
+    the device's free memory exactly where it was - nothing is allocated, nothing is freed. head_size 64 rides along."""
+    out, ref = run_both(16, 2, 64, 90, 3)     # first use of this shape; also the head_size 64 case
+    assert (out.view(np.uint16) == ref.view(np.uint16)).all()
+    rng = np.random.default_rng(5)
+    heads, kv_mul, hs, pos = 32, 1, 128, 200
+    q = dev(rng.standard_normal(heads * hs).astype(np.float16))
+    kc = dev((rng.standard_normal((pos + 1, heads * hs)) * 0.5).astype(np.float16))
+    vc = dev(rng.standard_normal((pos + 1, heads * hs)).astype(np.float16))
+    pd = torch.tensor([pos], dtype=torch.int32, device="cuda")
+    out = torch.empty(heads * hs, dtype=torch.float16, device="cuda")
+    L = _lib.lib()
+    s = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    args = (s, C.c_void_p(out.data_ptr()), C.c_void_p(q.data_ptr()), C.c_void_p(kc.data_ptr()), C.c_void_p(vc.data_ptr()), heads, hs, kv_mul, pos + 1,
+            C.c_void_p(pd.data_ptr()))
+    assert L.q4_attention_static(*args) == _lib.Q4_OK
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        assert L.q4_attention_static(*args) == _lib.Q4_OK
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+
+
 def test_static_scratch_rejects_oversized_shapes():
     L = _lib.lib()
     heads, hs = 1024, 256
