@@ -353,7 +353,8 @@ def gemm_table(torch):
 
 
 def allreduce_table(comm, dist, torch):
-    """Microseconds per in-place fp16 all-reduce of one model vector (8, 10, 16 KB) and of 64 KB: peer push vs NCCL."""
+    """Microseconds per in-place fp16 all-reduce of one model vector (8, 10, 16 KB) and of the [rows x dim] messages of
+    batched decode (32-256 KB): peer push (one CTA up to 64 KB, four above) vs NCCL."""
     from llama_cu_awq_b200 import _lib
     L = _lib.lib()
     out = {}
@@ -364,7 +365,7 @@ def allreduce_table(comm, dist, torch):
     except Exception as e:  # NCCL cannot be opened: the table then has the peer push only
         out["nccl_error"] = str(e)[:120]
     s = torch.cuda.current_stream()
-    for count in (4096, 5120, 8192, 16384, 32768):
+    for count in (4096, 5120, 8192, 16384, 32768, 65536, 131072):
         buf = torch.zeros(count, dtype=torch.float16, device="cuda")
         row = {}
         for name, backend in (("p2p_push", _lib.Q4_COMM_BACKEND_P2P), ("nccl", _lib.Q4_COMM_BACKEND_NCCL)):

@@ -215,10 +215,13 @@ int q4_comm_export(q4_comm* comm, uint8_t handle[64]);
 int q4_comm_import(q4_comm* comm, int peer, const uint8_t handle[64]);
 /* cudaAllReduce (fp16 sum, in place): cuda_comm.h:160-224; call sites llama2_q4.cu:474-476,505-507.
  * One-shot push over NVLink: every rank stores its vector into every peer's inbox and sums the gpu_count
- * inbox slots in rank order in fp32, so all ranks obtain identical bits. count <= Q4_COMM_MAX_HALFS. */
-#define Q4_COMM_MAX_HALFS 32768
+ * inbox slots in rank order in fp32, so all ranks obtain identical bits. count <= Q4_COMM_MAX_HALFS; vectors above
+ * 64 KB are moved by four CTAs, each with its own part, flags and call counter. */
+#define Q4_COMM_MAX_HALFS 131072
 int q4_all_reduce(q4_comm* comm, void* stream, uint16_t* buf, int count);
-/* cudaAllGather (fp16): cuda_comm.h:227-275; call site llama2_q4.cu:534-536. recv holds gpu_count*sendcount. */
+/* cudaAllGather (fp16): cuda_comm.h:227-275; call site llama2_q4.cu:534-536. recv holds gpu_count*sendcount;
+ * sendcount <= Q4_COMM_MAX_GATHER_HALFS. */
+#define Q4_COMM_MAX_GATHER_HALFS 32768
 int q4_all_gather(q4_comm* comm, void* stream, const uint16_t* send, uint16_t* recv, int sendcount);
 /* Device-side wait status: 0, or Q4_ERR_TIMEOUT after a peer flag did not arrive within the bound. */
 int q4_comm_status(q4_comm* comm);

@@ -2,7 +2,7 @@
 // Replaces cudaAllReduce / cudaAllGather / reduce_sum_half_kernel of the reference (cuda_comm.h:144-275),
 // which stage through a 128 MB buffer, two host barriers and one kernel per peer for every call.
 //
-// Every rank owns an inbox in its own memory: slots[2][g][Q4_COMM_MAX_HALFS] halfs and flags[2][g] words,
+// Every rank owns an inbox in its own memory: slots[2][g][Q4_COMM_MAX_GATHER_HALFS] halfs and flags[2][g] words,
 // double buffered by the parity of a call counter (epoch). A call is one kernel:
 //   1. store this rank's vector into slot [parity][rank] of EVERY rank's inbox (plain 128-bit peer stores),
 //   2. fence, then release-store the epoch into flag [parity][rank] of every inbox,
@@ -25,12 +25,23 @@ namespace {
 constexpr unsigned long long kDefaultWaitNs = 2000ULL * 1000 * 1000;  // default bound of the flag wait: 2 s on the device's global timer
 constexpr int kCommThreads = 1024;
 
+// Messages above kWideAbove halfs are moved by kWideCtas CTAs, each with its own part of the vector, its own flags and its
+// own call counter (a single CTA would need one call per 64 KB piece).
+constexpr int kWideCtas = 4;        // measured on 2 GPUs at 128 / 256 KB: 4 CTAs 13.6 / 15.7 us, 8: 16.1 / 17.1, 16: 18.8 / 19.5
+constexpr int kWideAbove = 32768;   // one CTA moves up to 64 KB faster (12.5 us) than several do
+constexpr int kWidePad = 1;         // words between the flags of two CTAs (spreading them over cache lines changed nothing)
+
 struct Inbox {
     uint32_t flags[2][Q4_MAX_GPUS];
     uint32_t epoch;    // local call counter
     uint32_t status;   // 0 or Q4_ERR_TIMEOUT
     uint32_t pad[14];
-    __half slots[2][Q4_MAX_GPUS][Q4_COMM_MAX_HALFS];
+    uint32_t wide_flags[2][kWideCtas][Q4_MAX_GPUS * kWidePad];
+    uint32_t wide_epoch[kWideCtas];
+    __half slots[2][Q4_MAX_GPUS][Q4_COMM_MAX_GATHER_HALFS];
+    // The wide kernel has slots of its own: its call counters are independent of the one-CTA kernel's, so the two must not
+    // share a buffer (the parity argument above holds per counter).
+    __half wide_slots[2][Q4_MAX_GPUS][Q4_COMM_MAX_HALFS];
     Q4LLArea ll;       // exchange area of the fused decode kernel
 };
 
@@ -122,6 +133,60 @@ __global__ void __launch_bounds__(kCommThreads) comm_kernel(PeerPtrs peers, Inbo
         for (int r = 0; r < g; r++)
             for (int i = threadIdx.x; i < nvec; i += blockDim.x)
                 reinterpret_cast<uint4*>(buf + (size_t)r * count)[i] = reinterpret_cast<const uint4*>(local->slots[par][r])[i];
+    }
+}
+
+// The all-reduce for long vectors: CTA c owns the c-th part of the vector and runs the same protocol as comm_kernel on it
+// with flags and a call counter of its own (wide_flags[.][.][c], wide_epoch[c]); CTAs never wait for one another, only for
+// the same CTA of the peers, so they need not be resident together. Every CTA takes part in every call, also with an empty
+// part, which keeps the counters of all ranks in step.
+__global__ void __launch_bounds__(kCommThreads) comm_wide_kernel(PeerPtrs peers, Inbox* local, int rank, int g, __half* buf, int count,
+                                                                 unsigned long long wait_ns) {
+    __shared__ uint32_t s_epoch;
+    griddep_wait();
+    griddep_launch_dependents();
+    const int c = blockIdx.x;
+    if (threadIdx.x == 0) s_epoch = ++local->wide_epoch[c];
+    __syncthreads();
+    const uint32_t epoch = s_epoch;
+    const int par = epoch & 1;
+    const int nvec = count >> 3;  // count is a multiple of 8
+    const int per = (nvec + kWideCtas - 1) / kWideCtas;
+    const int v0 = min(c * per, nvec), v1 = min(v0 + per, nvec);
+    for (int p = 0; p < g; p++) {
+        uint4* dst = reinterpret_cast<uint4*>(peers.p[p]->wide_slots[par][rank]);
+        for (int i = v0 + threadIdx.x; i < v1; i += blockDim.x) dst[i] = reinterpret_cast<const uint4*>(buf)[i];
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < g) {
+        st_release_sys(&peers.p[threadIdx.x]->wide_flags[par][c][rank * kWidePad], epoch);
+        unsigned long long t_start = 0;
+        unsigned spins = 0;
+        while (ld_acquire_sys(&local->wide_flags[par][c][threadIdx.x * kWidePad]) != epoch) {
+            if ((++spins & 255u) == 0) {
+                const unsigned long long now = global_timer_ns();
+                if (t_start == 0) t_start = now;
+                else if (now - t_start > wait_ns) { local->status = Q4_ERR_TIMEOUT; break; }
+            }
+        }
+    }
+    __syncthreads();
+    for (int i = v0 + threadIdx.x; i < v1; i += blockDim.x) {
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[j] = 0.f;
+        for (int r = 0; r < g; r++) {
+            const uint4 v = reinterpret_cast<const uint4*>(local->wide_slots[par][r])[i];
+            const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+            for (int j = 0; j < 4; j++) { const float2 f = __half22float2(h[j]); acc[2 * j] += f.x; acc[2 * j + 1] += f.y; }
+        }
+        uint4 o;
+        __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; j++) oh[j] = __floats2half2_rn(acc[2 * j], acc[2 * j + 1]);
+        reinterpret_cast<uint4*>(buf)[i] = o;
     }
 }
 
@@ -239,9 +304,14 @@ extern "C" int q4_comm_import(q4_comm* comm, int peer, const uint8_t handle[64])
 
 static int comm_launch(q4_comm* c, cudaStream_t s, __half* buf, const __half* send, int count, int mode) {
     if (!c || !buf || count <= 0 || (count & 7)) return Q4_ERR_INVALID;
-    if (count > Q4_COMM_MAX_HALFS) return Q4_ERR_LIMIT;
+    if (count > (mode == 0 ? Q4_COMM_MAX_HALFS : Q4_COMM_MAX_GATHER_HALFS)) return Q4_ERR_LIMIT;
     for (int i = 0; i < c->gpu_count; i++)
         if (!c->peers.p[i]) return Q4_ERR_INVALID;
+    if (mode == 0 && count > kWideAbove) {
+        Q4Launch L(dim3(kWideCtas), dim3(kCommThreads), 0, s);
+        Q4_CUDA_TRY(cudaLaunchKernelEx(&L.cfg, comm_wide_kernel, c->peers, c->local, c->rank, c->gpu_count, buf, count, c->wait_ns));
+        return Q4_OK;
+    }
     Q4Launch L(dim3(1), dim3(kCommThreads), 0, s);
     Q4_CUDA_TRY(cudaLaunchKernelEx(&L.cfg, comm_kernel, c->peers, c->local, c->rank, c->gpu_count, buf, send, count, mode, c->wait_ns));
     return Q4_OK;

@@ -21,7 +21,7 @@ def _run_tp(cfg, fwd_path, n, tmp_path, mode="hybrid", extra=""):
         synth.write_model_file(path, cfg, seed=7)
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
-           "--master-port", str(29500 + fwd_path + (10 if cfg == "mid" else 20) + 40 * (n - 2) + (5 if mode == "column" else 0) + {"": 0, "synthetic": 100, "nccl": 200, "prefill": 300, "prefill-p2p": 350, "batch": 400}[extra]),
+           "--master-port", str(29500 + fwd_path + (10 if cfg == "mid" else 20) + 40 * (n - 2) + (5 if mode == "column" else 0) + {"": 0, "synthetic": 100, "nccl": 200, "prefill": 300, "prefill-p2p": 350, "batch": 400, "collectives": 450}[extra]),
            os.path.join(ROOT, "tests", "tp_worker.py"), cfg, path, str(fwd_path), mode, extra]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
@@ -70,3 +70,13 @@ def test_tp2_prefill(extra, tmp_path):
 def test_tp2_batched_decode(tmp_path):
     """Three sequences decoded together on two ranks (skinny W4 kernels + peer-push all-reduce inside the step graph)."""
     _run_tp("mid-gqa", 2, 2, tmp_path, extra="batch")
+
+
+def test_tp2_collectives_short_and_long_vectors(tmp_path):
+    """The peer-push all-reduce on 16-byte to 256 KB vectors (one CTA / several CTAs, interleaved) and the all-gather."""
+    _run_tp("mid", 0, 2, tmp_path, extra="collectives")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs 4 GPUs")
+def test_tp4_collectives_short_and_long_vectors(tmp_path):
+    _run_tp("mid", 0, 4, tmp_path, extra="collectives")

@@ -15,6 +15,49 @@ from llama_cu_awq_b200.comm import ProcessComm  # noqa: E402
 from llama_cu_awq_b200.model import Batch, Transformer  # noqa: E402
 
 
+def collectives_mode(comm, rank, world):
+    """q4_all_reduce / q4_all_gather alone: short vectors (one CTA), long ones (several CTAs with their own flags and
+    counters) and the two kinds interleaved, several rounds without any host synchronisation in between; the result must
+    be, bit for bit, the fp32 sum in rank order rounded once - on every rank."""
+    import ctypes as C
+    L = _lib.lib()
+    s = torch.cuda.current_stream()
+    ok = 1
+    counts = [8, 4096, 16384, 16392, 40960, 65536, 131072, 5120, 131072, 8]
+    for rnd in range(3):
+        bufs, wants = [], []
+        for i, n in enumerate(counts):
+            parts = [np.random.default_rng(1000 * rnd + 10 * i + r).standard_normal(n).astype(np.float16) for r in range(world)]
+            acc = np.zeros(n, np.float32)
+            for r in range(world):
+                acc += parts[r].astype(np.float32)
+            wants.append(acc.astype(np.float16))
+            bufs.append(torch.from_numpy(parts[rank].copy()).cuda())
+        torch.cuda.synchronize()
+        dist.barrier()
+        for b, n in zip(bufs, counts):     # queued back to back
+            assert L.q4_all_reduce(comm.handle, C.c_void_p(s.cuda_stream), C.c_void_p(b.data_ptr()), n) == 0
+        torch.cuda.synchronize()
+        for b, w, n in zip(bufs, wants, counts):
+            if not (b.cpu().numpy().view(np.uint16) == w.view(np.uint16)).all():
+                print(f"rank {rank}: all-reduce of {n} halfs (round {rnd}) differs from the rank-order fp32 sum")
+                ok = 0
+    n = 4000
+    mine = torch.from_numpy(np.random.default_rng(rank).standard_normal(n).astype(np.float16)).cuda()
+    out = torch.zeros(world * n, dtype=torch.float16, device="cuda")
+    assert L.q4_all_gather(comm.handle, C.c_void_p(s.cuda_stream), C.c_void_p(mine.data_ptr()), C.c_void_p(out.data_ptr()), n) == 0
+    torch.cuda.synchronize()
+    want = np.concatenate([np.random.default_rng(r).standard_normal(n).astype(np.float16) for r in range(world)])
+    if not (out.cpu().numpy().view(np.uint16) == want.view(np.uint16)).all():
+        print(f"rank {rank}: all-gather differs")
+        ok = 0
+    assert L.q4_all_reduce(comm.handle, C.c_void_p(s.cuda_stream), C.c_void_p(out.data_ptr()), 131072 + 8) == _lib.Q4_ERR_LIMIT
+    assert comm.status() == 0
+    if rank == 0:
+        print(f"TP{world} collectives: ranks identical: {bool(ok)}")
+    return ok
+
+
 def batch_mode(t, comm, cfg_name, path, rank, world):
     """Three sequences decoded together on the sharded model (q4_batch_*): eight prompt positions, then four generated ones;
     each sequence's logits against the single-GPU oracle fed the same ids, every rank holding the same bits."""
@@ -77,6 +120,14 @@ def main():
     if prefill and sys.argv[5] == "prefill":   # large all-reduces of the prefill through NCCL, the decode steps' small ones stay on the peer push
         comm.attach_nccl(dist)
         comm.set_backend(_lib.Q4_COMM_BACKEND_AUTO)
+    if len(sys.argv) > 5 and sys.argv[5] == "collectives":
+        ok = collectives_mode(comm, rank, world)
+        flag = torch.tensor([ok], device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        comm.close()
+        dist.barrier()
+        dist.destroy_process_group()
+        sys.exit(0 if int(flag.item()) == 1 else 1)
     t = Transformer(path, rank=rank, gpu_count=world, tp_mode=tp_mode, comm=comm.handle,
                     synthetic=(synth.CONFIGS[cfg_name], 7) if synthetic else None)
     vocab = synth.CONFIGS[cfg_name][5]
