@@ -109,8 +109,9 @@ __global__ void __launch_bounds__(kRowThreads) rmsnorm_rows_kernel(__half* o, co
 // depend on the position only and are computed once per block, in the reference's arithmetic (powf, cosf, sinf in fp32).
 // head_size <= 256. grid (rows, ceil((heads + kv_heads) / kRopeHeads)), block 256.
 constexpr int kRopeHeads = 4;
-__global__ void __launch_bounds__(256) rope_store_rows_kernel(__half* q, const __half* k, const __half* v, __half* kc, __half* vc, int n_heads, int n_kv_heads,
-                                                              int head_size, const int* row_seq, const int* row_pos, long long seq_stride, long long loff, float theta) {
+__global__ void __launch_bounds__(256) rope_store_rows_kernel(__half* q, const __half* k, const __half* v, int ldq, int ldkv, __half* kc, __half* vc, int n_heads,
+                                                              int n_kv_heads, int head_size, const int* row_seq, const int* row_pos, long long seq_stride, long long loff,
+                                                              float theta) {
     griddep_wait();   // launched with programmatic stream serialisation: wait for the producer, then let the consumer's prologue start
     griddep_launch_dependents();
     __shared__ float2 table[128];
@@ -119,8 +120,8 @@ __global__ void __launch_bounds__(256) rope_store_rows_kernel(__half* q, const _
     const int half_hs = head_size / 2;
     for (int i = threadIdx.x; i < half_hs; i += blockDim.x) table[i] = rope_cos_sin(pos, i, head_size, theta);
     __syncthreads();
-    __half* qr = q + (size_t)m * n_heads * head_size;
-    const size_t src0 = (size_t)m * n_kv_heads * head_size;
+    __half* qr = q + (size_t)m * ldq;      // ldq, ldkv: halfs between rows of q and of k / v (they may be slices of one wider buffer)
+    const size_t src0 = (size_t)m * ldkv;
     const size_t dst0 = (size_t)row_seq[m] * seq_stride + loff + (size_t)pos * n_kv_heads * head_size;
     const int h_first = blockIdx.y * kRopeHeads, h_end = min(h_first + kRopeHeads, n_heads + n_kv_heads);
     for (int e = threadIdx.x; e < (h_end - h_first) * half_hs; e += blockDim.x) {
@@ -144,7 +145,7 @@ __global__ void __launch_bounds__(256) rope_store_rows_kernel(__half* q, const _
 // A warp takes four keys per round (keys 4 (warp + 8 i) .. + 3) and issues their eight K/V loads together, so a round costs
 // one memory latency, not eight. head_size 128: a lane holds four dims. grid (heads, rows), block 256.
 constexpr int kAttWarps = 8, kAttKeys = 4;
-__global__ void __launch_bounds__(kAttWarps * 32) attention_rows_kernel(__half* out, const __half* q, const __half* kc, const __half* vc, int n_heads, int kv_mul,
+__global__ void __launch_bounds__(kAttWarps * 32) attention_rows_kernel(__half* out, const __half* q, int ldq, const __half* kc, const __half* vc, int n_heads, int kv_mul,
                                                                        const int* row_seq, const int* row_pos, long long seq_stride, long long loff, int kv_n) {
     griddep_wait();   // launched with programmatic stream serialisation: wait for the producer, then let the consumer's prologue start
     griddep_launch_dependents();
@@ -155,7 +156,7 @@ __global__ void __launch_bounds__(kAttWarps * 32) attention_rows_kernel(__half* 
     const __half* vb = vc + (size_t)row_seq[m] * seq_stride + loff + (size_t)(h / kv_mul) * HS + lane * 4;
     float qf[4];
     {
-        const uint2 qv = *reinterpret_cast<const uint2*>(q + ((size_t)m * n_heads + h) * HS + lane * 4);
+        const uint2 qv = *reinterpret_cast<const uint2*>(q + (size_t)m * ldq + (size_t)h * HS + lane * 4);
         const __half2* qh = reinterpret_cast<const __half2*>(&qv);
         qf[0] = __low2float(qh[0]); qf[1] = __high2float(qh[0]); qf[2] = __low2float(qh[1]); qf[3] = __high2float(qh[1]);
     }
@@ -242,7 +243,7 @@ __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
 }
 
 // grid (heads, ceil(n / 64)), block 128. kc / vc point at this layer's cache rows of the sequence (position 0).
-__global__ void __launch_bounds__(128) attention_prefill_kernel(__half* out, const __half* q, const __half* kc, const __half* vc, int n_heads, int kv_mul,
+__global__ void __launch_bounds__(128) attention_prefill_kernel(__half* out, const __half* q, int ldq, const __half* kc, const __half* vc, int n_heads, int kv_mul,
                                                                 int n, int pos0, int kv_n) {
     griddep_wait();   // launched with programmatic stream serialisation: wait for the producer, then let the consumer's prologue start
     griddep_launch_dependents();
@@ -261,8 +262,8 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(__half* out, con
     // Q fragments: 8 k-steps of 16 dims; rows past the prompt read as zero
     uint32_t qa[8][4];
     {
-        const __half* qa_p = q + ((size_t)row_a * n_heads + h) * HS;
-        const __half* qb_p = q + ((size_t)row_b * n_heads + h) * HS;
+        const __half* qa_p = q + (size_t)row_a * ldq + (size_t)h * HS;
+        const __half* qb_p = q + (size_t)row_b * ldq + (size_t)h * HS;
 #pragma unroll
         for (int s = 0; s < 8; s++) {
             qa[s][0] = row_a < n ? *reinterpret_cast<const uint32_t*>(qa_p + 16 * s + 2 * t) : 0u;
@@ -367,25 +368,28 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(__half* out, con
     }
 }
 
-// ffn_matvec_silu's epilogue (gpu_kernels.h:278-281) on two GEMM results: h = silu(gate) * up in fp32, fp16 out. n % 8 == 0.
-__global__ void silu_mul_rows_kernel(__half* h, const __half* gate, const __half* up, size_t n) {
+// ffn_matvec_silu's epilogue (gpu_kernels.h:278-281) on the result of the fused gate|up GEMM: row m of gu holds the hid gate
+// values and then the hid up values; h[m][j] = silu(gate) * up in fp32, fp16 out. hid % 8 == 0.
+__global__ void silu_mul_rows_kernel(__half* h, const __half* gu, int hid, int rows) {
     griddep_wait();   // launched with programmatic stream serialisation: wait for the producer, then let the consumer's prologue start
     griddep_launch_dependents();
-    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n / 8; i += (size_t)gridDim.x * blockDim.x) {
-        const uint4 gv = reinterpret_cast<const uint4*>(gate)[i], uv = reinterpret_cast<const uint4*>(up)[i];
+    const int per_row = hid / 8;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < (size_t)rows * per_row; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t m = i / per_row, j = i - m * per_row;
+        const uint4 gv = reinterpret_cast<const uint4*>(gu + m * 2 * hid)[j], uv = reinterpret_cast<const uint4*>(gu + m * 2 * hid + hid)[j];
         const __half2* gh = reinterpret_cast<const __half2*>(&gv);
         const __half2* uh = reinterpret_cast<const __half2*>(&uv);
         uint4 o;
         __half2* oh = reinterpret_cast<__half2*>(&o);
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const float2 g = __half22float2(gh[j]), u = __half22float2(uh[j]);
+        for (int jj = 0; jj < 4; jj++) {
+            const float2 g = __half22float2(gh[jj]), u = __half22float2(uh[jj]);
             float a = g.x, b = g.y;
             a *= 1.0f / (1.0f + expf(-a));
             b *= 1.0f / (1.0f + expf(-b));
-            oh[j] = __floats2half2_rn(a * u.x, b * u.y);
+            oh[jj] = __floats2half2_rn(a * u.x, b * u.y);
         }
-        reinterpret_cast<uint4*>(h)[i] = o;
+        reinterpret_cast<uint4*>(h + m * hid)[j] = o;
     }
 }
 
@@ -571,11 +575,15 @@ __global__ void __launch_bounds__(1024) argmax_rows_kernel(const __half* logits,
 // ------------------------------------------------------------------------------------------------------------
 struct q4_rows {
     int cap = 0;   // rows the buffers hold
-    __half *X = nullptr, *XB = nullptr, *Q = nullptr, *K = nullptr, *V = nullptr, *ATT = nullptr, *G = nullptr, *U = nullptr;
+    __half *X = nullptr, *XB = nullptr, *Q = nullptr, *K = nullptr, *V = nullptr, *ATT = nullptr, *G = nullptr;
+    __half *QKV = nullptr, *GU = nullptr;   // GEMM path: [rows][q_n + 2 kv_n] and [rows][2 hid], written by one GEMM each
     int *row_seq = nullptr, *row_pos = nullptr;
     void* ws = nullptr;
     size_t ws_bytes = 0;
-    std::vector<uint32_t*> wi;   // [layer * 7 + matrix] interleaved copy of the packed weights (q k v o gate up down)
+    // GEMM path, per layer four matrices: q|k|v and gate|up stacked along the output axis (one launch each), o, down.
+    // Interleaved copy of the packed words, and for the stacked ones a copy of zeros and scales in the same order.
+    struct GemmMat { uint32_t* wi; q4_qweight w; int K, N; };
+    std::vector<GemmMat> gm;     // [layer * 4 + {0 qkv, 1 o, 2 gate|up, 3 down}]
     std::vector<void*> allocs;
 };
 
@@ -601,11 +609,6 @@ int q4_rows_status(q4_model* m) {
     return st[0];
 }
 
-static const DevQW* layer_mats(const DevLayer& L, int i) {
-    const DevQW* a[7] = {&L.q, &L.k, &L.v, &L.o, &L.gate, &L.up, &L.down};
-    return a[i];
-}
-
 // More than this many rows go through the tcgen05 GEMM, fewer through the mma.sync kernels that stream the packed weights.
 constexpr int kSkinnyRows = 16;
 
@@ -617,16 +620,40 @@ static int rows_prepare(q4_model* m, int rows) {
     const q4_config& c = m->cfg;
     int e;
 #define RTRY(expr) do { e = (expr); if (e != Q4_OK) return e; } while (0)
-    if (r->wi.empty() && rows > kSkinnyRows) {
-        r->wi.assign((size_t)c.n_layers * 7, nullptr);
-        for (int l = 0; l < c.n_layers; l++)
-            for (int i = 0; i < 7; i++) {
-                const DevQW* q = layer_mats(m->layers[l], i);
-                uint32_t* d = nullptr;
-                RTRY(rows_alloc(r, (void**)&d, (size_t)q->N * q4_pw(q->K) * 4));
-                RTRY(q4_gemm_interleave_weights(nullptr, d, q->w.weight, q->K, q->N));
-                r->wi[(size_t)l * 7 + i] = d;
+    if (r->gm.empty() && rows > kSkinnyRows) {
+        r->gm.assign((size_t)c.n_layers * 4, q4_rows::GemmMat{});
+        for (int l = 0; l < c.n_layers; l++) {
+            const DevLayer& L = m->layers[l];
+            const DevQW* groups[4][3] = {{&L.q, &L.k, &L.v}, {&L.o, nullptr, nullptr}, {&L.gate, &L.up, nullptr}, {&L.down, nullptr, nullptr}};
+            for (int i = 0; i < 4; i++) {
+                q4_rows::GemmMat& gmat = r->gm[(size_t)l * 4 + i];
+                const int K = groups[i][0]->K;
+                int N = 0, parts = 0;
+                for (int j = 0; j < 3 && groups[i][j]; j++) { N += groups[i][j]->N; parts++; }
+                gmat.K = K;
+                gmat.N = N;
+                RTRY(rows_alloc(r, (void**)&gmat.wi, (size_t)N * q4_pw(K) * 4));
+                uint32_t* zeros = nullptr;
+                uint16_t* scales = nullptr;
+                if (parts > 1) {
+                    RTRY(rows_alloc(r, (void**)&zeros, (size_t)N * q4_pz(K) * 4));
+                    RTRY(rows_alloc(r, (void**)&scales, (size_t)N * q4_groups(K) * 2));
+                }
+                size_t row0 = 0;
+                for (int j = 0; j < parts; j++) {
+                    const DevQW* q = groups[i][j];
+                    RTRY(q4_gemm_interleave_weights(nullptr, gmat.wi + row0 * q4_pw(K), q->w.weight, K, q->N));
+                    if (parts > 1) {
+                        Q4_CUDA_TRY(cudaMemcpy(zeros + row0 * q4_pz(K), q->w.zeros, (size_t)q->N * q4_pz(K) * 4, cudaMemcpyDeviceToDevice));
+                        Q4_CUDA_TRY(cudaMemcpy(scales + row0 * q4_groups(K), q->w.scales, (size_t)q->N * q4_groups(K) * 2, cudaMemcpyDeviceToDevice));
+                    }
+                    row0 += q->N;
+                }
+                gmat.w.weight = gmat.wi;   // (the GEMM reads the interleaved words; this field only has to be non-null)
+                gmat.w.zeros = parts > 1 ? zeros : groups[i][0]->w.zeros;
+                gmat.w.scales = parts > 1 ? scales : groups[i][0]->w.scales;
             }
+        }
         Q4_CUDA_TRY(cudaDeviceSynchronize());
     }
     if (rows > r->cap) {
@@ -639,11 +666,14 @@ static int rows_prepare(q4_model* m, int rows) {
         RTRY(rows_alloc(r, (void**)&r->V, 2 * (size_t)cap * m->kv_n));
         RTRY(rows_alloc(r, (void**)&r->ATT, 2 * (size_t)cap * m->q_n));
         RTRY(rows_alloc(r, (void**)&r->G, 2 * cap * hk));
-        RTRY(rows_alloc(r, (void**)&r->U, 2 * cap * hk));
+        if (cap > kSkinnyRows) {
+            RTRY(rows_alloc(r, (void**)&r->QKV, 2 * (size_t)cap * (m->q_n + 2 * m->kv_n)));
+            RTRY(rows_alloc(r, (void**)&r->GU, 2 * cap * 2 * hk));
+        }
         RTRY(rows_alloc(r, (void**)&r->row_seq, sizeof(int) * cap));
         RTRY(rows_alloc(r, (void**)&r->row_pos, sizeof(int) * cap));
         size_t ws = 0;
-        const int shapes[5][2] = {{c.dim, m->q_n}, {c.dim, m->kv_n}, {m->o_kc, c.dim}, {c.dim, m->h_kc}, {m->h_kc, c.dim}};
+        const int shapes[4][2] = {{c.dim, m->q_n + 2 * m->kv_n}, {m->o_kc, c.dim}, {c.dim, 2 * m->h_kc}, {m->h_kc, c.dim}};
         for (auto& s : shapes)
             for (int mm : {1, 16, 17, 64, 65, cap}) ws = std::max(ws, q4_matmul_q4_batched_workspace_bytes(std::min(mm, cap), s[0], s[1]));
         RTRY(rows_alloc(r, &r->ws, ws));
@@ -678,11 +708,12 @@ static int rows_layers(q4_model* m, cudaStream_t s, int n, __half* kc, __half* v
     const int heads = c.n_heads / g, kv_heads = c.n_kv_heads / g;
     int e;
 #define OP(expr) do { e = (expr); if (e != Q4_OK) return e; } while (0)
-    auto gemm = [&](__half* y, const __half* x, int l, int mat, const __half* resid, float rs) {
-        const DevQW* q = layer_mats(m->layers[l], mat);
-        return q4_matmul_q4_batched_residual(s, (uint16_t*)y, (const uint16_t*)x, &q->w, r->wi[(size_t)l * 7 + mat], n, q->K, q->N, (const uint16_t*)resid, rs,
-                                             r->ws, r->ws_bytes);
+    auto gemm = [&](__half* y, const __half* x, int l, int mat) {   // mat: 0 q|k|v, 1 o, 2 gate|up, 3 down
+        const q4_rows::GemmMat& gmat = r->gm[(size_t)l * 4 + mat];
+        return q4_matmul_q4_batched(s, (uint16_t*)y, (const uint16_t*)x, &gmat.w, gmat.wi, n, gmat.K, gmat.N, r->ws, r->ws_bytes);
     };
+    // q, k, v of the rows: three buffers (few-rows kernels) or three slices of the fused GEMM's output
+    const int nqkv = m->q_n + 2 * m->kv_n;
     const bool skinny = n <= kSkinnyRows;
     const bool overlap = pos0 < 0;   // batched decode: programmatic dependent launches (see launch_rows)
     for (int l = 0; l < c.n_layers; l++) {
@@ -692,20 +723,24 @@ static int rows_layers(q4_model* m, cudaStream_t s, int n, __half* kc, __half* v
         if (skinny) {
             OP(q4_qkv_matmul_rows(s, (uint16_t*)r->Q, (uint16_t*)r->K, (uint16_t*)r->V, (const uint16_t*)r->XB, &L.q.w, &L.k.w, &L.v.w, n, dim, m->q_n, m->kv_n));
         } else {
-            OP(gemm(r->Q, r->XB, l, 0, nullptr, 0.f));
-            OP(gemm(r->K, r->XB, l, 1, nullptr, 0.f));
-            OP(gemm(r->V, r->XB, l, 2, nullptr, 0.f));
+            OP(gemm(r->QKV, r->XB, l, 0));
         }
-        launch_rows(overlap, rope_store_rows_kernel, dim3(n, q4_div_up(heads + kv_heads, kRopeHeads)), dim3(256), 0, s, r->Q, r->K, r->V, kc, vc, heads, kv_heads, hs, r->row_seq, r->row_pos, seq_stride,
-                                                                              loff, c.rope_theta);
-        if (pos0 >= 0 && n > 16)
-            launch_rows(overlap, attention_prefill_kernel, dim3(dim3(heads, q4_div_up(n, kAtRows))), dim3(128), 0, s, r->ATT, r->Q, kc + loff, vc + loff, heads, m->kv_mul, n, pos0, m->kv_n);
+        __half* qp = skinny ? r->Q : r->QKV;
+        const __half* kp = skinny ? r->K : r->QKV + m->q_n;
+        const __half* vp = skinny ? r->V : r->QKV + m->q_n + m->kv_n;
+        const int ldq = skinny ? m->q_n : nqkv, ldkv = skinny ? m->kv_n : nqkv;
+        launch_rows(overlap, rope_store_rows_kernel, dim3(n, q4_div_up(heads + kv_heads, kRopeHeads)), dim3(256), 0, s, qp, kp, vp, ldq, ldkv, kc, vc, heads, kv_heads, hs,
+                    r->row_seq, r->row_pos, seq_stride, loff, c.rope_theta);
+        if (pos0 >= 0 && !skinny)
+            launch_rows(overlap, attention_prefill_kernel, dim3(heads, q4_div_up(n, kAtRows)), dim3(128), 0, s, r->ATT, (const __half*)qp, ldq, kc + loff, vc + loff, heads,
+                        m->kv_mul, n, pos0, m->kv_n);
         else
-            launch_rows(overlap, attention_rows_kernel, dim3(heads, n), dim3(kAttWarps * 32), 0, s, r->ATT, r->Q, kc, vc, heads, m->kv_mul, r->row_seq, r->row_pos, seq_stride, loff, m->kv_n);
+            launch_rows(overlap, attention_rows_kernel, dim3(heads, n), dim3(kAttWarps * 32), 0, s, r->ATT, (const __half*)qp, ldq, kc, vc, heads, m->kv_mul, r->row_seq,
+                        r->row_pos, seq_stride, loff, m->kv_n);
         // x = o_proj(att) + x / g, summed over the ranks (gpu_kernels.h:237-238, llama2_q4.cu:472-476)
         if (skinny) OP(q4_matmul_q4_rows(s, (uint16_t*)r->X, (const uint16_t*)r->ATT, &L.o.w, n, m->o_kc, dim, (const uint16_t*)r->X, 1.0f / g));
         else {   // the normalised rows in XB are spent: the projection lands there, then x = projection + x / g
-            OP(gemm(r->XB, r->ATT, l, 3, nullptr, 0.f));
+            OP(gemm(r->XB, r->ATT, l, 1));
             launch_rows(overlap, add_residual_rows_kernel, dim3(148 * 4), dim3(256), 0, s, r->X, (const __half*)r->XB, 1.0f / g, (size_t)n * dim);
         }
         OP(rows_all_reduce(m, s, r->X, (size_t)n * dim, pos0 >= 0));
@@ -715,10 +750,9 @@ static int rows_layers(q4_model* m, cudaStream_t s, int n, __half* kc, __half* v
             OP(q4_ffn_silu_rows(s, (uint16_t*)r->G, (const uint16_t*)r->XB, &L.gate.w, &L.up.w, n, dim, m->h_kc));
             OP(q4_matmul_q4_rows(s, (uint16_t*)r->X, (const uint16_t*)r->G, &L.down.w, n, m->h_kc, dim, (const uint16_t*)r->X, 1.0f / g));
         } else {
-            OP(gemm(r->G, r->XB, l, 4, nullptr, 0.f));
-            OP(gemm(r->U, r->XB, l, 5, nullptr, 0.f));
-            launch_rows(overlap, silu_mul_rows_kernel, dim3(148 * 4), dim3(256), 0, s, r->G, r->G, r->U, (size_t)n * m->h_kc);
-            OP(gemm(r->XB, r->G, l, 6, nullptr, 0.f));
+            OP(gemm(r->GU, r->XB, l, 2));
+            launch_rows(overlap, silu_mul_rows_kernel, dim3(148 * 4), dim3(256), 0, s, r->G, (const __half*)r->GU, m->h_kc, n);
+            OP(gemm(r->XB, r->G, l, 3));
             launch_rows(overlap, add_residual_rows_kernel, dim3(148 * 4), dim3(256), 0, s, r->X, (const __half*)r->XB, 1.0f / g, (size_t)n * dim);
         }
         OP(rows_all_reduce(m, s, r->X, (size_t)n * dim, pos0 >= 0));
