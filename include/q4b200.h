@@ -236,7 +236,7 @@ int q4_comm_reset(q4_comm* comm);
  * the other calls return Q4_ERR_UNSUPPORTED_SIZE. One rank creates the id, the caller distributes its 128 bytes,
  * then every rank calls q4_comm_nccl_init (collective) on its communicator. The backend chooses the transport per
  * call: P2P (default) = one-shot peer push; NCCL; AUTO = by message size from the measured latency table (peer push
- * up to 32 KB, NCCL above). */
+ * up to 32 KB on two GPUs and up to 128 KB on more, NCCL above). */
 typedef struct { char internal[128]; } q4_nccl_id; /* same size and meaning as ncclUniqueId */
 #define Q4_COMM_BACKEND_P2P 0
 #define Q4_COMM_BACKEND_NCCL 1

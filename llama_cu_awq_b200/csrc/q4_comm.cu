@@ -12,7 +12,8 @@
 // Parity p is reused at epoch e+2; a rank can only reach e+2 after every peer published e+1, which a peer does
 // only after it finished reading its epoch-e slots, so no slot is overwritten while it is still being read.
 // No host synchronisation is involved, so the call can be captured in a CUDA graph.
-// Waits are bounded: after kWaitLimitNs the kernel records Q4_ERR_TIMEOUT in the status word and returns.
+// Waits are bounded: after the communicator's wait limit (q4_comm_set_wait_limit_ns, default 2 s) the kernel records
+// Q4_ERR_TIMEOUT in the status word and returns.
 #include <chrono>
 #include <dlfcn.h>
 #include <mutex>
@@ -383,11 +384,13 @@ extern "C" int q4_comm_set_backend(q4_comm* comm, int backend) {
 
 // Which implementation serves a message of `count` halfs. AUTO follows the measured latency table: the one-shot peer
 // push for the vectors of this path (8-16 KB), NCCL for large messages when it is attached.
-constexpr int kAutoNcclAbove = 16384;   // halfs (32 KB): measured on 2 B200s, the peer push takes 8.5-9.0 us up to 16 KB against NCCL's 10.2-10.3 us; at 64 KB NCCL wins (10.8 vs 11.9 us)
+// Measured, us per call, peer push vs NCCL: 2 GPUs 8.7 / 9.2 at 8 KB, 9.3 / 10.1 at 16 KB, 10.2 / 10.0 at 32 KB, 12.3 / 10.3 at
+// 64 KB; 4 GPUs 9.3 / 15.1 at 8 KB, 12.2 / 16.0 at 32 KB, 16.3 / 16.4 at 64 KB, 14.8 / 16.7 at 128 KB, 19.2 / 16.5 at 256 KB.
+static int auto_nccl_above(int gpu_count) { return gpu_count <= 2 ? 16384 : 65536; }   // halfs: 32 KB on two GPUs, 128 KB on more
 static bool use_nccl(const q4_comm* c, int count) {
     if (!c->nccl) return false;
     if (c->backend == Q4_COMM_BACKEND_NCCL) return true;
-    return c->backend == Q4_COMM_BACKEND_AUTO && count > kAutoNcclAbove;
+    return c->backend == Q4_COMM_BACKEND_AUTO && count > auto_nccl_above(c->gpu_count);
 }
 
 bool q4_comm_prefers_nccl(const q4_comm* c, int count) { return c && use_nccl(c, count); }

@@ -5,9 +5,9 @@
 // still read once per STEP, so the op stays bound by HBM as long as the per-weight work is small. That is what this
 // kernel is built for; the tcgen05 GEMM (q4_gemm.cu) takes over from M > 16, where the contraction starts to matter.
 //
-// Work split: a CTA (8 warps) owns 16 * MT output features of one launch and the whole K axis; warp w takes the w-th
-// eighth of the 128-input groups, and the eight partial tiles are summed in warp order through shared memory (fixed
-// order: results are bit-reproducible). Inside a warp the product runs on mma.sync m16n8k16 (fp16 in, fp32 out) with
+// Work split: a unit is 16 * MT output features of one launch over the whole K axis; one persistent CTA (8 warps) per SM
+// walks the units; warp w takes the w-th eighth of a unit's 128-input groups, and the eight partial tiles are summed in
+// warp order through shared memory (fixed order: results are bit-reproducible). Inside a warp the product runs on mma.sync m16n8k16 (fp16 in, fp32 out) with
 // the weights as the 16-row operand and the batch as the 8-column one. The k index of an MMA is only a summation
 // label, so the packed words are used as they lie in the file: thread (g, t) of the warp loads 16 bytes = 32 inputs of
 // feature rows g and g + 8 at input offset 32 t of the group, unpacks a word into the half2 pairs (q0,q4) (q1,q5)
