@@ -56,6 +56,22 @@ def test_7b_projection_shapes(M, K, N):
     assert (y2.cpu().numpy().view(np.uint16) == y.view(np.uint16)).all()
 
 
+def test_back_to_back_launches_are_bit_reproducible():
+    """Forty launches queued back to back on one workspace (their prologues overlap the previous launch's tail through
+    programmatic dependent launch): every result equals the first, bit for bit."""
+    M, K, N = 512, 4096, 11008
+    q, x, y, mm, xd = _case(M, K, N, seed=3, interleave=True)
+    first = torch.from_numpy(y).cuda()
+    outs = [torch.zeros_like(first) for _ in range(8)]
+    for _ in range(5):
+        for o in outs:
+            mm(o, xd, M)
+        torch.cuda.synchronize()
+        for o in outs:
+            assert torch.equal(o, first)
+    assert mm.status() == 0
+
+
 def test_rejects_unsupported_arguments():
     from llama_cu_awq_b200 import _lib
     rng = np.random.default_rng(0)
