@@ -231,12 +231,21 @@ def run_reference(args, rank, world):
 # ---------------------------------------------------------------------------------------------------------------
 # our arm
 # ---------------------------------------------------------------------------------------------------------------
-def time_generations(t, prompt, fwd_path, steps, warmup, barrier, torch, dist, on_timed_start=None):
-    """Device-timed tokens/s over `steps` generations (max over ranks), and the token ids of the last one."""
+def time_generations(t, prompt, fwd_path, steps, warmup, barrier, torch, dist, on_timed_start=None, prompt_one_pass=False):
+    """Device-timed tokens/s over `steps` generations (max over ranks), and the token ids of the last one. With
+    prompt_one_pass the prompt positions but the last go through q4_model_prefill (what q4_generate does with
+    Q4_PATH_PROMPT_ONE_PASS); the positions counted are the same."""
+    def run():
+        first = 0
+        if prompt_one_pass and N_PROMPT > 1:
+            t.prefill(N_PROMPT - 1, gen_token=False)
+            first = N_PROMPT - 1
+        for pos in range(first, STEPS_PER_GEN - 1):  # the reference counts pos-1 = 271 timed positions per run
+            t.forward(gen_token=pos >= N_PROMPT - 1, path=fwd_path)
+
     def one():
         t.reset(prompt, 0)
-        for pos in range(STEPS_PER_GEN - 1):  # the reference counts pos-1 = 271 timed positions per run
-            t.forward(gen_token=pos >= N_PROMPT - 1, path=fwd_path)
+        run()
 
     for _ in range(warmup):
         one()
@@ -251,8 +260,7 @@ def time_generations(t, prompt, fwd_path, steps, warmup, barrier, torch, dist, o
         barrier()
         with torch.cuda.stream(t.stream):
             e0.record(t.stream)
-            for pos in range(STEPS_PER_GEN - 1):
-                t.forward(gen_token=pos >= N_PROMPT - 1, path=fwd_path)
+            run()
             e1.record(t.stream)
         t.synchronize()
         total_ms += e0.elapsed_time(e1)
@@ -675,6 +683,21 @@ def main():
         roof = {"bound": "hbm", "kernel": "q4_gemv_kernel (fused gate/up + SiLU)", "achieved": k.get("gbs"), "peak": pk["hbm_gbs"], "unit": "GB/s",
                 "frac": k.get("frac_of_hbm_peak"), "peak_kind": pk_kind, "traffic": None, "bytes_per_launch": k.get("bytes"), "us_per_launch": k.get("us")}
     if not args.no_extras:
+        try:
+            # The same workload with the prompt (but its last position) in one pass, as a user of q4_generate gets it with
+            # Q4_PATH_PROMPT_ONE_PASS: the metric above keeps the reference's token-by-token prompt so that the two arms
+            # measure the same thing.
+            v1, _, tok1 = time_generations(t, prompt, fwd_path, max(1, args.steps - 1), 1, barrier, torch, dist, prompt_one_pass=True)
+            barrier()
+            toks1, timed1, secs1 = t.generate(prompt, STEPS_PER_GEN, path=fwd_path, prompt_one_pass=True)
+            st1 = torch.tensor([secs1], dtype=torch.float64, device="cuda")
+            if dist is not None:
+                dist.all_reduce(st1, op=dist.ReduceOp.MAX)
+            extra["prompt_one_pass"] = {"value": v1, "e2e": timed1 / float(st1.item()), "unit": "tok/s",
+                                        "tokens_match_e2e": bool((tok1 == toks1[:STEPS_PER_GEN]).all()),
+                                        "first_generated_id_matches_token_by_token": bool(tok1[N_PROMPT] == tokens_dev[N_PROMPT])}
+        except Exception as e:
+            extra["prompt_one_pass_error"] = str(e)[:300]
         try:
             if comm is not None and _lib.lib().q4_comm_nccl_available():
                 comm.attach_nccl(dist)   # the [rows x dim] all-reduces of the GEMM paths go through NCCL; one-token ones stay on the peer push

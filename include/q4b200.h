@@ -337,6 +337,10 @@ int q4_model_status(q4_model* model);
 /* generate_thread(): the token loop with the reference's timing window (llama2_q4.cu:708-745). Runs `steps`
  * positions starting from the n_prompt given ids, stops at EOS (id 2). out_tokens receives tokens[0..steps];
  * *timed_tokens = pos-1 and *seconds is the wall time of the loop. */
+/* OR-ed into `path`: the prompt positions but the last go through q4_model_prefill in one pass (the last prompt
+ * position and everything after it through `path` as usual); models the many-row kernels do not serve fall back to the
+ * token loop. Same timing window, same *timed_tokens. */
+#define Q4_PATH_PROMPT_ONE_PASS 0x100
 int q4_generate(q4_model* model, const int* prompt_tokens, int n_prompt, int steps, int path, int* out_tokens,
                 int* timed_tokens, double* seconds);
 /* Algorithmic bytes one token at position `pos` reads and writes on this rank (weights, metadata,

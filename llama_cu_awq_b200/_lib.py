@@ -19,6 +19,7 @@ Q4_ERR_BAD_MODEL = 4
 Q4_ERR_INVALID = 5
 Q4_ERR_TIMEOUT = 6
 Q4_ERR_LIMIT = 7
+Q4_PATH_PROMPT_ONE_PASS = 0x100
 Q4_MAX_SEQ_LEN = 128 * 1024
 Q4_TP_NONE, Q4_TP_COLUMN, Q4_TP_HYBRID = 0, 1, 2
 Q4_COMM_BACKEND_P2P, Q4_COMM_BACKEND_NCCL, Q4_COMM_BACKEND_AUTO = 0, 1, 2

@@ -59,6 +59,7 @@ private:
     fprintf(stderr, "  -x <string> tensor parallel mode: none|column|hybrid, default none\n");
     fprintf(stderr, "  -k <string> path to a file of prompt token ids (replaces -i/-f)\n");
     fprintf(stderr, "  -g <int>    forward path: 0 per-op launches, 1 CUDA graph, 2 persistent fused kernel (default; falls back to 1)\n");
+    fprintf(stderr, "  -b <0|1>    1: process the prompt in one pass (tensor-core prefill) instead of token by token, default 0\n");
     exit(EXIT_FAILURE);
 }
 
@@ -113,7 +114,7 @@ void load_thread(Shared* sh, const char* path, int rank, int gpu_count, int tp_m
 // The token loop of generate_thread (llama2_q4.cu:683-757) with rank 0 streaming the text.
 struct SamplerArgs { float temperature, topp; unsigned long long seed; };
 
-void generate_thread(Shared* sh, const Vocab* vocab, const std::vector<int>* prompt, int steps, int rank, int fwd_path, SamplerArgs sa) {
+void generate_thread(Shared* sh, const Vocab* vocab, const std::vector<int>* prompt, int steps, int rank, int fwd_path, SamplerArgs sa, int prompt_one_pass) {
     cudaSetDevice(rank);
     q4_model* m = sh->models[rank];
     q4_config cfg;
@@ -127,6 +128,21 @@ void generate_thread(Shared* sh, const Vocab* vocab, const std::vector<int>* pro
     if (e) die(e, "build_sampler");
     int token = (*prompt)[0], next = 0, pos = 0;
     const auto start = std::chrono::steady_clock::now();
+    const int n_prompt = (int)prompt->size();
+    if (prompt_one_pass && n_prompt > 1 && steps > n_prompt - 1) {
+        // -b 1: the prompt but its last position in one pass (q4_model_prefill); the text of those positions is the prompt
+        // itself, so it is echoed at once. Shapes the many-row kernels do not serve keep the token loop.
+        e = q4_model_prefill(m, stream, n_prompt - 1, 0);
+        if (e == Q4_OK) {
+            if (rank == 0)
+                for (int i = 1; i < n_prompt - 1; i++) {   // what the loop would have printed at positions 1 .. n_prompt - 2
+                    if (vocab->loaded()) fputs(vocab->decode((*prompt)[i - 1], (*prompt)[i]).c_str(), stdout);
+                    else printf(" %d", (*prompt)[i]);
+                }
+            pos = n_prompt - 1;
+            token = (*prompt)[pos - 1];
+        } else if (e != Q4_ERR_UNSUPPORTED_SIZE) die(e, "prefill");
+    }
     while (pos < steps) {
         cudaStreamSynchronize(stream);
         e = q4_model_forward(m, stream, pos >= (int)prompt->size() - 1, fwd_path);
@@ -161,7 +177,7 @@ int main(int argc, char* argv[]) {
     const char* tokenizer_path = "tokenizer.bin";
     const char* dataset_path = nullptr;
     const char* token_file = nullptr;
-    int steps = 0, fwd_path = 2;
+    int steps = 0, fwd_path = 2, prompt_one_pass = 0;
     std::string prompt;
     bool have_prompt = false;
     float temperature = 0.5f, topp = 0.6f;  // the reference's defaults in code (llama2_q4.cu:852-853)
@@ -184,6 +200,7 @@ int main(int argc, char* argv[]) {
             case 'q': dataset_path = v; break;
             case 'k': token_file = v; break;
             case 'g': fwd_path = atoi(v); break;
+            case 'b': prompt_one_pass = atoi(v); break;
             case 'x':
                 if (!strcmp(v, "none")) tp_mode = Q4_TP_NONE;
                 else if (!strcmp(v, "column")) tp_mode = Q4_TP_COLUMN;
@@ -263,7 +280,7 @@ int main(int argc, char* argv[]) {
 
     {
         std::vector<std::thread> th;
-        for (int r = 0; r < gpu_count; r++) th.emplace_back(generate_thread, &sh, &vocab, &prompt_tokens, steps, r, fwd_path, SamplerArgs{temperature, topp, rng_seed});
+        for (int r = 0; r < gpu_count; r++) th.emplace_back(generate_thread, &sh, &vocab, &prompt_tokens, steps, r, fwd_path, SamplerArgs{temperature, topp, rng_seed}, prompt_one_pass);
         for (auto& t : th) t.join();
     }
     for (int r = 0; r < gpu_count; r++) {

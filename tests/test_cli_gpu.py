@@ -94,3 +94,15 @@ def test_cli_hybrid_all_gpus(model_and_prompt, fwd_path):
     same = sum(int(x == y) for x, y in zip(ids, single))
     assert same >= len(single) // 2, (ids, single)
     assert ids[:4] == single[:4]
+
+
+def test_cli_prompt_in_one_pass(model_and_prompt):
+    """-b 1: the prompt but its last position through q4_model_prefill; same ids as q4_generate with the same option."""
+    path, tf, prompt = model_and_prompt
+    out = run_cli(path, tf, ["-x", "none", "-g", "2", "-b", "1"])
+    ids = generated_ids(out)
+    t = Transformer(path)
+    toks, timed, _ = t.generate(prompt, 24, path=2, prompt_one_pass=True)
+    t.close()
+    assert ids == [int(v) for v in toks[1:1 + len(ids)]]
+    assert abs(len(ids) - timed) <= 1
