@@ -247,6 +247,7 @@ def time_generations(t, prompt, fwd_path, steps, warmup, barrier, torch, dist, o
         t.reset(prompt, 0)
         run()
 
+    barrier()   # ranks start together: a rank that comes late (rank 0 runs the CPU oracle) must not leave its peers' kernels waiting
     for _ in range(warmup):
         one()
     t.synchronize()
@@ -705,6 +706,8 @@ def main():
             extra.update(prefill_and_batch(t, cfg, fwd_path, value, rank, world, dist, torch, barrier, pk))
         except Exception as e:   # reported, not fatal: the headline line stays valid
             extra["prefill_batch_error"] = str(e)[:300]
+    if not args.no_extras:
+        extra["status_after_extras"] = t.status()   # 0, or the code a bounded device-side wait recorded during the extra legs
     t.close()
     if comm:
         comm.close()
