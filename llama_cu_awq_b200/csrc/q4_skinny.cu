@@ -5,9 +5,9 @@
 // still read once per STEP, so the op stays bound by HBM as long as the per-weight work is small. That is what this
 // kernel is built for; the tcgen05 GEMM (q4_gemm.cu) takes over from M > 16, where the contraction starts to matter.
 //
-// Work split: a unit is 16 * MT output features of one launch over the whole K axis; one persistent CTA (8 warps) per SM
-// walks the units; warp w takes the w-th eighth of a unit's 128-input groups, and the eight partial tiles are summed in
-// warp order through shared memory (fixed order: results are bit-reproducible). Inside a warp the product runs on mma.sync m16n8k16 (fp16 in, fp32 out) with
+// Work split: a unit is 16 * MT output features of one launch over the whole K axis; one persistent CTA (12 warps; 8 for
+// 9-16 rows) per SM walks the units; warp w takes the w-th share of a unit's 128-input groups, and the warps' partial
+// tiles are summed in warp order through shared memory (fixed order: results are bit-reproducible). Inside a warp the product runs on mma.sync m16n8k16 (fp16 in, fp32 out) with
 // the weights as the 16-row operand and the batch as the 8-column one. The k index of an MMA is only a summation
 // label, so the packed words are used as they lie in the file: thread (g, t) of the warp loads 16 bytes = 32 inputs of
 // feature rows g and g + 8 at input offset 32 t of the group, unpacks a word into the half2 pairs (q0,q4) (q1,q5)
@@ -59,26 +59,26 @@ __device__ __forceinline__ void unpack8(uint32_t w, uint32_t zlo, uint32_t zhi, 
 }
 
 #ifndef SK_WARPS
-#define SK_WARPS 8
+#define SK_WARPS 12
 #endif
 #ifndef SK_D1
-#define SK_D1 4
+#define SK_D1 3
 #endif
 #ifndef SK_D2
-#define SK_D2 4
+#define SK_D2 2
 #endif
 #ifndef SK_D22
 #define SK_D22 3
 #endif
 // warps of a CTA = K slices of a unit
-__host__ __device__ constexpr int warps_of(int MT, int NT) { return SK_WARPS; }
+__host__ __device__ constexpr int warps_of(int MT, int NT) { return NT == 2 ? 8 : SK_WARPS; }   // (16 batch rows need the registers of 8-warp CTAs)
 
 // MT: 16-feature tiles per unit (1 or 2); NT: 8-row batch tiles (1: M <= 8, 2: M <= 16); SILU: tile 0 = gate, tile 1 = up.
 // Persistent: one CTA per SM walks units blockIdx.x, blockIdx.x + gridDim.x, ...; a warp's weight loads run D groups ahead
 // of its math ACROSS unit boundaries and its x fragments one group ahead (a unit gives a warp only G / kWarps groups - four
 // at K = 4096 - so a pipeline that restarted per unit would spend its time on load latency, and one-unit CTAs would
-// quantise the work badly over the SMs). Few warps with everything they need already in flight, rather than many warps
-// that each wait: the registers of the SM go to the prefetch stages.
+// quantise the work badly over the SMs). Measured on the four 7B ops with 8 rows (us): 8 warps with 4 groups ahead
+// 4.4 / 10.4 / 11.9 / 19.9; 12 warps with 2-3 ahead 4.5 / 9.4 / 10.6 / 16.6; 16 warps with 2 ahead 4.8 / 9.6 / 11.6 / 19.2.
 template <int MT, int NT, bool SILU>
 __global__ void __launch_bounds__(warps_of(MT, NT) * 32, 1) q4_skinny_kernel(const SkParams p) {
     constexpr int kWarps = warps_of(MT, NT);
