@@ -186,7 +186,7 @@ void q4o_matvec(f16 *y, const f16 *x, const uint32_t *weight, const uint32_t *ze
     }
 }
 
-/* fp32 (unrounded) variant used to judge the CUDA kernels against the exact sum. */
+/* fp32 (unrounded) variant used to compare the CUDA kernels with the exact sum. */
 void q4o_matvec_f32(float *y, const f16 *x, const uint32_t *weight, const uint32_t *zeros, const f16 *scales, int K, int N) {
     int PW = q4o_packed_wt_height(K), PZ = q4o_packed_zeros_height(K), G = q4o_groups(K);
 #pragma omp parallel for schedule(static)

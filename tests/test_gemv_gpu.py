@@ -44,7 +44,7 @@ def test_matvec_parity(K, N):
     torch.cuda.synchronize()
     ref = O.matvec(x, q, K, N, order=1)
     r, _ = assert_close(y.cpu().numpy(), ref, f"matvec {K}x{N}")
-    assert r < 4e-3  # well inside the tolerance; also judged against the unrounded sum:
+    assert r < 4e-3  # well inside the tolerance; also compared with the unrounded sum:
     assert_close(y.cpu().numpy(), O.matvec_f32(x, q, K, N), f"matvec {K}x{N} vs f64", max_rel=4e-3)
 
 
