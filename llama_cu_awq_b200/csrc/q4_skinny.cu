@@ -301,6 +301,7 @@ __global__ void __launch_bounds__(warps_of(MT, NT) * 32, 1) q4_skinny_kernel(con
     }
 }
 
+constexpr int kSms = 148;   // B200: one persistent CTA per SM (a smaller part would only leave CTAs queued behind the first wave)
 constexpr size_t red_bytes(int MT, int NT) { return 2 * (size_t)warps_of(MT, NT) * MT * NT * 4 * 32 * sizeof(float); }
 
 int fill(SkParams& p, const uint16_t* x, int M, int K) {
@@ -328,14 +329,10 @@ SkMat sk_mat(const q4_qweight* w, uint16_t* y, int ldy, int tile0) {
 
 template <int MT, int NT, bool SILU>
 int launch_variant(const SkParams& p, cudaStream_t s) {
-    static bool attr_set = false;   // (the attribute is per function and per device context; setting it again is harmless)
-    const size_t smem = red_bytes(MT, NT);
-    if (!attr_set) {
-        Q4_CUDA_TRY(cudaFuncSetAttribute(q4_skinny_kernel<MT, NT, SILU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr_set = true;
-    }
+    constexpr size_t smem = red_bytes(MT, NT);
+    static_assert(smem <= 48 * 1024, "the reduction buffers fit the default dynamic shared memory limit: no per-device opt-in is needed");
     const int units = SILU ? p.total_tiles : p.total_tiles / MT;
-    Q4Launch L(dim3(units < 148 ? units : 148), dim3(warps_of(MT, NT) * 32), smem, s);
+    Q4Launch L(dim3(units < kSms ? units : kSms), dim3(warps_of(MT, NT) * 32), smem, s);
     Q4_CUDA_TRY(cudaLaunchKernelEx(&L.cfg, q4_skinny_kernel<MT, NT, SILU>, p));
     return Q4_OK;
 }
@@ -347,7 +344,7 @@ int launch(const SkParams& p, cudaStream_t s) {
     // Two tiles per unit halve the reads of x but double the grain the work is dealt in: take pairs when the most loaded
     // SM then carries no more features than with single tiles.
     const int t = p.total_tiles;
-    const bool pair = (t % 2 == 0) && 2 * q4_div_up(t / 2, 148) <= q4_div_up(t, 148);
+    const bool pair = (t % 2 == 0) && 2 * q4_div_up(t / 2, kSms) <= q4_div_up(t, kSms);
     if (pair) return two ? launch_variant<2, 2, false>(p, s) : launch_variant<2, 1, false>(p, s);
     return two ? launch_variant<1, 2, false>(p, s) : launch_variant<1, 1, false>(p, s);
 }

@@ -106,3 +106,17 @@ def test_cli_prompt_in_one_pass(model_and_prompt):
     t.close()
     assert ids == [int(v) for v in toks[1:1 + len(ids)]]
     assert abs(len(ids) - timed) <= 1
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_cli_prompt_in_one_pass_hybrid(model_and_prompt):
+    """-b 1 with -x hybrid (thread per GPU): the prompt rows' all-reduce goes through the peer-push kernels; the echoed prompt
+    and the first generated ids agree with the single-GPU run of the same option."""
+    path, tf, _ = model_and_prompt
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="0,1")
+    out = run_cli(path, tf, ["-x", "hybrid", "-g", "2", "-b", "1"], env=env)
+    assert "[GPU: 0] achieved tok/s" in out and "[GPU: 1] achieved tok/s" in out
+    ids = generated_ids(out)
+    single = generated_ids(run_cli(path, tf, ["-x", "none", "-g", "2", "-b", "1"]))
+    assert ids[:4] == single[:4]
+    assert sum(int(x == y) for x, y in zip(ids, single)) >= len(single) // 2, (ids, single)
